@@ -1,0 +1,324 @@
+"""Model-level quantisation -- drop-in for the reference's src/fdk/models.py on the LUT path.
+
+Same surface: QuantisationConfig, QuantisedLinear (create / forward / state_dict keys
+weight_data, scale, lut), quantise(), Generator, count_ops, count_parameter_read_bytes,
+the custom-llama configs and the `python -m fdk.models` selector.  What differs is below
+the operator boundary: the `triton` kernel selector runs the native sm_100a kernels of
+libfdk_b200 on a tiled copy of the packed weights built once per module.
+
+Kernel selectors (QuantisationConfig.kernel):
+  "triton"         native fused kernel (name kept so existing configs keep working); bf16
+  "torch.compile"  the torch reference, dequantise then matmul (eager here)
+  "marlin", "marlin-lut"  the reference's fp16 4-bit selectors (models.py:107-125): same
+                   numbers (scale = absmax / 7, codes = round(w / s) + 8 clamped, values
+                   arange(-8, 8)), run by the same native kernel in its fp16 instantiation.
+"""
+
+from __future__ import annotations
+
+import copy
+import re
+import sys
+from dataclasses import dataclass
+from typing import Iterable, Literal
+
+import torch
+from torch import Tensor, nn
+
+from . import kernels, native
+
+# Quantised models
+
+
+@dataclass
+class QuantisationConfig:
+    bits: int
+    block_size: int
+    kernel: Literal["triton", "torch.compile", "marlin", "marlin-lut"] = "triton"
+    skip: str | None = "^lm_head$"
+
+
+def _pack_codes(indices: Tensor, bits: int) -> Tensor:
+    """[N, K] integer codes -> packed uint8 rows, first element of a byte in the high bits."""
+    n, k = indices.shape
+    idx = indices.to(torch.uint8)
+    if 8 % bits == 0:
+        per_byte = 8 // bits
+        place = 2 ** torch.arange(0, 8, bits, device=idx.device, dtype=torch.uint8).flip(0)
+        return idx.unflatten(-1, (-1, per_byte)).mul(place).sum(-1, dtype=torch.uint8)
+    # 3 bits: one MSB-first bit stream per row
+    shifts = torch.arange(bits - 1, -1, -1, device=idx.device, dtype=torch.uint8)
+    stream = ((idx[..., None] >> shifts) & 1).reshape(n, k * bits // 8, 8)
+    place = 2 ** torch.arange(7, -1, -1, device=idx.device, dtype=torch.uint8)
+    return stream.mul(place).sum(-1, dtype=torch.uint8)
+
+
+class QuantisedLinear(nn.Module):
+    def __init__(
+        self,
+        in_features: int,
+        out_features: int,
+        weight_data: Tensor,
+        scale: Tensor,
+        lut: Tensor,
+        kernel: Literal["triton", "torch.compile", "marlin", "marlin-lut"],
+    ):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight_data = nn.Parameter(weight_data, requires_grad=False)
+        self.scale = nn.Parameter(scale, requires_grad=False)
+        self.lut = nn.Buffer(lut)
+        self.kernel = kernel
+        self._tiled: Tensor | None = None  # derived from the three tensors above, never saved
+        self._tiled_key: tuple | None = None
+
+    @property
+    def bits(self) -> int:
+        return kernels.bits_of_lut(self.lut)
+
+    @property
+    def block_size(self) -> int:
+        return self.in_features // self.scale.shape[1]
+
+    def tiled(self) -> Tensor:
+        """The kernels' tiled copy of (weight_data, scale); rebuilt when they change or move."""
+        key = (
+            self.weight_data.data_ptr(), self.scale.data_ptr(),
+            self.weight_data._version, self.scale._version, str(self.weight_data.device),
+        )
+        if self._tiled is None or self._tiled_key != key:
+            self._tiled = native.repack(
+                self.weight_data.data, self.scale.data, self.out_features, self.in_features,
+                self.bits, self.block_size,
+            )
+            self._tiled_key = key
+        return self._tiled
+
+    def forward(self, x: Tensor) -> Tensor:
+        if x.ndim > 2:
+            return self.forward(x.flatten(end_dim=-2)).unflatten(0, x.shape[:-1])
+        if self.kernel == "torch.compile":
+            return kernels.mm_lut_ref(x, self.weight_data, self.lut, self.scale)
+        assert self.kernel in ("triton", "marlin", "marlin-lut")
+        out = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=x.dtype)
+        assert x.dtype == self.lut.dtype == self.scale.dtype
+        native.linear_lut(
+            x.contiguous(), self.tiled(), self.lut, out, self.out_features, self.in_features, self.bits
+        )
+        return out
+
+    @classmethod
+    def create(cls, weight: Tensor, c: QuantisationConfig, lut: Tensor | None = None) -> "QuantisedLinear":
+        device = weight.device
+        n_codes = 2**c.bits
+        if lut is not None:
+            assert lut.ndim == 1 and lut.shape[0] <= n_codes, f"lut must have at most {n_codes} entries, got {lut.shape[0]}"
+            lut = nn.functional.pad(lut, (0, n_codes - lut.shape[0]), value=lut[-1])
+        else:
+            lut = torch.linspace(-1, 1, steps=n_codes, device=device, dtype=weight.dtype)  # uniform [-1, 1]
+
+        # one scale per block_size run of the input dimension
+        blocks = weight.unflatten(-1, (-1, c.block_size))
+        scale = blocks.abs().mean(dim=-1) if c.bits <= 2 else blocks.abs().amax(dim=-1)
+        scale.clamp_min_(1e-12)
+        scaled = (blocks / scale[..., None]).flatten(-2)
+
+        # nearest codebook entry = bucket between codebook midpoints
+        indices = torch.bucketize(scaled, (lut[1:] + lut[:-1]) / 2).clamp_(0, n_codes - 1)
+        weight_data = _pack_codes(indices, c.bits)
+        if 8 % c.bits == 0:
+            table = torch.cartesian_prod(*([lut] * (8 // c.bits))).view(256, -1)
+        else:
+            table = lut.reshape(n_codes, 1)
+        return cls(*weight.T.shape, weight_data, scale, table, kernel=c.kernel)
+
+    @classmethod
+    def create_marlin(cls, weight: Tensor, c: QuantisationConfig) -> "QuantisedLinear":
+        """The reference's Marlin selectors as numbers (models.py:107-125, marlin/__init__.py:152-189):
+        fp16, 4 bits, scale = absmax / 7, code = round(w / scale) + 8 clamped to [0, 15],
+        value = code - 8."""
+        assert c.bits == 4, "Marlin backend only supports 4-bit quantisation"
+        assert c.block_size in (64, 128), "Marlin backend requires block_size 64 or 128"
+        assert weight.dtype == torch.half, "Marlin backend requires float16 weights"
+        blocks = weight.unflatten(-1, (-1, c.block_size))
+        scale = blocks.abs().amax(dim=-1) / 7
+        scale.clamp_min_(1e-12)
+        codes = torch.round(blocks / scale[..., None]).add_(8).clamp_(0, 15).flatten(-2)
+        values = torch.arange(-8, 8, dtype=torch.half, device=weight.device)
+        table = torch.cartesian_prod(values, values).view(256, -1)
+        return cls(*weight.T.shape, _pack_codes(codes, 4), scale, table, kernel=c.kernel)
+
+
+def quantise(
+    source: nn.Module,
+    config: QuantisationConfig | None,
+    device: torch.device,
+    dtype: torch.dtype,
+    key: tuple[str, ...] = (),
+    lut: Tensor | None = None,
+) -> nn.Module:
+    """Quantise all nn.Linear layers in a module according to config, returning a new
+    quantised module.  The original module is left untouched; parameter sharing is lost.
+    As in the reference, `lut` applies to `source` itself only, not to its children."""
+    should_quantise = (
+        isinstance(source, nn.Linear)
+        and config is not None
+        and (config.skip is None or not re.search(config.skip, ".".join(key)))
+    )
+    if should_quantise:
+        assert type(source) == nn.Linear, f"nn.Linear subclasses are not supported: {type(source)}"
+        assert source.bias is None, "Bias is unsupported"
+        assert source.in_features % 64 == 0, f"in_features must be multiple of 64, got {source.in_features}"
+        weight = source.weight.data.to(device, dtype)
+        if config.kernel.startswith("marlin"):
+            module: nn.Module = QuantisedLinear.create_marlin(weight, config)
+        else:
+            module = QuantisedLinear.create(weight, config, lut=lut)
+    else:
+        # shallow copy of the module object, fresh containers, own tensors moved
+        module = copy.copy(source)
+        module._modules = {}
+        module._parameters = {}
+        module._buffers = {}
+        for name, p in source._parameters.items():
+            module._parameters[name] = (
+                None if p is None else nn.Parameter(p.to(device=device, dtype=dtype), requires_grad=p.requires_grad)
+            )
+        for name, b in source._buffers.items():
+            module._buffers[name] = None if b is None else b.to(device=device, dtype=dtype)
+
+    for name, m in source._modules.items():
+        module._modules[name] = None if m is None else quantise(m, config, device, dtype, key + (name,))
+    return module
+
+
+# Benchmarking helpers
+
+
+def count_ops(model: nn.Module) -> int:
+    """Approximate ops per token, respecting quantised layers (ignoring attention)."""
+    ops = 0
+    for module in model.modules():
+        if isinstance(module, QuantisedLinear):
+            ops += 2 * module.in_features * module.out_features
+        else:
+            ops += sum(2 * p.numel() for p in module.parameters(recurse=False))
+    return ops
+
+
+def count_parameter_read_bytes(model: nn.Module) -> int:
+    """Approximate bytes read per token: every parameter except embeddings; the lookup
+    table is a buffer and is not counted."""
+    bytes_r = 0
+    for module in model.modules():
+        if isinstance(module, nn.Embedding):
+            continue
+        bytes_r += sum(p.numel() * p.element_size() for p in module.parameters(recurse=False))
+    return bytes_r
+
+
+@dataclass
+class Result:
+    batch_size: int
+    bytes_rw: int
+    ops: int
+    avg_time: float
+    avg_time_stderr: float
+    output: list[str]
+
+    def __str__(self) -> str:
+        bandwidth = self.bytes_rw / self.avg_time / 1e9
+        ops_per_s = self.ops / self.avg_time / 1e12
+        return "  ".join(
+            [
+                f"{self.batch_size / self.avg_time:>6.1f} tokens/s",
+                f"{bandwidth:>6.1f} GB/s",
+                f"{ops_per_s:>6.1f} TFLOPS",
+            ]
+        )
+
+
+# Custom model configs (the reference's own shapes, models.py:345-379, plus the
+# shapes the B200 measurements are quoted on)
+
+custom_llama_configs = {
+    "4B": dict(dim=3072, n_layers=24, n_heads=24, n_kv_heads=8, ffn_dim_multiplier=1.3, multiple_of=1024, rope_theta=500000),
+    "12B": dict(dim=4096, n_layers=48, n_heads=32, n_kv_heads=8, ffn_dim_multiplier=1.3, multiple_of=1024, rope_theta=500000),
+    "31B": dict(dim=6144, n_layers=60, n_heads=48, n_kv_heads=8, ffn_dim_multiplier=1.3, multiple_of=1024, rope_theta=500000),
+}
+
+# explicit FFN widths: 32 x 3072 / 8192, 40 x 5120 / 13824, 64 x 6144 / 20480
+b200_llama_configs = {
+    "b200-4B": dict(dim=3072, n_layers=32, n_heads=24, n_kv_heads=8, intermediate_size=8192, rope_theta=500000),
+    "b200-12B": dict(dim=5120, n_layers=40, n_heads=40, n_kv_heads=8, intermediate_size=13824, rope_theta=500000),
+    "b200-31B": dict(dim=6144, n_layers=64, n_heads=48, n_kv_heads=8, intermediate_size=20480, rope_theta=500000),
+}
+
+
+@dataclass
+class LlamaDims:
+    """Plain description of a Llama-style decoder (what get_custom_llama_config resolves to)."""
+
+    name: str
+    hidden_size: int
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    intermediate_size: int
+    vocab_size: int = 128256
+    head_dim: int = 128
+    rope_theta: float = 500000.0
+    rms_norm_eps: float = 1e-6
+    tie_word_embeddings: bool = False
+
+
+def get_custom_llama_dims(key: str) -> LlamaDims:
+    if key in b200_llama_configs:
+        c = b200_llama_configs[key]
+        inter = c["intermediate_size"]
+    else:
+        c = custom_llama_configs[key]
+        multiple_of = c["multiple_of"]
+        inter = multiple_of * ((int(4 * 2 / 3 * c["dim"] * c["ffn_dim_multiplier"]) + multiple_of - 1) // multiple_of)
+    return LlamaDims(
+        name=f"custom-llama-{key}",
+        hidden_size=c["dim"],
+        num_hidden_layers=c["n_layers"],
+        num_attention_heads=c["n_heads"],
+        num_key_value_heads=c["n_kv_heads"],
+        intermediate_size=inter,
+        rope_theta=c["rope_theta"],
+    )
+
+
+def get_custom_llama_config(key: str):
+    """transformers LlamaConfig for a custom-llama size (needs `transformers`)."""
+    import transformers
+
+    d = get_custom_llama_dims(key)
+    return transformers.models.llama.modeling_llama.LlamaConfig(
+        _name_or_path=d.name,
+        vocab_size=d.vocab_size,
+        hidden_size=d.hidden_size,
+        num_hidden_layers=d.num_hidden_layers,
+        num_attention_heads=d.num_attention_heads,
+        num_key_value_heads=d.num_key_value_heads,
+        intermediate_size=d.intermediate_size,
+        rope_theta=d.rope_theta,
+        dtype=torch.bfloat16,
+        tie_word_embeddings=d.tie_word_embeddings,
+    )
+
+
+def _quantisation_configs(
+    bits: list[int], block_sizes: list[int], kernels_: list[str], skip: str
+) -> Iterable[QuantisationConfig | None]:
+    if 16 in bits:
+        yield None  # 16-bit (no quantisation)
+    for b in bits:
+        if b < 16:
+            for block_size in block_sizes:
+                for kernel in kernels_:
+                    if not (kernel.startswith("marlin") and b != 4):
+                        yield QuantisationConfig(bits=b, block_size=block_size, kernel=kernel, skip=skip)

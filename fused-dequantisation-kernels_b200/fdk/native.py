@@ -1,0 +1,186 @@
+"""ctypes binding of libfdk_b200.so: the only way the package reaches the GPU kernels.
+
+There is no fallback: if the library is missing or a call returns a non-zero
+status, an exception is raised (the reference turns its native error codes into
+exceptions in the same way, src/fdk/marlin/marlin_cuda.cpp:63-66,84-93).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+from torch import Tensor
+
+_LIB_PATH = Path(__file__).resolve().parent / "libfdk_b200.so"
+
+OK = 0
+DTYPE_BF16 = 0
+DTYPE_F16 = 1
+FLAG_PDL = 1
+
+
+class FdkError(RuntimeError):
+    def __init__(self, status: int, text: str, detail: str):
+        super().__init__(f"libfdk_b200: {text} (status {status}): {detail}")
+        self.status = status
+
+
+_lib: ctypes.CDLL | None = None
+
+_SIGNATURES = {
+    "fdk_version": (ctypes.c_int, []),
+    "fdk_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "fdk_last_error_detail": (ctypes.c_char_p, []),
+    "fdk_tiled_size": (ctypes.c_int, [ctypes.c_int] * 3 + [ctypes.POINTER(ctypes.c_size_t)]),
+    "fdk_repack": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 2),
+    "fdk_unpack": (ctypes.c_int, [ctypes.c_void_p] + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 3),
+    "fdk_dequantise": (ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5 + [ctypes.c_void_p] * 2),
+    "fdk_dequantise_tiled": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 2),
+    "fdk_workspace_size": (ctypes.c_int, [ctypes.POINTER(ctypes.c_size_t)]),
+    "fdk_workspace_init": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "fdk_linear_lut": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p],
+    ),
+}
+
+
+def library_path() -> Path:
+    return Path(os.environ.get("FDK_B200_LIBRARY", _LIB_PATH))
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the shared library once.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not path.exists():
+            raise FdkError(
+                -1,
+                "native library not built",
+                f"{path} is missing; run `python fused-dequantisation-kernels_b200/build.py` "
+                "(there is no CPU or PyTorch fallback for the kernels)",
+            )
+        handle = ctypes.CDLL(str(path))
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is None:
+                continue  # optional entry points are bound where they are used
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        handle = lib()
+        raise FdkError(
+            status,
+            handle.fdk_status_string(status).decode(),
+            handle.fdk_last_error_detail().decode(),
+        )
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return DTYPE_BF16
+    if dtype == torch.float16:
+        return DTYPE_F16
+    raise TypeError(f"fdk kernels take bfloat16 or float16, got {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise FdkError(-2, "tensor not on a CUDA device", "the fdk kernels have no CPU path")
+
+
+def tiled_size(n: int, k: int, bits: int) -> int:
+    out = ctypes.c_size_t(0)
+    check(lib().fdk_tiled_size(n, k, bits, ctypes.byref(out)))
+    return out.value
+
+
+def repack(codes: Tensor, scale: Tensor, n: int, k: int, bits: int, block_size: int) -> Tensor:
+    """Packed codes + scales (reference layout) -> tiled uint8 buffer on the same device."""
+    _require_cuda(codes, scale)
+    assert codes.dtype == torch.uint8 and codes.is_contiguous() and scale.is_contiguous()
+    tiled = torch.empty(tiled_size(n, k, bits), dtype=torch.uint8, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(lib().fdk_repack(codes.data_ptr(), scale.data_ptr(), n, k, bits, block_size, tiled.data_ptr(), _stream()))
+    return tiled
+
+
+def unpack(tiled: Tensor, n: int, k: int, bits: int, block_size: int, dtype: torch.dtype) -> tuple[Tensor, Tensor]:
+    _require_cuda(tiled)
+    codes = torch.empty((n, k * bits // 8), dtype=torch.uint8, device=tiled.device)
+    scale = torch.empty((n, k // block_size), dtype=dtype, device=tiled.device)
+    with torch.cuda.device(tiled.device):
+        check(lib().fdk_unpack(tiled.data_ptr(), n, k, bits, block_size, codes.data_ptr(), scale.data_ptr(), _stream()))
+    return codes, scale
+
+
+def dequantise(codes: Tensor, lut: Tensor, scale: Tensor, bits: int) -> Tensor:
+    _require_cuda(codes, lut, scale)
+    n = codes.shape[0]
+    k = codes.shape[1] * 8 // bits
+    block_size = k // scale.shape[1]
+    assert lut.dtype == scale.dtype and all(t.is_contiguous() for t in (codes, lut, scale))
+    w = torch.empty((n, k), dtype=scale.dtype, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(
+            lib().fdk_dequantise(
+                codes.data_ptr(), lut.data_ptr(), scale.data_ptr(), n, k, bits, block_size,
+                dtype_code(scale.dtype), w.data_ptr(), _stream(),
+            )
+        )
+    return w
+
+
+def dequantise_tiled(tiled: Tensor, lut: Tensor, n: int, k: int, bits: int) -> Tensor:
+    _require_cuda(tiled, lut)
+    w = torch.empty((n, k), dtype=lut.dtype, device=tiled.device)
+    with torch.cuda.device(tiled.device):
+        check(lib().fdk_dequantise_tiled(tiled.data_ptr(), lut.data_ptr(), n, k, bits, dtype_code(lut.dtype), w.data_ptr(), _stream()))
+    return w
+
+
+_workspaces: dict[tuple[int, int], Tensor] = {}
+
+
+def workspace(device: torch.device) -> Tensor:
+    """One zero-initialised scratch buffer per (device, stream).  Allocated on first use,
+    so the first call on a stream must happen before that stream is captured in a graph."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, _stream())
+    ws = _workspaces.get(key)
+    if ws is None:
+        with torch.cuda.device(index):
+            size = ctypes.c_size_t(0)
+            check(lib().fdk_workspace_size(ctypes.byref(size)))
+            ws = torch.empty(size.value, dtype=torch.uint8, device=f"cuda:{index}")
+            check(lib().fdk_workspace_init(ws.data_ptr(), size.value, _stream()))
+        _workspaces[key] = ws
+    return ws
+
+
+def linear_lut(x: Tensor, tiled: Tensor, lut: Tensor, out: Tensor, n: int, k: int, bits: int, pdl: bool = False) -> None:
+    """out[m, n] = x[m, k] @ W.T, W never materialised.  Writes `out` in place."""
+    _require_cuda(x, tiled, lut, out)
+    m = x.shape[0]
+    ws = workspace(x.device)
+    with torch.cuda.device(x.device):
+        check(
+            lib().fdk_linear_lut(
+                x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), out.data_ptr(), m, n, k, bits,
+                dtype_code(x.dtype), ws.data_ptr(), ws.numel(), FLAG_PDL if pdl else 0, _stream(),
+            )
+        )

@@ -1,0 +1,125 @@
+/* libfdk_b200 -- C ABI of the B200 (sm_100a) fused-dequantisation kernels.
+ *
+ * Drop-in boundary for the LUT hot path of graphcore-research/
+ * fused-dequantisation-kernels ("fdk").  The reference reaches its kernels
+ * through Python operator functions that take torch tensors, write into a
+ * caller-allocated `out` and launch on the current CUDA stream
+ * (src/fdk/kernels.py:158-182 run_mv_lut, :460-489 run_mm_lut); its one native
+ * extension shows the C convention it uses for compiled code:
+ * `int marlin_cuda(const void* A, const void* B, void* C, void* s, ...,
+ * cudaStream_t stream, ...)` returning 0 or a small error code that the
+ * binding turns into an exception (src/fdk/marlin/marlin_cuda.cpp:25-45,
+ * 63-66, 84-93).  This header follows that convention: plain pointers and
+ * sizes, an explicit stream, an int status, no torch types.
+ *
+ * Every pointer is a DEVICE pointer unless the parameter name ends in
+ * `_host`.  `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ * stream).  All calls are asynchronous on `stream`, never synchronise, and,
+ * except where a comment says otherwise, allocate nothing, so they can be
+ * captured in a CUDA graph as the reference's timing harness does
+ * (src/fdk/bench.py:67-99, src/fdk/models.py:329-331).
+ *
+ * 16-bit floating-point data is bfloat16 (FDK_DTYPE_BF16) or IEEE half
+ * (FDK_DTYPE_F16); the reference uses bf16 for its LUT kernels and fp16 for
+ * its Marlin selectors (src/fdk/models.py:486-491).
+ */
+#ifndef FDK_B200_H_
+#define FDK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (0 = success, like marlin_cuda's return value) ---------- */
+#define FDK_OK 0
+#define FDK_ERR_BAD_ARG 1   /* null pointer, non-positive size, unknown dtype/flag      */
+#define FDK_ERR_SHAPE 2     /* shape the kernels do not take (cf. ERR_PROB_SHAPE,
+                               src/fdk/marlin/marlin_cuda.cpp:25): bits not in
+                               {1,2,3,4,8}, k or block_size not a multiple of 64 ...   */
+#define FDK_ERR_ALIGN 3     /* pointer not 16-byte aligned where the kernels need it    */
+#define FDK_ERR_ARCH 4      /* current device is not compute capability 10.x            */
+#define FDK_ERR_CUDA 5      /* a CUDA runtime call failed; see fdk_last_error_detail()  */
+#define FDK_ERR_WORKSPACE 6 /* workspace missing or smaller than fdk_workspace_size()   */
+
+#define FDK_DTYPE_BF16 0
+#define FDK_DTYPE_F16 1
+
+/* flags of fdk_linear_lut */
+#define FDK_FLAG_PDL 1u /* launch with programmatic stream serialisation: the kernel's
+                           weight prefetch may overlap the tail of the previous kernel
+                           on the stream; x / out / workspace are only touched after
+                           the previous kernel has completed.                          */
+
+/* Library version: major*10000 + minor*100 + patch. */
+int fdk_version(void);
+
+/* Static text for a status code. */
+const char* fdk_status_string(int status);
+
+/* Detail of the last non-zero status returned on the calling thread
+ * (e.g. which argument, or the CUDA error string).  Never NULL. */
+const char* fdk_last_error_detail(void);
+
+/* Size in bytes of the tiled buffer for an [n, k] matrix of `bits`-bit codes.
+ * Host-only arithmetic.  Replaces nothing in the reference: the tiled layout
+ * is this library's own (the reference's kernels read the packed tensors of
+ * src/fdk/models.py:94-104 directly). */
+int fdk_tiled_size(int n, int k, int bits, size_t* bytes_host);
+
+/* Offline repacker: the reference's packed tensors -> tiled buffer.
+ *   codes  [n, k*bits/8] uint8, element 0 of a byte in the high bits
+ *          (src/fdk/models.py:94-102); for bits == 3, which the reference
+ *          does not have, one MSB-first bit stream per row.
+ *   scale  [n, k/block_size] 16-bit floats (src/fdk/models.py:81-88).
+ * block_size must be a multiple of 64 and divide k; k a multiple of 64.
+ * `tiled` must hold fdk_tiled_size() bytes and be 16-byte aligned.
+ * Stands where QuantisedLinear.create hands its tensors to the module
+ * (src/fdk/models.py:104). */
+int fdk_repack(const void* codes, const void* scale, int n, int k, int bits, int block_size,
+               void* tiled, void* stream);
+
+/* Inverse of fdk_repack (tests, state_dict export).  block_size as above; the
+ * scale written for a block_size > 64 is that of the first 64-run. */
+int fdk_unpack(const void* tiled, int n, int k, int bits, int block_size, void* codes, void* scale,
+               void* stream);
+
+/* Bit-exact dequantisation, W[n,k] = dtype(float(lut[byte][j]) * float(scale[n, k/block_size])),
+ * i.e. the first two lines of mm_lut_ref (src/fdk/kernels.py:23-24).
+ *   lut    [256, 8/bits] byte table (src/fdk/models.py:103); for bits == 3 the
+ *          plain 8-entry codebook.
+ *   w_out  [n, k] 16-bit floats, 16-byte aligned. */
+int fdk_dequantise(const void* codes, const void* lut, const void* scale, int n, int k, int bits,
+                   int block_size, int dtype, void* w_out, void* stream);
+
+/* Same result, read from the tiled buffer. */
+int fdk_dequantise_tiled(const void* tiled, const void* lut, int n, int k, int bits, int dtype,
+                         void* w_out, void* stream);
+
+/* Scratch needed by fdk_linear_lut on the current device (split-K partial sums
+ * and arrival counters).  One workspace per stream that runs the kernels
+ * concurrently.  Compare Marlin's `workspace` (src/fdk/marlin/__init__.py:37-51,
+ * marlin_cuda.cpp:65-66): caller-allocated, zeroed once, left zeroed by every call. */
+int fdk_workspace_size(size_t* bytes_host);
+
+/* Zeroes the arrival counters (cudaMemsetAsync).  Call once after allocating. */
+int fdk_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Fused dequantise + matrix product, out[m, n] = x[m, k] . W[n, k]^T with W as
+ * fdk_dequantise defines it but never materialised; fp32 accumulation, block
+ * scale applied to the fp32 block sum.  Replaces run_mv_lut (m == 1,
+ * src/fdk/kernels.py:158-182) and run_mm_lut (m > 1, src/fdk/kernels.py:460-489).
+ *   x    [m, k] row-major, 16-byte aligned rows (k % 8 == 0)
+ *   out  [m, n] row-major
+ *   m    >= 1; rows are processed 16 (bits..) at a time, any m is accepted.
+ * Deterministic: the same inputs give the same bits on every call. */
+int fdk_linear_lut(const void* x, const void* tiled, const void* lut, void* out, int m, int n,
+                   int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
+                   unsigned flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FDK_B200_H_ */

@@ -1,0 +1,179 @@
+"""GPU parity tests: every call goes through the C-ABI library (fdk.native) and is checked
+against the CPU oracle on the same seeded inputs.  Bit-exact for byte / index work
+(repack, unpack, dequantise); rel-RMS error <= 1e-2 (the reference's own tolerance for its
+LUT kernels, src/fdk/kernels.py:196,502) for the fused products -- measured values are
+~1e-3, the bf16 output rounding."""
+
+import numpy as np
+import pytest
+import torch
+
+import fdk_oracle as O
+import tiled_layout as TL
+from gpu_util import from_bits, oracle_dense, random_problem, to_bits
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2
+
+SHAPES = [(64, 64), (16, 256), (100, 384), (256, 1024), (200, 4096), (1024, 768)]
+
+
+@pytest.fixture(scope="module")
+def native():
+    from fdk import native as nat
+
+    nat.lib()
+    return nat
+
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("n,k", SHAPES)
+def test_repack_matches_host_model_and_round_trips(native, bits, n, k):
+    codes, lut, scale, _ = random_problem(n, k, bits, 1, seed=n + k + bits)
+    d_codes = torch.from_numpy(codes).cuda()
+    d_scale = from_bits(scale)
+    tiled = native.repack(d_codes, d_scale, n, k, bits, 64)
+    assert tiled.numel() == TL.tiled_size(n, k, bits)
+    assert np.array_equal(tiled.cpu().numpy(), TL.repack(codes, scale, bits))
+    back_codes, back_scale = native.unpack(tiled, n, k, bits, 64, torch.bfloat16)
+    assert np.array_equal(back_codes.cpu().numpy(), codes)
+    assert np.array_equal(to_bits(back_scale), scale)
+
+
+@pytest.mark.parametrize("block_size", [128, 256])
+def test_repack_wider_blocks(native, block_size):
+    n, k, bits = 96, 512, 4
+    codes, lut, scale, x = random_problem(n, k, bits, 3, seed=9, g=block_size)
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, block_size)
+    assert np.array_equal(tiled.cpu().numpy(), TL.repack(codes, scale, bits))
+    w = native.dequantise_tiled(tiled, from_bits(lut), n, k, bits)
+    assert np.array_equal(to_bits(w), O.dequantise(codes, lut, scale))
+
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("n,k", SHAPES)
+def test_dequantise_bit_exact(native, bits, n, k):
+    codes, lut, scale, _ = random_problem(n, k, bits, 1, seed=3 * n + k + bits)
+    expected = oracle_dense(codes, lut, scale, bits, k)
+    d_codes, d_lut, d_scale = torch.from_numpy(codes).cuda(), from_bits(lut), from_bits(scale)
+    w = native.dequantise(d_codes, d_lut, d_scale, bits)
+    assert np.array_equal(to_bits(w), expected)
+    tiled = native.repack(d_codes, d_scale, n, k, bits, 64)
+    w2 = native.dequantise_tiled(tiled, d_lut, n, k, bits)
+    assert np.array_equal(to_bits(w2), expected)
+
+
+def test_dequantise_bit_exact_fp16_and_small_blocks(native):
+    n, k, bits = 64, 256, 4
+    rng = np.random.default_rng(5)
+    codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    base = O.f32_to_f16(np.arange(-8, 8, dtype=np.float32))
+    lut = np.stack([base[np.arange(256) >> 4], base[np.arange(256) & 15]], axis=1)
+    scale = O.f32_to_f16(rng.random((n, k // 32), dtype=np.float32))
+    w = native.dequantise(torch.from_numpy(codes).cuda(), from_bits(lut, torch.float16), from_bits(scale, torch.float16), bits)
+    assert np.array_equal(to_bits(w), O.dequantise(codes, lut, scale, dtype="f16"))
+
+
+@pytest.mark.parametrize("name,bit_list", [("quantise_linspace.npz", [8, 4, 2, 1]), ("quantise_codebook.npz", [4, 2])])
+def test_dequantise_golden_vectors(native, golden_dir, name, bit_list):
+    z = np.load(golden_dir / name)
+    for bits in bit_list:
+        p = f"b{bits}_"
+        w = native.dequantise(torch.from_numpy(z[p + "weight_data"]).cuda(), from_bits(z[p + "lut"]), from_bits(z[p + "scale"]), bits)
+        assert np.array_equal(to_bits(w), z[p + "w_deq"]), f"bits={bits}"
+
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16, 17, 40])
+@pytest.mark.parametrize("n,k", [(64, 64), (100, 384), (256, 1024), (1024, 768)])
+def test_linear_lut_matches_oracle(native, bits, m, n, k):
+    codes, lut, scale, x = random_problem(n, k, bits, m, seed=m + n + k + bits)
+    expected = O.mm_dense(x, oracle_dense(codes, lut, scale, bits, k))
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    native.linear_lut(from_bits(x), tiled, from_bits(lut), out, n, k, bits)
+    err = O.rmsen(O.bf16_to_f32(expected), O.bf16_to_f32(to_bits(out)))
+    assert err < TOL, f"rmsen={err}"
+    assert err < 3e-3  # what fp32 accumulation + one bf16 rounding should give
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (3072, 8192), (8192, 3072), (13824, 5120)])
+def test_linear_lut_large_shapes(native, bits, n, k):
+    m = 3
+    codes, lut, scale, x = random_problem(n, k, bits, m, seed=n + bits)
+    expected = O.mm_dense(x, oracle_dense(codes, lut, scale, bits, k))
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    native.linear_lut(from_bits(x), tiled, from_bits(lut), out, n, k, bits)
+    err = O.rmsen(O.bf16_to_f32(expected), O.bf16_to_f32(to_bits(out)))
+    assert err < 3e-3, f"rmsen={err}"
+
+
+def test_linear_lut_is_deterministic_and_leaves_workspace_clean(native):
+    n, k, bits, m = 4096, 4096, 4, 4
+    codes, lut, scale, x = random_problem(n, k, bits, m, seed=1)
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
+    d_x, d_lut = from_bits(x), from_bits(lut)
+    outs = []
+    for _ in range(5):
+        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        native.linear_lut(d_x, tiled, d_lut, out, n, k, bits)
+        outs.append(to_bits(out))
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    ws = native.workspace(torch.device("cuda", torch.cuda.current_device()))
+    torch.cuda.synchronize()
+    assert int(ws[:16384].view(torch.int32).abs().sum()) == 0  # arrival counters back to zero
+
+
+def test_linear_lut_fp16(native):
+    n, k, bits, m = 256, 512, 4, 3
+    rng = np.random.default_rng(11)
+    codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    base = O.f32_to_f16(np.arange(-8, 8, dtype=np.float32))
+    lut = np.stack([base[np.arange(256) >> 4], base[np.arange(256) & 15]], axis=1)
+    scale = O.f32_to_f16(rng.random((n, k // 64), dtype=np.float32) * np.float32(0.01))
+    x = O.f32_to_f16(rng.standard_normal((m, k)).astype(np.float32))
+    expected = O.mm_dense(x, O.dequantise(codes, lut, scale, dtype="f16"), dtype="f16")
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale, torch.float16), n, k, bits, 64)
+    out = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    native.linear_lut(from_bits(x, torch.float16), tiled, from_bits(lut, torch.float16), out, n, k, bits)
+    assert O.rmsen(O.f16_to_f32(expected), O.f16_to_f32(to_bits(out))) < 2e-3
+
+
+def test_linear_lut_cuda_graph_capture(native):
+    n, k, bits, m = 1024, 1024, 4, 1
+    codes, lut, scale, x = random_problem(n, k, bits, m, seed=2)
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
+    d_x, d_lut = from_bits(x), from_bits(lut)
+    out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        native.linear_lut(d_x, tiled, d_lut, out, n, k, bits)  # allocates this stream's workspace
+        torch.cuda.synchronize()
+        eager = to_bits(out).copy()
+        out.zero_()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(3):
+                native.linear_lut(d_x, tiled, d_lut, out, n, k, bits)
+        graph.replay()
+        torch.cuda.synchronize()
+    assert np.array_equal(to_bits(out), eager)
+
+
+def test_error_statuses_on_device(native):
+    x = torch.zeros((1, 128), dtype=torch.bfloat16, device="cuda")
+    tiled = torch.zeros(native.tiled_size(64, 128, 4), dtype=torch.uint8, device="cuda")
+    lut = torch.zeros((256, 2), dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros((1, 64), dtype=torch.bfloat16, device="cuda")
+    lib = native.lib()
+    ws = native.workspace(x.device)
+    args = lambda xp, wsp, wsn: lib.fdk_linear_lut(xp, tiled.data_ptr(), lut.data_ptr(), out.data_ptr(), 1, 64, 128, 4, 0, wsp, wsn, 0, None)
+    assert args(x.data_ptr() + 2, ws.data_ptr(), ws.numel()) == 3  # misaligned x
+    assert args(x.data_ptr(), ws.data_ptr(), 100) == 6  # workspace too small
+    assert args(x.data_ptr(), None, 0) == 6
+    assert args(x.data_ptr(), ws.data_ptr(), ws.numel()) == 0
+    torch.cuda.synchronize()
