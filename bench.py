@@ -1,0 +1,377 @@
+"""Headline benchmark: packed-weight HBM GB/s of the fused 4-bit LUT GEMV.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): y = x . W^T with K = N = 8192, batch 1, 4-bit codes, block 64, a
+16-entry k-means-like codebook -- the largest shape of the reference's kernel sweep
+(`python -m fdk.bench -k 8192 -b 4 -m 1`, README of the reference).  One STEP is one pass
+over `copies` independent weight sets (8 x 35.7 MB, more than the 126 MB L2, so every
+pass streams from HBM), captured once as a CUDA graph the way the reference's harness
+does (src/fdk/bench.py:67-99) and replayed per step.
+
+Printed JSON line: `value` = packed-weight bytes (codes + block scales) of all GPUs per
+second, device-timed with inputs resident in HBM; `e2e` = the same bytes per second
+through the public module call with host buffers (pinned x copied in, y copied out, per
+GEMV); `roofline` relates the per-launch time to the measured HBM copy bandwidth;
+`cpu_baseline` times the CPU oracle port of the reference operator on the host cores.
+
+N > 1: the kernel benchmark does not shard (one matrix, one GPU); ranks run independent
+replicas (weak scaling), timed as the max over ranks.
+
+`--impl reference` times the reference's CPU path (eager torch dequantise-then-matmul,
+the oracle port) on the same workload, one GEMV per step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "fused-dequantisation-kernels_b200"))
+
+K = N = 8192
+BITS = 4
+BLOCK = 64
+BATCH = 1
+COPIES = 8
+WORKLOAD = f"gemv_lut k={K} n={N} m={BATCH} bits={BITS} g={BLOCK} codebook=kmeans16 copies={COPIES}"
+PACKED_BYTES = N * K * BITS // 8 + N * (K // BLOCK) * 2  # codes + bf16 block scales
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------
+# synthetic inputs (seeded; same recipe for every arm)
+# ---------------------------------------------------------------------------------------
+
+
+def kmeans_codebook(bits: int, seed: int):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(20000, generator=g).sort().values
+    c = torch.quantile(x, (torch.arange(2**bits) + 0.5) / 2**bits)
+    for _ in range(8):
+        idx = torch.bucketize(x, (c[1:] + c[:-1]) / 2)
+        c = torch.stack([x[idx == i].mean() if (idx == i).any() else c[i] for i in range(2**bits)])
+    return c.sort().values.bfloat16()
+
+
+def make_weight(seed: int, device):
+    """bf16 W ~ N(0, 1/K), drawn on `device`."""
+    import torch
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn((N, K), generator=g, device=device, dtype=torch.float32) * K**-0.5).bfloat16()
+
+
+# ---------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------
+
+
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs (reading only)."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                sm_max.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference operator, timed on the host cores
+# ---------------------------------------------------------------------------------------
+
+
+def cpu_reference_times(reps: int, warmup: int) -> tuple[list[float], int, str]:
+    """Seconds per GEMV of the eager-torch reference operator on the host (all cores)."""
+    import torch
+
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import fdk_oracle_torch as OT
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cpu = torch.device("cpu")
+    w = make_weight(100, cpu)
+    data, scale, table = OT.quantise_weight(w, BITS, BLOCK, lut=kmeans_codebook(BITS, 0))
+    del w
+    x = torch.randn((BATCH, K), generator=torch.Generator().manual_seed(1)).bfloat16()
+    times = []
+    for i in range(warmup + reps):
+        t0 = time.perf_counter()
+        OT.mm_lut_ref(x, data, table, scale)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    return times, torch.get_num_threads(), f"{reps} GEMVs of the workload's shape, one weight set (eager torch dequantise-then-matmul, bf16)"
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times, cores, sample = cpu_reference_times(args.steps, args.warmup)
+    mean = statistics.fmean(times)
+    value = PACKED_BYTES / mean / 1e9
+    line = {
+        "impl": "reference",
+        "metric": "packed_weight_gbs_gemv",
+        "value": value,
+        "unit": "GB/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": mean * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "step": "one GEMV on the host CPU (bounded sample of the GPU arm's step)"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------
+
+
+def run_gpu_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from fdk import models, native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the fdk kernels have no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    native.lib()
+
+    # `copies` quantised layers through the public API (quantise -> QuantisedLinear)
+    config = models.QuantisationConfig(bits=BITS, block_size=BLOCK)
+    codebook = kmeans_codebook(BITS, 0).to(device)
+    layers = []
+    for c in range(COPIES):
+        w = make_weight(100 + c, device)
+        layer = models.QuantisedLinear.create(w, config, lut=codebook)
+        layer.tiled()
+        layers.append(layer)
+        del w
+    gx = torch.Generator(device=device).manual_seed(1)
+    xs = [torch.randn((BATCH, K), generator=gx, device=device).bfloat16() for _ in range(COPIES)]
+    outs = [torch.empty((BATCH, N), device=device, dtype=torch.bfloat16) for _ in range(COPIES)]
+
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        def one_pass():
+            for layer, x, out in zip(layers, xs, outs):
+                native.linear_lut(x, layer.tiled(), layer.lut, out, N, K, BITS)
+
+        one_pass()  # allocates this stream's workspace before capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        torch.cuda.synchronize()
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            barrier()
+            start.record()
+            for _ in range(args.steps):
+                graph.replay()
+            end.record()
+            barrier()
+        elapsed_ms = start.elapsed_time(end)
+
+        # end to end through the module call with host buffers, per GEMV: pinned x -> device,
+        # forward, y -> host (the device->host copy synchronises).
+        e2e_steps = max(1, min(args.steps, 20))
+        e2e_s = float("nan")
+        if not args.kernel_only:
+            x_host = [x.cpu().pin_memory() for x in xs]
+            y_host = torch.empty((BATCH, N), dtype=torch.bfloat16).pin_memory()
+            for layer, xh in zip(layers, x_host):  # warm-up
+                y_host.copy_(layer(xh.to(device, non_blocking=True)))
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                for layer, xh in zip(layers, x_host):
+                    y_host.copy_(layer(xh.to(device, non_blocking=True)))
+            torch.cuda.synchronize()
+            e2e_s = time.perf_counter() - t0
+
+    t = torch.tensor([elapsed_ms, e2e_s], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_s = float(t[0]), float(t[1])
+
+    launches = COPIES * args.steps
+    ms_per_step = elapsed_ms / args.steps
+    value = world * COPIES * PACKED_BYTES / (ms_per_step * 1e-3) / 1e9
+    e2e_value = world * COPIES * e2e_steps * PACKED_BYTES / e2e_s / 1e9
+    per_launch_s = elapsed_ms * 1e-3 / launches
+    achieved = PACKED_BYTES / per_launch_s / 1e9
+    peak, peak_kind = measured_peak_gbs()
+
+    if rank == 0:
+        cpu_baseline = None
+        if world == 1 and not args.kernel_only:  # the CPU arm is reported beside the single-GPU number only
+            cpu_times, cores, sample = cpu_reference_times(reps=20, warmup=2)
+            cpu_value = PACKED_BYTES / statistics.fmean(cpu_times) / 1e9
+            cpu_baseline = {"value": cpu_value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+        traffic = None
+        traffic_file = ROOT / "profiles" / "gemv_lut_4bit_8192_traffic.json"
+        if traffic_file.exists():
+            try:
+                traffic = json.loads(traffic_file.read_text())["dram_bytes_per_launch"]
+            except Exception:
+                traffic = None
+        line = {
+            "metric": "packed_weight_gbs_gemv",
+            "value": value,
+            "unit": "GB/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD,
+                "step": f"{COPIES} GEMV launches, one per weight set, one CUDA graph",
+                "cache": f"inputs larger than L2: {COPIES} x {PACKED_BYTES} B of weights cycled",
+                "parallelism": "replicas" if world > 1 else "single",
+            },
+            "roofline": {
+                "bound": "hbm",
+                "achieved": achieved,
+                "peak": peak,
+                "unit": "GB/s",
+                "frac": achieved / peak,
+                "traffic": traffic,
+                "peak_kind": f"of {peak_kind}",
+                "kernel": "linear_lut_kernel<4,1,bf16>",
+                "us_per_launch": per_launch_s * 1e6,
+            },
+            "cpu_baseline": cpu_baseline,
+            "e2e": {
+                "value": e2e_value,
+                "unit": "GB/s",
+                "h2d_bytes_per_step": COPIES * BATCH * K * 2,
+                "d2h_bytes_per_step": COPIES * BATCH * N * 2,
+            },
+            "gpu_launches": launches,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    global COPIES, WORKLOAD
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    # profiling aids (the defaults are the benchmark): smaller footprint, kernel launches only
+    ap.add_argument("--copies", type=int, default=COPIES, help="weight sets cycled per step")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs")
+    args = ap.parse_args()
+    if args.copies != COPIES:
+        COPIES = args.copies
+        WORKLOAD = f"gemv_lut k={K} n={N} m={BATCH} bits={BITS} g={BLOCK} codebook=kmeans16 copies={COPIES}"
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -95,7 +95,7 @@ def test_linear_lut_matches_oracle(native, bits, m, n, k):
     native.linear_lut(from_bits(x), tiled, from_bits(lut), out, n, k, bits)
     err = O.rmsen(O.bf16_to_f32(expected), O.bf16_to_f32(to_bits(out)))
     assert err < TOL, f"rmsen={err}"
-    assert err < 3e-3  # what fp32 accumulation + one bf16 rounding should give
+    assert err < 4e-3  # fp32 accumulation + one bf16 output rounding (2^-9 / sqrt(3) .. 2^-8 / sqrt(3))
 
 
 @pytest.mark.parametrize("bits", [1, 2, 4])
