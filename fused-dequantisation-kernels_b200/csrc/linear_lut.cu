@@ -1,13 +1,15 @@
 // Fused dequantise + GEMV / skinny GEMM for sm_100a:  out[m, n] = x[m, k] . W[n, k]^T,
 // W given as tiled low-bit codes + block scales + a lookup table (fdk_layout.cuh).
 //
-// Shape of the kernel (one persistent CTA per SM, 16 warps):
-//   * The weight stream is cut into slabs (64 rows x 64*KSB columns, ~2-6 KB).  The
+// Shape of the kernel (one persistent CTA per SM, up to 24 warps):
+//   * The weight stream is cut into slabs (64 rows x 64*KSB columns, 2-6 KB).  The
 //     slabs of the whole matrix form one linear sequence (row tile major); CTA c owns
 //     a contiguous range of it ("stream-K"), its warps take slabs round-robin.  Every
 //     SM therefore streams the same number of bytes (+-1 slab) whatever N and K are.
-//   * A warp keeps kDepth slabs in flight as 16-byte-per-lane global loads straight
-//     into registers (512 contiguous bytes per load instruction, no L1 allocation).
+//   * Every warp owns a small ring of slab-sized stages in shared memory.  Lane 0
+//     fills them with one bulk asynchronous copy per slab (cp.async.bulk, completion
+//     on an mbarrier), so the data in flight costs no registers and the loads need
+//     no issue slots.  All waits on those barriers are bounded.
 //   * Codes are turned into tensor-core A fragments by table lookup in shared memory:
 //     one code byte indexes a per-lane replica of the byte table, so a lookup is one
 //     PRMT (byte -> address) and one conflict-free LDS that returns 2 (4-bit), 4
@@ -18,12 +20,16 @@
 //     The tensor pipe is used because the FMA work would otherwise compete with the
 //     lookups for issue slots; at m <= 16 it is far from being the limiter, so the
 //     synchronous MMA form is enough and keeps the weights in registers (a tcgen05
-//     MMA would need them written back to shared or tensor memory first).
+//     MMA would need them written back to shared or tensor memory first).  What
+//     bounds the kernel besides HBM is the shared-memory pipe: one 128-byte wavefront
+//     per 32 code bytes looked up, plus the wavefronts that bring the codes in.
 //   * At a row-tile boundary the warps of a CTA reduce through shared memory in a
 //     fixed order.  A CTA that owns only part of a row tile's K range writes its
 //     partial sums to the workspace and bumps an arrival counter; the last arriver
 //     adds the partials in CTA order and writes the result.  No spinning, and the
 //     summation order never depends on timing, so results are reproducible.
+#include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 #include "fdk_common.cuh"
@@ -31,40 +37,42 @@
 namespace fdk {
 namespace {
 
-constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
-// Slabs in flight per warp: as many as the register file allows for the slab size.
-template <int BITS, int NB>
-__host__ __device__ constexpr int depth_for() {
-  if (BITS == 4) return NB == 1 ? 3 : 2;
-  if (BITS == 2) return 2;
-  if (BITS == 1) return NB == 1 ? 2 : 1;
-  return 1;
-}
+constexpr int kMaxStages = 4;
+
+constexpr int kStatusWord = 4095;        // counters[kStatusWord] collects device-side error bits
+constexpr int kStatusTimeout = 1;        // a bounded wait on a copy barrier ran out
+constexpr int kStatusSmemLayout = 2;     // shared window base differs from what the host planned for
+constexpr uint32_t kWaitLimit = 1u << 22;  // try_wait rounds before giving up (seconds, not microseconds)
 
 struct LinearParams {
   const uint8_t* tiled;
-  const void* lut;
+  const void* lut;  // byte table in device memory, or null when it travels in the parameters
   const uint16_t* x;
   uint16_t* out;
-  float* partial;  // [grid][2][512 * NB]
-  int* counters;   // [row_tiles], zero between launches
+  uint2* partial;  // [grid][512 * NB] {partial sum, tag} words
+  int* counters;   // [row_tiles] use counts of the split row tiles + status word
   int m, n, k;
   int k_slabs;     // slabs per row tile
   int total;       // row_tiles * k_slabs
   int base, rem;   // CTA c owns `base + (c < rem)` consecutive slabs
+  // shared-memory plan, as addresses in the shared window
+  uint32_t smem_base;     // expected address of the dynamic shared memory
+  uint32_t table_addr;
+  uint32_t slots_addr;
+  uint32_t mbar_addr;
+  uint32_t stage_a_addr;  // first stages live below the table ...
+  uint32_t stage_a_count;
+  uint32_t stage_b_addr;  // ... the others above it
+  uint32_t stage_bytes;   // slab + this launch's x rows, rounded to 128
+  uint32_t stages;        // ring stages per warp
+  uint32_t slot_t;        // fragment column pairs kept per row in the reduction slots: ceil(min(m, 8) / 2)
+#ifdef FDK_TRACE
+  unsigned long long* trace;  // [grid][warps][8] cycle counts (development builds only)
+#endif
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
 }
 
 __device__ __forceinline__ uint4 ldg_l1(const void* p) {
@@ -82,34 +90,70 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b) {
   return d;
 }
 
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+// Table lookups: pure functions of the address once the table is filled (it never
+// changes afterwards), so the compiler may schedule them freely.
+__device__ __forceinline__ uint32_t lut32(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+__device__ __forceinline__ uint2 lut64(uint32_t addr) {
   uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+__device__ __forceinline__ uint4 lut128(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+// Ring reads: ordered after the barrier wait that precedes them.
+__device__ __forceinline__ uint4 ring128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
   return v;
 }
 
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Waits for the phase with the given parity; gives up after kWaitLimit rounds.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
 template <bool FP16>
-__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                         const float (&c)[4]) {
   if constexpr (FP16) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
   } else {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
   }
 }
 
@@ -139,29 +183,42 @@ struct Table {
   static constexpr bool kAligned64K = (BITS != 1);
 };
 
-template <int BITS, bool FP16>
-__device__ void fill_table(uint32_t table_base, const void* lut) {
+// The byte table may travel inside the kernel parameters (no memory latency at all) or be
+// read from device memory.  16-bit entries, packed two per word.
+template <int BITS>
+struct InlineLut {
+  static constexpr int kWords = (BITS == 3) ? 4 : 256 * (8 / BITS) / 2;
+  uint32_t w[kWords];
+};
+
+// Fills the per-lane replicated table.  A plain loop on purpose: code that runs once per
+// launch costs mostly instruction fetches, so it is kept short rather than unrolled.
+// word(i) returns 32-bit word i of the source table.
+template <int BITS, class WordFn>
+__device__ __forceinline__ void fill_table(uint32_t table_base, WordFn word) {
   using T = Table<BITS>;
-  for (int idx = threadIdx.x; idx < T::kEntries * 32; idx += kThreads) {
-    int e = idx >> 5, l = idx & 31;
-    uint32_t addr = table_base + e * T::kStride + l * T::kEntryBytes;
+#pragma unroll 1
+  for (int idx = threadIdx.x; idx < T::kEntries * 32; idx += blockDim.x) {
+    const int e = idx >> 5, l = idx & 31;
+    const uint32_t addr = table_base + e * T::kStride + l * T::kEntryBytes;
     if constexpr (BITS == 4) {
-      uint32_t v = reinterpret_cast<const uint32_t*>(lut)[e];
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v));
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(word(e)) : "memory");
     } else if constexpr (BITS == 2) {
-      uint2 v = reinterpret_cast<const uint2*>(lut)[e];
-      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(v.x), "r"(v.y));
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(word(2 * e)), "r"(word(2 * e + 1)) : "memory");
     } else if constexpr (BITS == 1) {
-      uint4 v = reinterpret_cast<const uint4*>(lut)[e];
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w));
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(word(4 * e)), "r"(word(4 * e + 1)),
+                   "r"(word(4 * e + 2)), "r"(word(4 * e + 3))
+                   : "memory");
     } else if constexpr (BITS == 8) {
-      uint32_t v = reinterpret_cast<const uint16_t*>(lut)[e];
-      v |= v << 16;
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v));
+      const uint32_t pair = word(e >> 1);
+      const uint32_t h = (e & 1) ? (pair >> 16) : (pair & 0xFFFFu);
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(h | (h << 16)) : "memory");
     } else {  // 3 bits: pair table from the 8-entry codebook, first code in the high 3 index bits
-      const uint16_t* cb = reinterpret_cast<const uint16_t*>(lut);
-      uint32_t v = (uint32_t)cb[e >> 3] | ((uint32_t)cb[e & 7] << 16);
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v));
+      auto code = [&](int c) {
+        const uint32_t pair = word(c >> 1);
+        return (c & 1) ? (pair >> 16) : (pair & 0xFFFFu);
+      };
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(code(e >> 3) | (code(e & 7) << 16)) : "memory");
     }
   }
 }
@@ -177,194 +234,322 @@ __device__ __forceinline__ uint32_t entry_addr(uint32_t w, uint32_t lane_base) {
   }
 }
 
-// ---- one slab in registers ----------------------------------------------------
-template <int BITS>
-struct Slab {
-  using L = Layout<BITS>;
-  uint4 code[kSubTiles * L::V];
-  uint4 sc[L::KSB];
-};
-
-template <int BITS>
-__device__ __forceinline__ void load_slab(Slab<BITS>& s, const uint8_t* slab, int lane) {
-  using L = Layout<BITS>;
-#pragma unroll
-  for (int i = 0; i < kSubTiles * L::V; ++i) s.code[i] = ldg_stream(slab + (i * 32 + lane) * 16);
-#pragma unroll
-  for (int jb = 0; jb < L::KSB; ++jb) s.sc[jb] = ldg_stream(slab + L::kCodeBytes + jb * 128 + (lane >> 2) * 16);
-}
-
-// A fragments of sub-tile R for the four MMA k-steps of 64-block JB.
+// A fragments of one sub-tile for the four MMA k-steps of 64-block JB, from the lane's
+// code vectors `code[0..V)` of that sub-tile.
 //   a[s][0] = row g,   elements 4s, 4s+1      a[s][1] = row g+8, elements 4s, 4s+1
 //   a[s][2] = row g,   elements 4s+2, 4s+3    a[s][3] = row g+8, elements 4s+2, 4s+3
 // (elements counted inside the lane's 16-element share of the block; x is read
 // with the same numbering, so the product does not depend on it).
-template <int BITS, int R, int JB>
-__device__ __forceinline__ void build_fragments(const Slab<BITS>& s, uint32_t lane_base, uint32_t (&a)[4][4]) {
-  using L = Layout<BITS>;
+template <int BITS, int JB>
+__device__ __forceinline__ void build_fragments(const uint4 (&code)[Layout<BITS>::V], uint32_t lane_base,
+                                                uint32_t (&a)[4][4]) {
   if constexpr (BITS == 4) {
-    const uint4& c = s.code[R];
-    a[0][0] = lds32(entry_addr<4, 0>(c.x, lane_base)); a[0][2] = lds32(entry_addr<4, 1>(c.x, lane_base));
-    a[1][0] = lds32(entry_addr<4, 2>(c.x, lane_base)); a[1][2] = lds32(entry_addr<4, 3>(c.x, lane_base));
-    a[2][0] = lds32(entry_addr<4, 0>(c.y, lane_base)); a[2][2] = lds32(entry_addr<4, 1>(c.y, lane_base));
-    a[3][0] = lds32(entry_addr<4, 2>(c.y, lane_base)); a[3][2] = lds32(entry_addr<4, 3>(c.y, lane_base));
-    a[0][1] = lds32(entry_addr<4, 0>(c.z, lane_base)); a[0][3] = lds32(entry_addr<4, 1>(c.z, lane_base));
-    a[1][1] = lds32(entry_addr<4, 2>(c.z, lane_base)); a[1][3] = lds32(entry_addr<4, 3>(c.z, lane_base));
-    a[2][1] = lds32(entry_addr<4, 0>(c.w, lane_base)); a[2][3] = lds32(entry_addr<4, 1>(c.w, lane_base));
-    a[3][1] = lds32(entry_addr<4, 2>(c.w, lane_base)); a[3][3] = lds32(entry_addr<4, 3>(c.w, lane_base));
+    const uint4& c = code[0];
+    a[0][0] = lut32(entry_addr<4, 0>(c.x, lane_base)); a[0][2] = lut32(entry_addr<4, 1>(c.x, lane_base));
+    a[1][0] = lut32(entry_addr<4, 2>(c.x, lane_base)); a[1][2] = lut32(entry_addr<4, 3>(c.x, lane_base));
+    a[2][0] = lut32(entry_addr<4, 0>(c.y, lane_base)); a[2][2] = lut32(entry_addr<4, 1>(c.y, lane_base));
+    a[3][0] = lut32(entry_addr<4, 2>(c.y, lane_base)); a[3][2] = lut32(entry_addr<4, 3>(c.y, lane_base));
+    a[0][1] = lut32(entry_addr<4, 0>(c.z, lane_base)); a[0][3] = lut32(entry_addr<4, 1>(c.z, lane_base));
+    a[1][1] = lut32(entry_addr<4, 2>(c.z, lane_base)); a[1][3] = lut32(entry_addr<4, 3>(c.z, lane_base));
+    a[2][1] = lut32(entry_addr<4, 0>(c.w, lane_base)); a[2][3] = lut32(entry_addr<4, 1>(c.w, lane_base));
+    a[3][1] = lut32(entry_addr<4, 2>(c.w, lane_base)); a[3][3] = lut32(entry_addr<4, 3>(c.w, lane_base));
   } else if constexpr (BITS == 2) {
-    const uint4& c = s.code[R];
+    const uint4& c = code[0];
     const uint32_t wg = word_of<2 * JB>(c), wh = word_of<2 * JB + 1>(c);
     uint2 q;
-    q = lds64(entry_addr<2, 0>(wg, lane_base)); a[0][0] = q.x; a[0][2] = q.y;
-    q = lds64(entry_addr<2, 1>(wg, lane_base)); a[1][0] = q.x; a[1][2] = q.y;
-    q = lds64(entry_addr<2, 2>(wg, lane_base)); a[2][0] = q.x; a[2][2] = q.y;
-    q = lds64(entry_addr<2, 3>(wg, lane_base)); a[3][0] = q.x; a[3][2] = q.y;
-    q = lds64(entry_addr<2, 0>(wh, lane_base)); a[0][1] = q.x; a[0][3] = q.y;
-    q = lds64(entry_addr<2, 1>(wh, lane_base)); a[1][1] = q.x; a[1][3] = q.y;
-    q = lds64(entry_addr<2, 2>(wh, lane_base)); a[2][1] = q.x; a[2][3] = q.y;
-    q = lds64(entry_addr<2, 3>(wh, lane_base)); a[3][1] = q.x; a[3][3] = q.y;
+    q = lut64(entry_addr<2, 0>(wg, lane_base)); a[0][0] = q.x; a[0][2] = q.y;
+    q = lut64(entry_addr<2, 1>(wg, lane_base)); a[1][0] = q.x; a[1][2] = q.y;
+    q = lut64(entry_addr<2, 2>(wg, lane_base)); a[2][0] = q.x; a[2][2] = q.y;
+    q = lut64(entry_addr<2, 3>(wg, lane_base)); a[3][0] = q.x; a[3][2] = q.y;
+    q = lut64(entry_addr<2, 0>(wh, lane_base)); a[0][1] = q.x; a[0][3] = q.y;
+    q = lut64(entry_addr<2, 1>(wh, lane_base)); a[1][1] = q.x; a[1][3] = q.y;
+    q = lut64(entry_addr<2, 2>(wh, lane_base)); a[2][1] = q.x; a[2][3] = q.y;
+    q = lut64(entry_addr<2, 3>(wh, lane_base)); a[3][1] = q.x; a[3][3] = q.y;
   } else if constexpr (BITS == 1) {
-    const uint32_t w = word_of<JB>(s.code[R]);  // bytes 0,1: row g; bytes 2,3: row g+8
+    const uint32_t w = word_of<JB>(code[0]);  // bytes 0,1: row g; bytes 2,3: row g+8
     uint4 q;
-    q = lds128(entry_addr<1, 0>(w, lane_base)); a[0][0] = q.x; a[0][2] = q.y; a[1][0] = q.z; a[1][2] = q.w;
-    q = lds128(entry_addr<1, 1>(w, lane_base)); a[2][0] = q.x; a[2][2] = q.y; a[3][0] = q.z; a[3][2] = q.w;
-    q = lds128(entry_addr<1, 2>(w, lane_base)); a[0][1] = q.x; a[0][3] = q.y; a[1][1] = q.z; a[1][3] = q.w;
-    q = lds128(entry_addr<1, 3>(w, lane_base)); a[2][1] = q.x; a[2][3] = q.y; a[3][1] = q.z; a[3][3] = q.w;
+    q = lut128(entry_addr<1, 0>(w, lane_base)); a[0][0] = q.x; a[0][2] = q.y; a[1][0] = q.z; a[1][2] = q.w;
+    q = lut128(entry_addr<1, 1>(w, lane_base)); a[2][0] = q.x; a[2][2] = q.y; a[3][0] = q.z; a[3][2] = q.w;
+    q = lut128(entry_addr<1, 2>(w, lane_base)); a[0][1] = q.x; a[0][3] = q.y; a[1][1] = q.z; a[1][3] = q.w;
+    q = lut128(entry_addr<1, 3>(w, lane_base)); a[2][1] = q.x; a[2][3] = q.y; a[3][1] = q.z; a[3][3] = q.w;
   } else if constexpr (BITS == 8) {
-    const uint4& cg = s.code[R * 2];      // row g: 16 bytes = 16 elements
-    const uint4& ch = s.code[R * 2 + 1];  // row g+8
+    const uint4& cg = code[0];  // row g: 16 bytes = 16 elements
+    const uint4& ch = code[1];  // row g+8
 #pragma unroll
     for (int st = 0; st < 4; ++st) {
       const uint32_t wg = word_at(cg, st), wh = word_at(ch, st);
-      a[st][0] = prmt<0x7610>(lds32(entry_addr<8, 0>(wg, lane_base)), lds32(entry_addr<8, 1>(wg, lane_base)));
-      a[st][2] = prmt<0x7610>(lds32(entry_addr<8, 2>(wg, lane_base)), lds32(entry_addr<8, 3>(wg, lane_base)));
-      a[st][1] = prmt<0x7610>(lds32(entry_addr<8, 0>(wh, lane_base)), lds32(entry_addr<8, 1>(wh, lane_base)));
-      a[st][3] = prmt<0x7610>(lds32(entry_addr<8, 2>(wh, lane_base)), lds32(entry_addr<8, 3>(wh, lane_base)));
+      a[st][0] = prmt<0x7610>(lut32(entry_addr<8, 0>(wg, lane_base)), lut32(entry_addr<8, 1>(wg, lane_base)));
+      a[st][2] = prmt<0x7610>(lut32(entry_addr<8, 2>(wg, lane_base)), lut32(entry_addr<8, 3>(wg, lane_base)));
+      a[st][1] = prmt<0x7610>(lut32(entry_addr<8, 0>(wh, lane_base)), lut32(entry_addr<8, 1>(wh, lane_base)));
+      a[st][3] = prmt<0x7610>(lut32(entry_addr<8, 2>(wh, lane_base)), lut32(entry_addr<8, 3>(wh, lane_base)));
     }
   } else {  // 3 bits: 96-bit little-endian group per block, pair field f at bits [6f, 6f+6)
     uint32_t w[3];
 #pragma unroll
     for (int i = 0; i < 3; ++i) {
-      constexpr int kWordsPerVec = 4;
       const int wi = 3 * JB + i;
-      w[i] = word_at(s.code[R * L::V + wi / kWordsPerVec], wi % kWordsPerVec);
+      w[i] = word_at(code[wi / 4], wi % 4);
     }
 #pragma unroll
     for (int f = 0; f < 16; ++f) {
-      const int o = 6 * f;            // bit offset of the field
+      const int o = 6 * f;  // bit offset of the field
       const int wi = o >> 5, sh = o & 31;
-      uint32_t v;
+      uint32_t v;  // field moved to bits 8..13
       if (sh + 6 <= 32) {
-        // want field << 8: shift right by sh-8 (or left by 8-sh)
         v = (sh >= 8) ? (w[wi] >> (sh - 8)) : (w[wi] << (8 - sh));
       } else {
         v = __funnelshift_r(w[wi], w[wi + 1], sh - 8);
       }
-      uint32_t addr = (v & 0x3F00u) | lane_base;
       const int p = f & 7, half = f >> 3;
-      a[p >> 1][(p & 1) * 2 + half] = lds32(addr);
+      a[p >> 1][(p & 1) * 2 + half] = lut32((v & 0x3F00u) | lane_base);
     }
   }
+}
+
+
+// ---- row-tile epilogue ----------------------------------------------------------
+// No CTA-wide barrier anywhere: a warp that has finished its slabs of a row tile deposits its
+// totals in shared memory and moves on; the LAST warp of the CTA to do so adds the deposits
+// up in warp order and finishes the tile (tile_finish).
+//
+// A row tile whose K range is split over several CTAs is finished by its OWNER, the CTA that
+// holds the tile's first slabs (for that CTA the tile is the last thing it works on).  The
+// other CTAs hold later slabs of the tile at the START of their ranges, so they are done with
+// it early: each stores its partial sums as {value, tag} 8-byte words into its own area of
+// the workspace and never waits.  The owner polls those words (bounded) until they carry this
+// use's tag, adds them to its own sums in CTA order, writes the outputs and bumps the tile's
+// use count.  tag = (use count + 1) * 4096 + row tile: a word left by an earlier launch or
+// another tile can never match.  No fences, no atomics, one memory round trip at the end;
+// and every sum has a fixed order, so results do not depend on timing.
+//
+// Reduction slots keep, per warp, sub-tile and n-tile, the float4 accumulator fragments of
+// the lanes that hold live batch columns only: lanes with t < TT, TT = ceil(min(m, 8) / 2),
+// stored densely as [t][g][4].  SW = 32 * TT floats per (warp, sub-tile, n-tile).
+// There are two sets of slots; consecutive row tiles of a CTA alternate between them.
+struct EpilogueSync {
+  int count[2];  // deposits so far in each slot set
+  int gen[2];    // reductions completed on each slot set
+};
+
+constexpr uint32_t kSpinLimit = 1u << 24;  // polls of a memory word before giving up
+
+__device__ __forceinline__ uint2 ld_relaxed_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_v2(uint2* p, uint2 v) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ int ld_relaxed_s32(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Run by one warp.  `slots` is the slot set of this row tile: per warp one block of
+// E = NB * 4 * SW floats laid out [sub-tile][n-tile][t][g][4].  Plain loops on purpose (this
+// runs once or twice per CTA, so its cost is mostly instruction fetches).  Returns false if a
+// bounded poll ran out.
+template <int NB, int WARPS, bool FP16>
+__device__ __noinline__ bool tile_finish(const LinearParams& p, float* slots, int rt, int c0, int c1) {
+  constexpr int EMAX = 512 * NB;  // outputs of one row tile at TT = 4
+  const int lane = threadIdx.x & 31;
+  const int tt = p.slot_t, sw = 32 * tt;
+  const int E = NB * kSubTiles * sw;
+  const int seg_lo = rt * p.k_slabs, seg_hi = seg_lo + p.k_slabs;
+  const bool full = (c0 <= seg_lo) && (c1 >= seg_hi);
+  const bool owner = (c0 <= seg_lo);  // holds the tile's first slab
+  int uses = 0;
+  if (!full) uses = ld_relaxed_s32(p.counters + rt);  // in flight while the slots are summed
+  const uint32_t tag = ((uint32_t)(uses + 1) << 12) | (uint32_t)rt;
+  uint2* mine = p.partial + (size_t)blockIdx.x * EMAX;
+  bool ok = true;
+
+  // 1. add the warps' deposits in warp order; keep the sums in warp 0's block, or (not the
+  //    owner of a split tile) publish them as tagged words and be done
+#pragma unroll 1
+  for (int e = lane; e < E; e += 32) {
+    float acc = 0.f;
+#pragma unroll 4
+    for (int w = 0; w < WARPS; ++w) acc += slots[w * E + e];
+    if (!full && !owner) {
+      st_relaxed_v2(mine + e, make_uint2(__float_as_uint(acc), tag));
+    } else {
+      slots[e] = acc;
+    }
+  }
+  if (!full && !owner) return true;
+
+  // 2. owner of a split tile: add the words of the CTAs after this one, up to the one holding
+  //    the tile's last slab, in CTA order
+  if (!full) {
+    const int big = p.rem * (p.base + 1);
+    const int last_item = seg_hi - 1;
+    const int last = last_item < big ? last_item / (p.base + 1) : p.rem + (last_item - big) / p.base;
+#pragma unroll 1
+    for (int c = blockIdx.x + 1; c <= last; ++c) {
+      const uint2* theirs = p.partial + (size_t)c * EMAX;
+#pragma unroll 1
+      for (int e0 = lane; e0 < E; e0 += 128) {  // four words per lane in flight
+        uint2 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = e0 + 32 * j;
+          v[j] = (e < E) ? ld_relaxed_v2(theirs + e) : make_uint2(0u, tag);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = e0 + 32 * j;
+          uint32_t spins = 0;
+          while (v[j].y != tag) {
+            if (++spins > kSpinLimit) {
+              ok = false;
+              break;
+            }
+            v[j] = ld_relaxed_v2(theirs + e);
+          }
+          if (e < E) slots[e] += __uint_as_float(v[j].x);
+        }
+      }
+    }
+  }
+
+  // 3. write the outputs
+#pragma unroll 1
+  for (int e = lane; e < E; e += 32) {
+    const int blk = e / sw, rem = e - blk * sw;       // blk = sub-tile * NB + n-tile
+    const int r = blk / NB, nb = blk - r * NB;
+    const int t = rem >> 5, g = (rem >> 2) & 7, c = rem & 3;
+    const int row = rt * kTileRows + 16 * r + g + 8 * (c >> 1);
+    const int b = 8 * nb + 2 * t + (c & 1);
+    if (row < p.n && b < p.m) p.out[(size_t)b * p.n + row] = from_float<FP16>(slots[e]);
+  }
+  if (!full) {
+    __syncwarp();
+    if (lane == 0) p.counters[rt] = (uses + 1) & 0x7FFFF;  // this use of the split tile is done
+  }
+  return ok;
 }
 
 // ---- the kernel -------------------------------------------------------------------
-template <int NB, bool FP16>
-__device__ __noinline__ void segment_reduce(const LinearParams& p, float* slots, int rt, int c0, int c1,
-                                            int* flag) {
-  constexpr int E = 512 * NB;  // outputs of one row tile: 64 rows x (8 * NB) batch columns
-  const int seg_lo = rt * p.k_slabs, seg_hi = seg_lo + p.k_slabs;
-  const bool full = (c0 <= seg_lo) && (c1 >= seg_hi);
-  __syncthreads();  // every warp has deposited its totals
-  float sums[NB];
-#pragma unroll
-  for (int nb = 0; nb < NB; ++nb) {
-    // element e = nb * 512 + threadIdx.x  <->  slot word (r * NB + nb) * 128 + lane * 4 + c
-    const int r = threadIdx.x >> 7, rem = threadIdx.x & 127;
-    float acc = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) acc += slots[((w * kSubTiles + r) * NB + nb) * 128 + rem];
-    sums[nb] = acc;
-  }
-  bool write_out = full;
-  if (!full) {
-    const int cta = blockIdx.x;
-    const int slot = (rt == c0 / p.k_slabs) ? 0 : 1;
-    float* mine = p.partial + ((size_t)cta * 2 + slot) * E;
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) __stcg(mine + nb * 512 + threadIdx.x, sums[nb]);
-    __threadfence();
-    __syncthreads();
-    // which CTAs share this row tile: those owning slab seg_lo .. seg_hi-1
-    const int big = p.rem * (p.base + 1);
-    auto owner = [&](int item) { return item < big ? item / (p.base + 1) : p.rem + (item - big) / p.base; };
-    const int first = owner(seg_lo), last = owner(seg_hi - 1);
-    if (threadIdx.x == 0) {
-      int old = atomicAdd(p.counters + rt, 1);
-      *flag = (old == last - first) ? 1 : 0;
-    }
-    __syncthreads();
-    if (*flag) {
-      __threadfence();
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb) sums[nb] = 0.f;
-      for (int c = first; c <= last; ++c) {
-        const int cs = c * p.base + min(c, p.rem);  // first slab of CTA c
-        const int sl = (rt == cs / p.k_slabs) ? 0 : 1;
-        const float* theirs = p.partial + ((size_t)c * 2 + sl) * E;
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) sums[nb] += __ldcg(theirs + nb * 512 + threadIdx.x);
-      }
-      if (threadIdx.x == 0) p.counters[rt] = 0;  // leave the workspace clean for the next launch
-      write_out = true;
-    }
-  }
-  if (write_out) {
-    const int r = threadIdx.x >> 7, lane = (threadIdx.x >> 2) & 31, c = threadIdx.x & 3;
-    const int row = rt * kTileRows + 16 * r + (lane >> 2) + 8 * (c >> 1);
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-      const int b = 8 * nb + 2 * (lane & 3) + (c & 1);
-      if (row < p.n && b < p.m) p.out[(size_t)b * p.n + row] = from_float<FP16>(sums[nb]);
-    }
-  }
-  __syncthreads();  // slots may be overwritten after this
-}
+constexpr int kXRowPad = 16;  // x rows in a stage are 16 bytes apart from a 128-byte multiple: no bank conflicts
 
-template <int BITS, int NB, bool FP16>
-__global__ void __launch_bounds__(kThreads, 1) linear_lut_kernel(const __grid_constant__ LinearParams p) {
+template <int BITS, int NB, int WARPS, bool FP16>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+    linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
   using T = Table<BITS>;
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  __shared__ int flag;
+  constexpr uint32_t kXRow = 128 * L::KSB + kXRowPad;  // bytes between x rows inside a stage
+  extern __shared__ __align__(128) uint8_t smem_raw[];
 
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-
-  // shared-memory carve-up: [pad to 64 KB][table][reduction slots]
+  // The host planned the shared-memory layout for a known window address; refuse to run on
+  // anything else (uniform exit before any barrier).
   const uint32_t raw = smem_addr(smem_raw);
-  const uint32_t table_base = T::kAligned64K ? ((raw + 0xFFFFu) & ~0xFFFFu) : ((raw + 15u) & ~15u);
-  float* slots = reinterpret_cast<float*>(smem_raw + (table_base - raw) + T::kBytes);
-  const uint32_t lane_base = table_base + lane * T::kEntryBytes;
+  if (raw != p.smem_base) {
+    if (threadIdx.x == 0) atomicOr(p.counters + kStatusWord, kStatusSmemLayout);
+    return;
+  }
+#ifdef FDK_TRACE
+  const long long tr0 = clock64();
+  long long tr_wait = 0, tr_comp = 0, tr_flush = 0, tr_refill = 0, tr_finish = 0;
+#define FDK_T(var) var
+#else
+#define FDK_T(var)
+#endif
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int W = WARPS;
+  const int S = p.stages;
+  const int g = lane >> 2, t = lane & 3;
+  float* slots = reinterpret_cast<float*>(smem_raw + (p.slots_addr - raw));
+  EpilogueSync* esync = reinterpret_cast<EpilogueSync*>(smem_raw + (p.mbar_addr - raw) + W * S * 8);
+  if (threadIdx.x == 0) {
+    esync->count[0] = esync->count[1] = 0;
+    esync->gen[0] = esync->gen[1] = 0;
+  }
+  const uint32_t lane_base = p.table_addr + lane * T::kEntryBytes;
+
 
   // my slab range
   const int cta = blockIdx.x;
   const int c0 = cta * p.base + min(cta, p.rem);
   const int c1 = c0 + p.base + (cta < p.rem ? 1 : 0);
 
-  // start streaming before anything else
-  constexpr int kDepth = depth_for<BITS, NB>();
-  Slab<BITS> buf[kDepth];
-  int it = c0 + warp;
-#pragma unroll
-  for (int d = 0; d < kDepth; ++d) {
-    const int i = it + d * kWarps;
-    if (i < c1) load_slab<BITS>(buf[d], p.tiled + (size_t)i * L::kSlabBytes, lane);
+  // this warp's ring: stage s lives at stage_addr(s), its barrier at bar_addr(s)
+  auto stage_addr = [&](int s) -> uint32_t {
+    const uint32_t q = warp * S + s;
+    return q < p.stage_a_count ? p.stage_a_addr + q * p.stage_bytes
+                               : p.stage_b_addr + (q - p.stage_a_count) * p.stage_bytes;
+  };
+  auto bar_addr = [&](int s) -> uint32_t { return p.mbar_addr + (warp * S + s) * 8; };
+  // valid x bytes per row for the slab at position kpos of its row tile
+  auto x_bytes = [&](int kpos) -> uint32_t {
+    const int left = p.k - kpos * L::kSlabK;
+    return 2u * (uint32_t)(left < L::kSlabK ? left : L::kSlabK);
+  };
+  // lane 0: announce the bytes of slab i and start its weight copy
+  auto issue_weights = [&](int i, int kpos, int s) {
+    const uint32_t bar = bar_addr(s);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                 "r"((uint32_t)L::kSlabBytes + (uint32_t)p.m * x_bytes(kpos))
+                 : "memory");
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            stage_addr(s)),
+        "l"(p.tiled + (size_t)i * L::kSlabBytes), "r"((uint32_t)L::kSlabBytes), "r"(bar)
+        : "memory");
+  };
+  // lanes 0..m-1: one x row each, for the same slab
+  auto issue_x = [&](int kpos, int s) {
+    if (lane < p.m) {
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+              stage_addr(s) + (uint32_t)L::kSlabBytes + lane * kXRow),
+          "l"(p.x + (size_t)lane * p.k + (size_t)kpos * L::kSlabK), "r"(x_bytes(kpos)), "r"(bar_addr(s))
+          : "memory");
+    }
+  };
+
+  int it = c0 + warp;               // next slab of this warp
+  int rt = it / p.k_slabs;          // its row tile and position inside the tile
+  int ks = it - rt * p.k_slabs;
+  // the prefetch cursor runs S slabs ahead
+  int pf_it = it, pf_ks = ks;
+  auto pf_advance = [&]() {
+    pf_it += W;
+    pf_ks += W;
+    while (pf_ks >= p.k_slabs) pf_ks -= p.k_slabs;
+  };
+
+  if (lane == 0) {
+    for (int s = 0; s < S; ++s) mbar_init(bar_addr(s), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // start streaming before anything else: these copies read weights only
+    int i = it, kp = ks;
+    for (int s = 0; s < S && i < c1; ++s) {
+      issue_weights(i, kp, s);
+      i += W;
+      kp += W;
+      while (kp >= p.k_slabs) kp -= p.k_slabs;
+    }
   }
-  fill_table<BITS, FP16>(table_base, p.lut);
-  // everything above reads only weights; x, out and the workspace belong to the stream order
+  if (p.lut == nullptr) {
+    fill_table<BITS>(p.table_addr, [&](int i) { return inl.w[i]; });
+  } else {
+    fill_table<BITS>(p.table_addr, [&](int i) { return __ldg(reinterpret_cast<const uint32_t*>(p.lut) + i); });
+  }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // everything above touched only weights; x, out and the workspace follow stream order
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  __syncwarp();
+  for (int s = 0; s < S && pf_it < c1; ++s) {
+    issue_x(pf_ks, s);
+    pf_advance();
+  }
+  FDK_T(const long long tr1 = clock64();)
   __syncthreads();
+  FDK_T(const long long tr2 = clock64();)
 
   float tot[kSubTiles][NB][4];
 #pragma unroll
@@ -377,54 +562,101 @@ __global__ void __launch_bounds__(kThreads, 1) linear_lut_kernel(const __grid_co
   const int rt_first = c0 / p.k_slabs;
   const int rt_last = (c1 - 1) / p.k_slabs;
   int cur_rt = rt_first;
+  bool timed_out = false;
+  const int tt = p.slot_t, sw = 32 * tt;
 
+  const uint32_t slot_set_floats = W * kSubTiles * NB * sw;
   auto flush_until = [&](int target) {
     while (cur_rt < target) {
+      const int seg = cur_rt - rt_first, set = seg & 1;
+      float* my_slots = slots + set * slot_set_floats;
+      // the slot set is free once the reduction of two row tiles ago has read it
+      {
+        volatile int* gen = &esync->gen[set];
+        uint32_t spins = 0;
+        while (*gen != (seg >> 1)) {
+          if (++spins > kSpinLimit) {
+            timed_out = true;
+            break;
+          }
+        }
+      }
 #pragma unroll
       for (int r = 0; r < kSubTiles; ++r)
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          float4 v = make_float4(tot[r][nb][0], tot[r][nb][1], tot[r][nb][2], tot[r][nb][3]);
-          *reinterpret_cast<float4*>(slots + ((warp * kSubTiles + r) * NB + nb) * 128 + lane * 4) = v;
+          if (t < tt) {
+            float4 v = make_float4(tot[r][nb][0], tot[r][nb][1], tot[r][nb][2], tot[r][nb][3]);
+            *reinterpret_cast<float4*>(my_slots + ((warp * kSubTiles + r) * NB + nb) * sw + t * 32 + g * 4) = v;
+          }
           tot[r][nb][0] = tot[r][nb][1] = tot[r][nb][2] = tot[r][nb][3] = 0.f;
         }
-      segment_reduce<NB, FP16>(p, slots, cur_rt, c0, c1, &flag);
+      __threadfence_block();
+      __syncwarp();
+      int old = 0;
+      if (lane == 0) old = atomicAdd(&esync->count[set], 1);
+      old = __shfl_sync(0xffffffffu, old, 0);
+      if (old == W - 1) {  // every warp of the CTA has deposited: this warp finishes the tile
+        __threadfence_block();
+        FDK_T(long long tf = clock64();)
+        if (!tile_finish<NB, WARPS, FP16>(p, my_slots, cur_rt, c0, c1)) timed_out = true;
+        FDK_T(tr_finish += clock64() - tf;)
+        __syncwarp();
+        if (lane == 0) {
+          esync->count[set] = 0;
+          __threadfence_block();
+          atomicAdd(&esync->gen[set], 1);
+        }
+      }
       ++cur_rt;
     }
   };
 
-  auto compute = [&](const Slab<BITS>& s, int ks) {
+  // One slab: stage address `sa`, slab position `kpos` inside its row tile.
+  auto compute = [&](uint32_t sa, int kpos) {
+    constexpr bool kPreload = (L::V == 1 && L::KSB > 1);
+    uint4 pre[kPreload ? kSubTiles : 1];
+    if constexpr (kPreload) {
+#pragma unroll
+      for (int r = 0; r < kSubTiles; ++r) pre[r] = ring128(sa + (r * 32 + lane) * 16);
+    }
     auto block = [&](auto jbc) {
       constexpr int JB = decltype(jbc)::value;
-      const int kb = (ks * L::KSB + JB) * kBlock;
+      if ((kpos * L::KSB + JB) * kBlock >= p.k) return;  // padded block: codes and scales are zero
       uint32_t xb[NB][8];
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
-        const int b = g + 8 * nb;
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-        if (b < p.m && kb < p.k) {
-          const uint16_t* src = p.x + (size_t)b * p.k + kb + 16 * t;
-          lo = ldg_l1(src);
-          hi = ldg_l1(src + 8);
-        }
+        const int b = min(g + 8 * nb, p.m - 1);  // lanes of unused batch columns read a live row
+        const uint32_t xa = sa + L::kSlabBytes + b * kXRow + JB * 128 + t * 32;
+        const uint4 lo = ring128(xa), hi = ring128(xa + 16);
         xb[nb][0] = lo.x; xb[nb][1] = lo.y; xb[nb][2] = lo.z; xb[nb][3] = lo.w;
         xb[nb][4] = hi.x; xb[nb][5] = hi.y; xb[nb][6] = hi.z; xb[nb][7] = hi.w;
       }
+      const uint4 sc = ring128(sa + L::kCodeBytes + JB * 128 + g * 16);
       auto sub_tile = [&](auto rc) {
         constexpr int R = decltype(rc)::value;
+        uint4 code[L::V];
+        if constexpr (kPreload) {
+          code[0] = pre[R];
+        } else {
+#pragma unroll
+          for (int v = 0; v < L::V; ++v) code[v] = ring128(sa + ((R * L::V + v) * 32 + lane) * 16);
+        }
         uint32_t a[4][4];
-        build_fragments<BITS, R, JB>(s, lane_base, a);
-        const uint32_t scw = word_of<R>(s.sc[JB]);
+        build_fragments<BITS, JB>(code, lane_base, a);
+        const uint32_t scw = word_of<R>(sc);
         const float s_lo = pair_lo<FP16>(scw), s_hi = pair_hi<FP16>(scw);
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          float acc[4];
+          const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+          mma16816<FP16>(acc, a[0], xb[nb][0], xb[nb][1], zero);
 #pragma unroll
-          for (int st = 0; st < 4; ++st) mma16816<FP16>(acc, a[st], xb[nb][2 * st], xb[nb][2 * st + 1]);
-          tot[R][nb][0] += acc[0] * s_lo;
-          tot[R][nb][1] += acc[1] * s_lo;
-          tot[R][nb][2] += acc[2] * s_hi;
-          tot[R][nb][3] += acc[3] * s_hi;
+          for (int st = 1; st < 4; ++st) mma16816<FP16>(acc, a[st], xb[nb][2 * st], xb[nb][2 * st + 1], acc);
+          tot[R][nb][0] = fmaf(acc[0], s_lo, tot[R][nb][0]);
+          tot[R][nb][1] = fmaf(acc[1], s_lo, tot[R][nb][1]);
+          tot[R][nb][2] = fmaf(acc[2], s_hi, tot[R][nb][2]);
+          tot[R][nb][3] = fmaf(acc[3], s_hi, tot[R][nb][3]);
         }
       };
       sub_tile(std::integral_constant<int, 0>{});
@@ -440,40 +672,142 @@ __global__ void __launch_bounds__(kThreads, 1) linear_lut_kernel(const __grid_co
     }
   };
 
+  int s = 0;
+  uint32_t parity = 0;
   while (it < c1) {
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
-      if (it < c1) {
-        const int rt = it / p.k_slabs;
-        const int ks = it - rt * p.k_slabs;
-        if (rt != cur_rt) flush_until(rt);
-        compute(buf[d], ks);
-        const int nx = it + kDepth * kWarps;
-        if (nx < c1) load_slab<BITS>(buf[d], p.tiled + (size_t)nx * L::kSlabBytes, lane);
-        it += kWarps;
-      }
+    FDK_T(long long ta = clock64();)
+    if (rt != cur_rt) flush_until(rt);
+    FDK_T(long long tb = clock64(); tr_flush += tb - ta;)
+    if (!mbar_wait(bar_addr(s), parity)) timed_out = true;  // carry on with whatever is there
+    FDK_T(long long tc = clock64(); tr_wait += tc - tb;)
+    compute(stage_addr(s), ks);
+    __syncwarp();  // every lane has consumed its share of this stage
+    FDK_T(long long td = clock64(); tr_comp += td - tc;)
+    if (pf_it < c1) {
+      if (lane == 0) issue_weights(pf_it, pf_ks, s);
+      __syncwarp();
+      issue_x(pf_ks, s);
+      pf_advance();
+    }
+    FDK_T(tr_refill += clock64() - td;)
+    it += W;
+    ks += W;
+    while (ks >= p.k_slabs) {
+      ks -= p.k_slabs;
+      ++rt;
+    }
+    if (++s == S) {
+      s = 0;
+      parity ^= 1;
     }
   }
+  FDK_T(const long long tr3 = clock64();)
   flush_until(rt_last + 1);
+  if (timed_out && lane == 0) atomicOr(p.counters + kStatusWord, kStatusTimeout);
+#ifdef FDK_TRACE
+  if (p.trace != nullptr && lane == 0) {
+    unsigned long long* o = p.trace + ((size_t)blockIdx.x * W + warp) * 8;
+    o[0] = tr1 - tr0; o[1] = tr_refill; o[2] = tr3 - tr2; o[3] = clock64() - tr3;
+    o[4] = tr_wait; o[5] = tr_comp; o[6] = tr_flush; o[7] = tr_finish + 1;
+  }
+#endif
+#undef FDK_T
 }
 
-constexpr size_t kCounterBytes = 16384;  // 4096 row tiles = 262144 output rows
+// ---- host side ----------------------------------------------------------------------
+constexpr size_t kCounterBytes = 16384;  // 4095 row-tile counters + 1 status word
 
-template <int BITS, int NB, bool FP16>
-int launch(const LinearParams& p, int grid, unsigned flags, cudaStream_t stream) {
-  using T = Table<BITS>;
-  const size_t smem = (T::kAligned64K ? 65536 : 16) + T::kBytes + (size_t)kWarps * kSubTiles * NB * 128 * sizeof(float);
-  auto kernel = linear_lut_kernel<BITS, NB, FP16>;
-  static bool configured[64] = {};
+__global__ void probe_smem_base_kernel(uint32_t* out) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  *out = smem_addr(smem_raw);
+}
+
+// Address, in the shared window, at which a kernel without static shared memory sees its
+// dynamic shared memory.  Asked of the device once (first call on a device synchronises).
+int dynamic_smem_base(uint32_t* out) {
+  static uint32_t cache[64];
+  static bool have[64] = {};
   int dev = 0;
   FDK_CUDA(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
+  dev &= 63;
+  if (!have[dev]) {
+    uint32_t* d = nullptr;
+    FDK_CUDA(cudaMalloc(&d, sizeof(uint32_t)));
+    probe_smem_base_kernel<<<1, 1, 1024>>>(d);
+    cudaError_t e = cudaMemcpy(&cache[dev], d, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    FDK_CUDA(e);
+    have[dev] = true;
+  }
+  *out = cache[dev];
+  return FDK_OK;
+}
+
+inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Plans the shared-memory layout for `warps` warps with `stages` ring stages each; returns
+// the dynamic size needed.
+template <int BITS, int NB>
+size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
+  using L = Layout<BITS>;
+  using T = Table<BITS>;
+  const uint32_t n_stages = warps * stages;
+  const uint32_t tt = ((p.m < 8 ? p.m : 8) + 1) / 2;
+  const uint32_t slot_bytes = 2 * warps * kSubTiles * NB * 32 * tt * sizeof(float);  // two sets
+  const uint32_t mbar_bytes = align_up(n_stages * 8 + sizeof(EpilogueSync), 128);  // barriers + epilogue sync words
+  const uint32_t stage_bytes = align_up(L::kSlabBytes + p.m * (128 * L::KSB + kXRowPad), 128);
+  p.stage_bytes = stage_bytes;
+  p.stages = stages;
+  p.slot_t = tt;
+  uint32_t cursor = align_up(base, 128);
+  p.smem_base = base;
+  p.mbar_addr = cursor;
+  cursor += mbar_bytes;
+  if (T::kAligned64K) {
+    const uint32_t table = align_up(cursor, 65536);
+    p.table_addr = table;
+    uint32_t above = table + T::kBytes;
+    // below the table: reduction slots if they fit, then as many stages as fit
+    if (cursor + slot_bytes <= table) {
+      p.slots_addr = cursor;
+      cursor += slot_bytes;
+    } else {
+      p.slots_addr = above;
+      above += slot_bytes;
+    }
+    cursor = align_up(cursor, 128);
+    p.stage_a_addr = cursor;
+    p.stage_a_count = (table - cursor) / stage_bytes;
+    if (p.stage_a_count > n_stages) p.stage_a_count = n_stages;
+    p.stage_b_addr = above;
+    above += (n_stages - p.stage_a_count) * stage_bytes;
+    return above - base;
+  }
+  p.slots_addr = cursor;
+  cursor = align_up(cursor + slot_bytes, 128);
+  p.table_addr = cursor;
+  cursor += T::kBytes;
+  p.stage_a_addr = cursor;
+  p.stage_a_count = n_stages;
+  p.stage_b_addr = cursor;
+  cursor += n_stages * stage_bytes;
+  return cursor - base;
+}
+
+template <int BITS, int NB, int WARPS, bool FP16>
+int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int grid, unsigned flags,
+                   cudaStream_t stream) {
+  auto kernel = linear_lut_kernel<BITS, NB, WARPS, FP16>;
+  static size_t configured[64] = {};
+  int dev = 0;
+  FDK_CUDA(cudaGetDevice(&dev));
+  if (configured[dev & 63] < smem) {
     FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[dev & 63] = true;
+    configured[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(WARPS * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -481,17 +815,73 @@ int launch(const LinearParams& p, int grid, unsigned flags, cudaStream_t stream)
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (flags & FDK_FLAG_PDL) ? 1 : 0;
-  FDK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+  FDK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, inl));
   return FDK_OK;
 }
 
+// Picks the widest CTA that still leaves two ring stages per warp (one being consumed, one
+// in flight); failing that, the widest that fits at all.
+template <int BITS, int NB, bool FP16>
+int launch(LinearParams p, const void* lut_host, int grid, unsigned flags, cudaStream_t stream) {
+  InlineLut<BITS> inl;
+  if (lut_host != nullptr) {
+    memcpy(inl.w, lut_host, sizeof(inl.w));
+    p.lut = nullptr;
+  } else {
+    memset(inl.w, 0, sizeof(inl.w));
+  }
+  uint32_t base = 0;
+  if (int st = dynamic_smem_base(&base)) return st;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  constexpr int kWide = (NB == 1) ? 24 : 16;
+  constexpr int kMid = (NB == 1) ? 16 : 8;
+  constexpr int kNarrow = (NB == 1) ? 8 : 4;
+  const int widths[3] = {kWide, kMid, kNarrow};
+  int best_w = 0, best_s = 0;
+  size_t best_smem = 0;
+#ifdef FDK_TRACE
+  static const char* env_s = getenv("FDK_STAGES");
+  static const char* env_w = getenv("FDK_WARPS");
+  if (env_s != nullptr) {
+    const int want_w = env_w ? atoi(env_w) : kWide;
+    LinearParams q = p;
+    best_smem = plan_smem<BITS, NB>(base, want_w, atoi(env_s), q);
+    best_w = want_w;
+    best_s = atoi(env_s);
+  }
+#endif
+  for (int want = 2; want >= 1 && !best_w; --want) {
+    for (int wi = 0; wi < 3 && !best_w; ++wi) {
+      for (int s = kMaxStages; s >= want; --s) {
+        LinearParams q = p;
+        size_t smem = plan_smem<BITS, NB>(base, widths[wi], s, q);
+        if (smem <= (size_t)di.max_smem_optin) {
+          best_w = widths[wi];
+          best_s = s;
+          best_smem = smem;
+          break;
+        }
+      }
+    }
+  }
+  FDK_CHECK_ARG(best_w != 0, FDK_ERR_CUDA, "no shared-memory plan fits %d bytes", di.max_smem_optin);
+  plan_smem<BITS, NB>(base, best_w, best_s, p);
+  if (best_w == kWide) return launch_variant<BITS, NB, kWide, FP16>(p, inl, best_smem, grid, flags, stream);
+  if (best_w == kMid) return launch_variant<BITS, NB, kMid, FP16>(p, inl, best_smem, grid, flags, stream);
+  return launch_variant<BITS, NB, kNarrow, FP16>(p, inl, best_smem, grid, flags, stream);
+}
+
 template <int BITS>
-int launch_bits(const LinearParams& p, int grid, int dtype, unsigned flags, cudaStream_t stream) {
+int launch_bits(const LinearParams& p, const void* lut_host, int grid, int dtype, unsigned flags,
+                cudaStream_t stream) {
   const bool wide = p.m > 8;
   if (dtype == FDK_DTYPE_F16) {
-    return wide ? launch<BITS, 2, true>(p, grid, flags, stream) : launch<BITS, 1, true>(p, grid, flags, stream);
+    return wide ? launch<BITS, 2, true>(p, lut_host, grid, flags, stream)
+                : launch<BITS, 1, true>(p, lut_host, grid, flags, stream);
   }
-  return wide ? launch<BITS, 2, false>(p, grid, flags, stream) : launch<BITS, 1, false>(p, grid, flags, stream);
+  return wide ? launch<BITS, 2, false>(p, lut_host, grid, flags, stream)
+              : launch<BITS, 1, false>(p, lut_host, grid, flags, stream);
 }
 
 }  // namespace
@@ -499,28 +889,41 @@ int launch_bits(const LinearParams& p, int grid, int dtype, unsigned flags, cuda
 
 using namespace fdk;
 
+#ifdef FDK_TRACE
+static unsigned long long* g_trace = nullptr;
+extern "C" void fdk_debug_set_trace(void* p) { g_trace = (unsigned long long*)p; }
+#endif
+
 extern "C" int fdk_workspace_size(size_t* bytes_host) {
   FDK_CHECK_ARG(bytes_host != nullptr, FDK_ERR_BAD_ARG, "bytes_host is null");
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
-  *bytes_host = kCounterBytes + (size_t)di.sm_count * 2 * 1024 * sizeof(float);
+  *bytes_host = kCounterBytes + (size_t)di.sm_count * 1024 * sizeof(uint2);
   return FDK_OK;
 }
 
 extern "C" int fdk_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
   FDK_CHECK_ARG(workspace != nullptr, FDK_ERR_WORKSPACE, "workspace is null");
   FDK_CHECK_ARG(workspace_bytes >= kCounterBytes, FDK_ERR_WORKSPACE, "workspace of %zu bytes is too small", workspace_bytes);
-  FDK_CUDA(cudaMemsetAsync(workspace, 0, kCounterBytes, (cudaStream_t)stream));
+  uint32_t base = 0;
+  if (int st = dynamic_smem_base(&base)) return st;  // one-time device query, kept out of later captures
+  FDK_CUDA(cudaMemsetAsync(workspace, 0, workspace_bytes, (cudaStream_t)stream));
   return FDK_OK;
 }
 
-extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut, void* out, int m, int n,
-                              int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
-                              unsigned flags, void* stream) {
+extern "C" int fdk_workspace_status(const void* workspace, int* status_host) {
+  FDK_CHECK_ARG(workspace != nullptr && status_host != nullptr, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CUDA(cudaMemcpy(status_host, (const int*)workspace + kStatusWord, sizeof(int), cudaMemcpyDeviceToHost));
+  return FDK_OK;
+}
+
+extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void* lut_host,
+                              void* out, int m, int n, int k, int bits, int dtype, void* workspace,
+                              size_t workspace_bytes, unsigned flags, void* stream) {
   FDK_CHECK_ARG(m > 0 && n > 0 && k > 0, FDK_ERR_BAD_ARG, "m=%d, n=%d, k=%d must be positive", m, n, k);
   FDK_CHECK_ARG(bits_supported(bits), FDK_ERR_SHAPE, "bits=%d not in {1,2,3,4,8}", bits);
   FDK_CHECK_ARG(k % kBlock == 0, FDK_ERR_SHAPE, "k=%d must be a multiple of 64", k);
-  FDK_CHECK_ARG(x && tiled && lut && out, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(x && tiled && (lut || lut_host) && out, FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(dtype == FDK_DTYPE_BF16 || dtype == FDK_DTYPE_F16, FDK_ERR_BAD_ARG, "dtype=%d", dtype);
   FDK_CHECK_ARG((flags & ~FDK_FLAG_PDL) == 0, FDK_ERR_BAD_ARG, "unknown flags 0x%x", flags);
   FDK_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)tiled & 15) == 0 && ((uintptr_t)lut & 15) == 0 &&
@@ -530,9 +933,8 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   if (int st = device_info(&di)) return st;
   FDK_CHECK_ARG(di.cc_major == 10, FDK_ERR_ARCH, "device has compute capability %d.%d", di.cc_major, di.cc_minor);
   const TiledDims d = tiled_dims(n, k, bits);
-  FDK_CHECK_ARG((size_t)d.row_tiles * sizeof(int) <= kCounterBytes, FDK_ERR_SHAPE, "n=%d exceeds %d rows", n,
-                (int)(kCounterBytes / sizeof(int)) * kTileRows);
-  const size_t need = kCounterBytes + (size_t)di.sm_count * 2 * 1024 * sizeof(float);
+  FDK_CHECK_ARG(d.row_tiles < kStatusWord, FDK_ERR_SHAPE, "n=%d exceeds %d rows", n, kStatusWord * kTileRows);
+  const size_t need = kCounterBytes + (size_t)di.sm_count * 1024 * sizeof(uint2);
   FDK_CHECK_ARG(workspace != nullptr && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
                 FDK_ERR_WORKSPACE, "workspace must be a 16-byte aligned buffer of at least %zu bytes", need);
 
@@ -540,7 +942,7 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   p.tiled = (const uint8_t*)tiled;
   p.lut = lut;
   p.counters = (int*)workspace;
-  p.partial = (float*)((uint8_t*)workspace + kCounterBytes);
+  p.partial = (uint2*)((uint8_t*)workspace + kCounterBytes);
   p.n = n;
   p.k = k;
   p.k_slabs = d.k_slabs;
@@ -548,17 +950,20 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   const int grid = p.total < di.sm_count ? p.total : di.sm_count;
   p.base = p.total / grid;
   p.rem = p.total % grid;
+#ifdef FDK_TRACE
+  p.trace = g_trace;
+#endif
   for (int m0 = 0; m0 < m; m0 += 16) {
     p.m = (m - m0) < 16 ? (m - m0) : 16;
     p.x = (const uint16_t*)x + (size_t)m0 * k;
     p.out = (uint16_t*)out + (size_t)m0 * n;
     int st;
     switch (bits) {
-      case 1: st = launch_bits<1>(p, grid, dtype, flags, (cudaStream_t)stream); break;
-      case 2: st = launch_bits<2>(p, grid, dtype, flags, (cudaStream_t)stream); break;
-      case 3: st = launch_bits<3>(p, grid, dtype, flags, (cudaStream_t)stream); break;
-      case 4: st = launch_bits<4>(p, grid, dtype, flags, (cudaStream_t)stream); break;
-      default: st = launch_bits<8>(p, grid, dtype, flags, (cudaStream_t)stream); break;
+      case 1: st = launch_bits<1>(p, lut_host, grid, dtype, flags, (cudaStream_t)stream); break;
+      case 2: st = launch_bits<2>(p, lut_host, grid, dtype, flags, (cudaStream_t)stream); break;
+      case 3: st = launch_bits<3>(p, lut_host, grid, dtype, flags, (cudaStream_t)stream); break;
+      case 4: st = launch_bits<4>(p, lut_host, grid, dtype, flags, (cudaStream_t)stream); break;
+      default: st = launch_bits<8>(p, lut_host, grid, dtype, flags, (cudaStream_t)stream); break;
     }
     if (st) return st;
   }

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from pathlib import Path
 
 import torch
@@ -41,9 +42,10 @@ _SIGNATURES = {
     "fdk_dequantise_tiled": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 2),
     "fdk_workspace_size": (ctypes.c_int, [ctypes.POINTER(ctypes.c_size_t)]),
     "fdk_workspace_init": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "fdk_workspace_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "fdk_linear_lut": (
         ctypes.c_int,
-        [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p],
+        [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p],
     ),
 }
 
@@ -172,15 +174,44 @@ def workspace(device: torch.device) -> Tensor:
     return ws
 
 
-def linear_lut(x: Tensor, tiled: Tensor, lut: Tensor, out: Tensor, n: int, k: int, bits: int, pdl: bool = False) -> None:
+def device_status(device: torch.device | None = None) -> int:
+    """Device-side status word of the current stream's workspace (synchronises)."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    out = ctypes.c_int(0)
+    check(lib().fdk_workspace_status(workspace(device).data_ptr(), ctypes.byref(out)))
+    return out.value
+
+
+_host_luts: dict[int, tuple[weakref.ref, int, bytes]] = {}
+
+
+def host_lut(lut: Tensor) -> bytes:
+    """Host copy of a lookup table, made once per tensor object and version: it rides along
+    with the launch parameters so that the kernel need not fetch the table from memory.
+    The first call for a table synchronises (device -> host copy)."""
+    key = id(lut)
+    hit = _host_luts.get(key)
+    if hit is not None and hit[0]() is lut and hit[1] == lut._version:
+        return hit[2]
+    data = lut.detach().contiguous().view(torch.int16).cpu().numpy().tobytes()
+    _host_luts[key] = (weakref.ref(lut, lambda _, k=key: _host_luts.pop(k, None)), lut._version, data)
+    return data
+
+
+def linear_lut(
+    x: Tensor, tiled: Tensor, lut: Tensor, out: Tensor, n: int, k: int, bits: int,
+    pdl: bool = False, lut_bytes: bytes | None = None,
+) -> None:
     """out[m, n] = x[m, k] @ W.T, W never materialised.  Writes `out` in place."""
     _require_cuda(x, tiled, lut, out)
     m = x.shape[0]
     ws = workspace(x.device)
+    if lut_bytes is None:
+        lut_bytes = host_lut(lut)
     with torch.cuda.device(x.device):
         check(
             lib().fdk_linear_lut(
-                x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), out.data_ptr(), m, n, k, bits,
+                x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), lut_bytes, out.data_ptr(), m, n, k, bits,
                 dtype_code(x.dtype), ws.data_ptr(), ws.numel(), FLAG_PDL if pdl else 0, _stream(),
             )
         )

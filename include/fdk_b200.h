@@ -98,25 +98,42 @@ int fdk_dequantise(const void* codes, const void* lut, const void* scale, int n,
 int fdk_dequantise_tiled(const void* tiled, const void* lut, int n, int k, int bits, int dtype,
                          void* w_out, void* stream);
 
-/* Scratch needed by fdk_linear_lut on the current device (split-K partial sums
- * and arrival counters).  One workspace per stream that runs the kernels
+/* Scratch needed by fdk_linear_lut on the current device (partial sums of row tiles
+ * whose K range is split over several SMs, and their use counts).  One workspace per stream that runs the kernels
  * concurrently.  Compare Marlin's `workspace` (src/fdk/marlin/__init__.py:37-51,
- * marlin_cuda.cpp:65-66): caller-allocated, zeroed once, left zeroed by every call. */
+ * marlin_cuda.cpp:65-66): caller-allocated, zeroed once (fdk_workspace_init), reusable
+ * by every later call on the same stream without clearing. */
 int fdk_workspace_size(size_t* bytes_host);
 
-/* Zeroes the arrival counters (cudaMemsetAsync).  Call once after allocating. */
+/* Zeroes the workspace (cudaMemsetAsync).  Call once after
+ * allocating.  The first call on a device also asks the device where kernels see their
+ * dynamic shared memory (one tiny kernel, synchronous), so make it outside any stream
+ * capture. */
 int fdk_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Reads the workspace's device-side status word (synchronous copy): 0 when every
+ * fdk_linear_lut that used the workspace ran normally; bit 0 = a bounded wait on a copy
+ * barrier ran out, bit 1 = the shared-memory layout planned by the host did not match the
+ * device.  The kernels never trap or spin without limit; this is where they report.
+ * No counterpart in the reference (its kernels have no device-side error reporting,
+ * cf. the soft handling in src/fdk/bench.py:457-458). */
+int fdk_workspace_status(const void* workspace, int* status_host);
 
 /* Fused dequantise + matrix product, out[m, n] = x[m, k] . W[n, k]^T with W as
  * fdk_dequantise defines it but never materialised; fp32 accumulation, block
  * scale applied to the fp32 block sum.  Replaces run_mv_lut (m == 1,
  * src/fdk/kernels.py:158-182) and run_mm_lut (m > 1, src/fdk/kernels.py:460-489).
- *   x    [m, k] row-major, 16-byte aligned rows (k % 8 == 0)
- *   out  [m, n] row-major
- *   m    >= 1; rows are processed 16 (bits..) at a time, any m is accepted.
+ *   x         [m, k] row-major, 16-byte aligned rows (k % 8 == 0)
+ *   lut       byte table in device memory ([256, 8/bits], or the 8-entry codebook
+ *             for bits == 3); may be NULL when lut_host is given
+ *   lut_host  optional HOST copy of the same table.  When given it is passed to the
+ *             kernel by value with the launch parameters, which saves the kernel a
+ *             memory round trip before it can start (the table is 16 B .. 4 KB)
+ *   out       [m, n] row-major
+ *   m         >= 1; batch rows are processed 16 at a time, any m is accepted.
  * Deterministic: the same inputs give the same bits on every call. */
-int fdk_linear_lut(const void* x, const void* tiled, const void* lut, void* out, int m, int n,
-                   int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
+int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
+                   int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
                    unsigned flags, void* stream);
 
 #ifdef __cplusplus

@@ -61,8 +61,8 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.fdk_tiled_size(64, 128, 4, None) == 1
     assert lib.fdk_repack(None, None, 64, 128, 4, 64, None, None) == 1
     assert lib.fdk_repack(None, None, 64, 128, 4, 32, None, None) == 2  # block size
-    assert lib.fdk_linear_lut(None, None, None, None, 1, 64, 128, 4, 0, None, 0, 0, None) == 1
-    assert lib.fdk_linear_lut(None, None, None, None, 1, 64, 128, 4, 0, None, 0, 8, None) == 1
+    assert lib.fdk_linear_lut(None, None, None, None, None, 1, 64, 128, 4, 0, None, 0, 0, None) == 1
+    assert lib.fdk_linear_lut(None, None, None, None, None, 1, 64, 128, 4, 0, None, 0, 8, None) == 1
     assert lib.fdk_workspace_init(None, 0, None) == 6
     with pytest.raises(native.FdkError) as e:
         native.check(lib.fdk_tiled_size(64, 100, 4, ctypes.byref(out)))
