@@ -239,7 +239,7 @@ def run_gpu_arm(args) -> None:
     with torch.cuda.stream(stream):
         def one_pass():
             for layer, x, out in zip(layers, xs, outs):
-                native.linear_lut(x, layer.tiled(), layer.lut, out, N, K, BITS)
+                native.linear_lut(x, layer.tiled(), layer.lut, out, N, K, BITS, pdl=True)
 
         one_pass()  # allocates this stream's workspace before capture
         torch.cuda.synchronize()
@@ -323,7 +323,7 @@ def run_gpu_arm(args) -> None:
             "data": "synthetic",
             "config": {
                 "workload": WORKLOAD,
-                "step": f"{COPIES} GEMV launches, one per weight set, one CUDA graph",
+                "step": f"{COPIES} GEMV launches, one per weight set, one CUDA graph, programmatic dependent launch",
                 "cache": f"inputs larger than L2: {COPIES} x {PACKED_BYTES} B of weights cycled",
                 "parallelism": "replicas" if world > 1 else "single",
             },

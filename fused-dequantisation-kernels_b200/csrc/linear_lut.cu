@@ -66,6 +66,9 @@ struct LinearParams {
   uint32_t stage_bytes;   // slab + this launch's x rows, rounded to 128
   uint32_t stages;        // ring stages per warp
   uint32_t slot_t;        // fragment column pairs kept per row in the reduction slots: ceil(min(m, 8) / 2)
+  uint32_t xres_addr;     // all of x staged once per CTA at this address (0: x rows come with each slab)
+  uint32_t xres_row;      // bytes between its rows
+  uint32_t xres_bar;      // barrier of that one copy
 #ifdef FDK_TRACE
   unsigned long long* trace;  // [grid][warps][8] cycle counts (development builds only)
 #endif
@@ -366,17 +369,28 @@ __device__ __noinline__ bool tile_finish(const LinearParams& p, float* slots, in
   uint2* mine = p.partial + (size_t)blockIdx.x * EMAX;
   bool ok = true;
 
-  // 1. add the warps' deposits in warp order; keep the sums in warp 0's block, or (not the
-  //    owner of a split tile) publish them as tagged words and be done
+  // 1. add the warps' deposits in a fixed order (even and odd warps in two chains, four
+  //    elements per lane in flight); keep the sums in warp 0's block, or (not the owner of a
+  //    split tile) publish them as tagged words and be done.  E is a multiple of 128.
 #pragma unroll 1
-  for (int e = lane; e < E; e += 32) {
-    float acc = 0.f;
-#pragma unroll 4
-    for (int w = 0; w < WARPS; ++w) acc += slots[w * E + e];
-    if (!full && !owner) {
-      st_relaxed_v2(mine + e, make_uint2(__float_as_uint(acc), tag));
-    } else {
-      slots[e] = acc;
+  for (int e0 = lane; e0 < E; e0 += 128) {
+    float even[4] = {0.f, 0.f, 0.f, 0.f}, odd[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+    for (int w = 0; w < WARPS; w += 2) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        even[j] += slots[w * E + e0 + 32 * j];
+        odd[j] += slots[(w + 1) * E + e0 + 32 * j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float acc = even[j] + odd[j];
+      if (!full && !owner) {
+        st_relaxed_v2(mine + e0 + 32 * j, make_uint2(__float_as_uint(acc), tag));
+      } else {
+        slots[e0 + 32 * j] = acc;
+      }
     }
   }
   if (!full && !owner) return true;
@@ -388,42 +402,53 @@ __device__ __noinline__ bool tile_finish(const LinearParams& p, float* slots, in
     const int last_item = seg_hi - 1;
     const int last = last_item < big ? last_item / (p.base + 1) : p.rem + (last_item - big) / p.base;
 #pragma unroll 1
-    for (int c = blockIdx.x + 1; c <= last; ++c) {
-      const uint2* theirs = p.partial + (size_t)c * EMAX;
+    for (int e0 = lane; e0 < E; e0 += 128) {        // four words per lane ...
 #pragma unroll 1
-      for (int e0 = lane; e0 < E; e0 += 128) {  // four words per lane in flight
-        uint2 v[4];
+      for (int cb = blockIdx.x + 1; cb <= last; cb += 4) {  // ... of up to four CTAs in flight
+        uint2 v[4][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int e = e0 + 32 * j;
-          v[j] = (e < E) ? ld_relaxed_v2(theirs + e) : make_uint2(0u, tag);
-        }
+        for (int ci = 0; ci < 4; ++ci)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int e = e0 + 32 * j;
-          uint32_t spins = 0;
-          while (v[j].y != tag) {
-            if (++spins > kSpinLimit) {
-              ok = false;
-              break;
+          for (int j = 0; j < 4; ++j)
+            v[ci][j] = (cb + ci <= last) ? ld_relaxed_v2(p.partial + (size_t)(cb + ci) * EMAX + e0 + 32 * j)
+                                         : make_uint2(0u, tag);
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t spins = 0;
+            while (v[ci][j].y != tag) {
+              if (++spins > kSpinLimit) {
+                ok = false;
+                break;
+              }
+              v[ci][j] = ld_relaxed_v2(p.partial + (size_t)(cb + ci) * EMAX + e0 + 32 * j);
             }
-            v[j] = ld_relaxed_v2(theirs + e);
           }
-          if (e < E) slots[e] += __uint_as_float(v[j].x);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // added in CTA order
+          float acc = slots[e0 + 32 * j];
+#pragma unroll
+          for (int ci = 0; ci < 4; ++ci) acc += __uint_as_float(v[ci][j].x);
+          slots[e0 + 32 * j] = acc;
         }
       }
     }
   }
 
-  // 3. write the outputs
+  // 3. write the outputs: element (blk, tq, lane) with blk = sub-tile * NB + n-tile
+  {
+    const int g = lane >> 2, c = lane & 3;
 #pragma unroll 1
-  for (int e = lane; e < E; e += 32) {
-    const int blk = e / sw, rem = e - blk * sw;       // blk = sub-tile * NB + n-tile
-    const int r = blk / NB, nb = blk - r * NB;
-    const int t = rem >> 5, g = (rem >> 2) & 7, c = rem & 3;
-    const int row = rt * kTileRows + 16 * r + g + 8 * (c >> 1);
-    const int b = 8 * nb + 2 * t + (c & 1);
-    if (row < p.n && b < p.m) p.out[(size_t)b * p.n + row] = from_float<FP16>(slots[e]);
+    for (int blk = 0; blk < kSubTiles * NB; ++blk) {
+      const int r = blk / NB, nb = blk - r * NB;
+      const int row = rt * kTileRows + 16 * r + g + 8 * (c >> 1);
+#pragma unroll 1
+      for (int tq = 0; tq < tt; ++tq) {
+        const int b = 8 * nb + 2 * tq + (c & 1);
+        if (row < p.n && b < p.m) p.out[(size_t)b * p.n + row] = from_float<FP16>(slots[blk * sw + tq * 32 + lane]);
+      }
+    }
   }
   if (!full) {
     __syncwarp();
@@ -466,6 +491,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
   if (threadIdx.x == 0) {
     esync->count[0] = esync->count[1] = 0;
     esync->gen[0] = esync->gen[1] = 0;
+    if (p.xres_addr) mbar_init(p.xres_bar, 1);
   }
   const uint32_t lane_base = p.table_addr + lane * T::kEntryBytes;
 
@@ -491,7 +517,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
   auto issue_weights = [&](int i, int kpos, int s) {
     const uint32_t bar = bar_addr(s);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                 "r"((uint32_t)L::kSlabBytes + (uint32_t)p.m * x_bytes(kpos))
+                 "r"((uint32_t)L::kSlabBytes + (p.xres_addr ? 0u : (uint32_t)p.m * x_bytes(kpos)))
                  : "memory");
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -501,7 +527,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
   };
   // lanes 0..m-1: one x row each, for the same slab
   auto issue_x = [&](int kpos, int s) {
-    if (lane < p.m) {
+    if (lane < p.m && p.xres_addr == 0) {
       asm volatile(
           "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
               stage_addr(s) + (uint32_t)L::kSlabBytes + lane * kXRow),
@@ -543,6 +569,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
   // everything above touched only weights; x, out and the workspace follow stream order
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __syncwarp();
+  if (p.xres_addr != 0 && warp == 0) {  // small x: one copy per batch row for the whole kernel
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(p.xres_bar),
+                   "r"((uint32_t)p.m * (uint32_t)p.k * 2u)
+                   : "memory");
+    }
+    __syncwarp();
+    if (lane < p.m) {
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+              p.xres_addr + lane * p.xres_row),
+          "l"(p.x + (size_t)lane * p.k), "r"((uint32_t)p.k * 2u), "r"(p.xres_bar)
+          : "memory");
+    }
+  }
   for (int s = 0; s < S && pf_it < c1; ++s) {
     issue_x(pf_ks, s);
     pf_advance();
@@ -627,7 +668,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
         const int b = min(g + 8 * nb, p.m - 1);  // lanes of unused batch columns read a live row
-        const uint32_t xa = sa + L::kSlabBytes + b * kXRow + JB * 128 + t * 32;
+        const uint32_t xa = p.xres_addr ? p.xres_addr + b * p.xres_row + (kpos * L::KSB + JB) * 128 + t * 32
+                                        : sa + L::kSlabBytes + b * kXRow + JB * 128 + t * 32;
         const uint4 lo = ring128(xa), hi = ring128(xa + 16);
         xb[nb][0] = lo.x; xb[nb][1] = lo.y; xb[nb][2] = lo.z; xb[nb][3] = lo.w;
         xb[nb][4] = hi.x; xb[nb][5] = hi.y; xb[nb][6] = hi.z; xb[nb][7] = hi.w;
@@ -672,6 +714,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
     }
   };
 
+  if (p.xres_addr != 0 && it < c1) {
+    if (!mbar_wait(p.xres_bar, 0)) timed_out = true;
+  }
   int s = 0;
   uint32_t parity = 0;
   while (it < c1) {
@@ -717,13 +762,16 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
 // ---- host side ----------------------------------------------------------------------
 constexpr size_t kCounterBytes = 16384;  // 4095 row-tile counters + 1 status word
 
-__global__ void probe_smem_base_kernel(uint32_t* out) {
+static __device__ uint32_t g_smem_probe;  // where the probe kernel leaves its answer
+
+__global__ void probe_smem_base_kernel() {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  *out = smem_addr(smem_raw);
+  g_smem_probe = smem_addr(smem_raw);
 }
 
 // Address, in the shared window, at which a kernel without static shared memory sees its
-// dynamic shared memory.  Asked of the device once (first call on a device synchronises).
+// dynamic shared memory.  Asked of the device once (the first call on a device runs a
+// one-thread kernel and synchronises); nothing is allocated.
 int dynamic_smem_base(uint32_t* out) {
   static uint32_t cache[64];
   static bool have[64] = {};
@@ -731,12 +779,9 @@ int dynamic_smem_base(uint32_t* out) {
   FDK_CUDA(cudaGetDevice(&dev));
   dev &= 63;
   if (!have[dev]) {
-    uint32_t* d = nullptr;
-    FDK_CUDA(cudaMalloc(&d, sizeof(uint32_t)));
-    probe_smem_base_kernel<<<1, 1, 1024>>>(d);
-    cudaError_t e = cudaMemcpy(&cache[dev], d, sizeof(uint32_t), cudaMemcpyDeviceToHost);
-    cudaFree(d);
-    FDK_CUDA(e);
+    probe_smem_base_kernel<<<1, 1, 1024>>>();
+    FDK_CUDA(cudaGetLastError());
+    FDK_CUDA(cudaMemcpyFromSymbol(&cache[dev], g_smem_probe, sizeof(uint32_t)));
     have[dev] = true;
   }
   *out = cache[dev];
@@ -754,15 +799,24 @@ size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
   const uint32_t n_stages = warps * stages;
   const uint32_t tt = ((p.m < 8 ? p.m : 8) + 1) / 2;
   const uint32_t slot_bytes = 2 * warps * kSubTiles * NB * 32 * tt * sizeof(float);  // two sets
-  const uint32_t mbar_bytes = align_up(n_stages * 8 + sizeof(EpilogueSync), 128);  // barriers + epilogue sync words
-  const uint32_t stage_bytes = align_up(L::kSlabBytes + p.m * (128 * L::KSB + kXRowPad), 128);
+  const uint32_t mbar_bytes = align_up(n_stages * 8 + 8 + sizeof(EpilogueSync), 128);  // barriers + epilogue sync words
+  // x small enough is staged whole, once per CTA; otherwise its rows travel with each slab
+  const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
+  const bool resident = (size_t)p.m * xres_row <= 36 * 1024;
+  const uint32_t xres_bytes = resident ? align_up(p.m * xres_row, 128) : 0;
+  const uint32_t stage_bytes =
+      align_up(L::kSlabBytes + (resident ? 0 : p.m * (128 * L::KSB + kXRowPad)), 128);
   p.stage_bytes = stage_bytes;
   p.stages = stages;
   p.slot_t = tt;
   uint32_t cursor = align_up(base, 128);
   p.smem_base = base;
   p.mbar_addr = cursor;
+  p.xres_bar = cursor + n_stages * 8 + sizeof(EpilogueSync);
   cursor += mbar_bytes;
+  p.xres_row = xres_row;
+  p.xres_addr = resident ? cursor : 0;
+  cursor += xres_bytes;
   if (T::kAligned64K) {
     const uint32_t table = align_up(cursor, 65536);
     p.table_addr = table;
