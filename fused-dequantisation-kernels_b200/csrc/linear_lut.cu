@@ -1023,3 +1023,39 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   }
   return FDK_OK;
 }
+
+// ---- entry point that allocates nothing ---------------------------------------------------
+// Some callers cannot give fdk_linear_lut a workspace because they cannot allocate device
+// memory at the point of the call: a plugin living inside a host runtime that owns every
+// device allocation, or code that runs while a stream capture is open in a mode that
+// forbids cudaMalloc.  For them the scratch lives in this library's own image: a file-scope
+// device array, sized for GPUs of up to kStaticMaxSms multiprocessors, that every GPU which
+// loads the library holds until the process exits.
+constexpr int kStaticMaxSms = 160;
+constexpr size_t kStaticScratchBytes = kCounterBytes + (size_t)kStaticMaxSms * 1024 * sizeof(uint2);  // 1,327,104
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+extern "C" int fdk_linear_lut_static(const void* x, const void* tiled, const void* lut, const void* lut_host,
+                                     void* out, int m, int n, int k, int bits, int dtype, unsigned flags,
+                                     void* stream) {
+  // In host code `g_static_scratch` is only a handle for the symbol; the kernel needs the
+  // array's address on the CURRENT device, looked up once per device.
+  static void* scratch_of_device[64] = {};
+  int dev = 0;
+  FDK_CUDA(cudaGetDevice(&dev));
+  FDK_CHECK_ARG(dev >= 0 && dev < 64, FDK_ERR_BAD_ARG, "device index %d out of range", dev);
+  if (scratch_of_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    FDK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    scratch_of_device[dev] = ptr;  // zero-filled when the module was loaded: nothing to clear
+  }
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  const size_t need = kCounterBytes + (size_t)di.sm_count * 1024 * sizeof(uint2);
+  FDK_CHECK_ARG(need <= kStaticScratchBytes, FDK_ERR_WORKSPACE,
+                "this GPU has %d multiprocessors and needs %zu bytes of scratch; the built-in scratch holds %zu "
+                "(up to %d multiprocessors): use fdk_linear_lut with a caller-allocated workspace",
+                di.sm_count, need, kStaticScratchBytes, kStaticMaxSms);
+  return fdk_linear_lut(x, tiled, lut, lut_host, out, m, n, k, bits, dtype, scratch_of_device[dev],
+                        kStaticScratchBytes, flags, stream);
+}

@@ -42,6 +42,10 @@ _SIGNATURES = {
     "fdk_dequantise_tiled": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 4 + [ctypes.c_void_p] * 2),
     "fdk_workspace_size": (ctypes.c_int, [ctypes.POINTER(ctypes.c_size_t)]),
     "fdk_workspace_init": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "fdk_linear_lut_static": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_uint, ctypes.c_void_p],
+    ),
     "fdk_workspace_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "fdk_linear_lut": (
         ctypes.c_int,

@@ -136,6 +136,25 @@ int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void
                    int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
                    unsigned flags, void* stream);
 
+/* fdk_linear_lut for callers that cannot allocate device memory where they call it -- a
+ * plugin inside a host runtime that owns all device allocations, or code running while a
+ * stream capture forbids cudaMalloc.  Same arguments and results as fdk_linear_lut minus the
+ * workspace: the scratch is an array inside the library image (1,327,104 bytes, enough for a
+ * GPU of up to 160 multiprocessors; a larger GPU is refused with FDK_ERR_WORKSPACE), held by
+ * every GPU that loads the library until the process exits.  The call itself allocates
+ * nothing, on the host or the device.
+ *   - The first call on a device looks up the array's device address and asks the device
+ *     where kernels see their shared memory (one one-thread kernel, synchronous): make that
+ *     first call before any stream capture.
+ *   - All calls on a device share the one array, so two calls that overlap on the GPU
+ *     (different streams, no ordering between them) race; serialise them or give the others
+ *     fdk_linear_lut with workspaces of their own.  Nothing needs clearing between calls:
+ *     the array starts zero-filled and every use of it is tagged.
+ * This entry point has no counterpart in the reference. */
+int fdk_linear_lut_static(const void* x, const void* tiled, const void* lut, const void* lut_host,
+                          void* out, int m, int n, int k, int bits, int dtype, unsigned flags,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif

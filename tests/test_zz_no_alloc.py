@@ -1,0 +1,51 @@
+"""The allocation-free entry point, fdk_linear_lut_static, against fdk_linear_lut.
+
+It exists for callers that cannot allocate device memory where they call the library (a
+plugin whose host runtime owns every allocation, code inside a stream capture that forbids
+cudaMalloc): its scratch is an array inside the library image instead of a caller-provided
+workspace.  Everything else is the same kernel, so the outputs must agree bit for bit --
+on a first call, and on a second one that finds the array as the first call left it.
+
+Collected last (file name) so that a run that stops at the first failure has already run
+every other test; it passes alone in a fresh process as well as after the others.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import from_bits, random_problem, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _call_static(native, x, tiled, lut, out, n, k, bits):
+    lib = native.lib()
+    native.check(
+        lib.fdk_linear_lut_static(
+            x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), native.host_lut(lut), out.data_ptr(),
+            x.shape[0], n, k, bits, native.dtype_code(x.dtype), 0, torch.cuda.current_stream().cuda_stream,
+        )
+    )
+
+
+@pytest.mark.parametrize("bits,m,n,k", [(4, 1, 4096, 4096), (2, 5, 1024, 768), (4, 16, 200, 4096)])
+def test_static_scratch_entry_matches_workspace_entry(bits, m, n, k):
+    from fdk import native
+
+    native.lib()
+    codes, lut, scale, x = random_problem(n, k, bits, m, seed=17 + bits + m)
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
+    d_x, d_lut = from_bits(x), from_bits(lut)
+
+    expected = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    native.linear_lut(d_x, tiled, d_lut, expected, n, k, bits)
+    torch.cuda.synchronize()
+
+    for call in range(2):  # the second call reuses the array exactly as the first left it
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        before = torch.cuda.memory_allocated()
+        _call_static(native, d_x, tiled, d_lut, out, n, k, bits)
+        assert torch.cuda.memory_allocated() == before  # nothing went through torch's allocator either
+        torch.cuda.synchronize()
+        assert np.array_equal(to_bits(out), to_bits(expected)), f"call {call}"
