@@ -1,0 +1,264 @@
+"""Custom-llama decode loop on the native kernels, single GPU or tensor parallel.
+
+The reference benchmarks decode by wrapping transformers' LlamaForCausalLM in a greedy
+`Generator` (prefill once, then one captured decode step per token; src/fdk/models.py:225-340)
+and replacing its nn.Linear layers with quantised ones.  This module is that decode step
+written out -- embedding, [RMSNorm, fused q|k|v projection, rotary + KV append, attention,
+o projection, RMSNorm, fused gate|up projection, SiLU*up, down projection] x layers, final
+norm, lm_head (left in bf16, as the reference's default `skip="^lm_head$"` does), argmax --
+with every projection a `QuantisedLinear` running libfdk_b200's fused kernel (or a bf16
+`nn.Linear` for the 16-bit baseline) and the glue in three fused CUDA kernels.  Attention
+over the static KV cache uses torch's scaled_dot_product_attention.
+
+Tensor parallelism (not in the reference, which is single-GPU): Megatron-style.  q|k|v and
+gate|up are split by output rows (whole heads), o and down by input columns; block scales run
+along K inside a row, so sharding the bf16 weight and then quantising equals quantising and
+then sharding.  One NCCL all-reduce of the [batch, hidden] bf16 activation follows o and down.
+Embedding, norms and lm_head are replicated.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+from . import native
+from .models import LlamaDims, QuantisationConfig, QuantisedLinear
+
+
+@dataclass
+class TensorParallel:
+    rank: int = 0
+    size: int = 1
+    group: "dist.ProcessGroup | None" = None
+
+    def all_reduce(self, t: Tensor) -> None:
+        if self.size > 1:
+            dist.all_reduce(t, group=self.group)
+
+
+def shard_rows(n: int, tp: TensorParallel) -> slice:
+    assert n % tp.size == 0, f"{n} rows do not split over {tp.size} ranks"
+    per = n // tp.size
+    return slice(tp.rank * per, (tp.rank + 1) * per)
+
+
+def shard_columns(k: int, tp: TensorParallel) -> slice:
+    assert k % (64 * tp.size) == 0, f"{k} columns do not split over {tp.size} ranks in multiples of 64"
+    per = k // tp.size
+    return slice(tp.rank * per, (tp.rank + 1) * per)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, qkv: nn.Module, o: nn.Module, gate_up: nn.Module, down: nn.Module,
+                 input_norm: Tensor, post_norm: Tensor):
+        super().__init__()
+        self.qkv, self.o, self.gate_up, self.down = qkv, o, gate_up, down
+        self.input_norm = nn.Parameter(input_norm, requires_grad=False)
+        self.post_norm = nn.Parameter(post_norm, requires_grad=False)
+
+
+def _make_linear(weight: Tensor, config: QuantisationConfig | None, lut: Tensor | None) -> nn.Module:
+    """weight [N, K] bf16 on the device -> QuantisedLinear (config) or nn.Linear (16-bit baseline)."""
+    if config is None:
+        layer = nn.Linear(weight.shape[1], weight.shape[0], bias=False, device=weight.device, dtype=weight.dtype)
+        layer.weight = nn.Parameter(weight, requires_grad=False)
+        return layer
+    layer = QuantisedLinear.create(weight, config, lut=lut)
+    if config.kernel != "torch.compile":
+        layer.tiled()
+    return layer
+
+
+class LlamaDecoder(nn.Module):
+    """Decode-only Llama.  Build with `random_init` (synthetic weights created shard by shard on
+    the device) or `from_hf` (weights of a transformers LlamaForCausalLM)."""
+
+    def __init__(self, dims: LlamaDims, layers: list[DecoderLayer], embed: Tensor, final_norm: Tensor,
+                 lm_head: Tensor, tp: TensorParallel):
+        super().__init__()
+        self.dims, self.tp = dims, tp
+        self.layers = nn.ModuleList(layers)
+        self.embed = nn.Embedding.from_pretrained(embed, freeze=True)
+        self.final_norm = nn.Parameter(final_norm, requires_grad=False)
+        self.lm_head = nn.Linear(dims.hidden_size, dims.vocab_size, bias=False, device=embed.device, dtype=embed.dtype)
+        self.lm_head.weight = nn.Parameter(lm_head, requires_grad=False)
+        self.q_heads = dims.num_attention_heads // tp.size
+        self.kv_heads = dims.num_key_value_heads // tp.size
+        assert dims.num_key_value_heads % tp.size == 0, "KV heads must split evenly over the ranks"
+        assert dims.head_dim == 128
+
+    # ---- construction -----------------------------------------------------------------
+
+    @staticmethod
+    def _shard_layer_weights(q, k, v, o, gate, up, down, dims: LlamaDims, tp: TensorParallel):
+        d = dims.head_dim
+        qs = shard_rows(dims.num_attention_heads, tp)
+        ks = shard_rows(dims.num_key_value_heads, tp)
+        qkv = torch.cat([q[qs.start * d: qs.stop * d], k[ks.start * d: ks.stop * d], v[ks.start * d: ks.stop * d]])
+        fs = shard_rows(dims.intermediate_size, tp)
+        gate_up = torch.cat([gate[fs], up[fs]])
+        o_s = o[:, qs.start * d: qs.stop * d].contiguous()
+        down_s = down[:, fs].contiguous()
+        return qkv, o_s, gate_up, down_s
+
+    @classmethod
+    def random_init(cls, dims: LlamaDims, config: QuantisationConfig | None, device: torch.device,
+                    tp: TensorParallel | None = None, seed: int = 0, lut: Tensor | None = None,
+                    std: float = 0.02) -> "LlamaDecoder":
+        """Random bf16 weights ~ N(0, std^2), generated per layer on the device with a seed that
+        does not depend on the rank (every rank draws the full matrix and keeps its shard)."""
+        tp = tp or TensorParallel()
+        gen = torch.Generator(device=device).manual_seed(seed)
+        h, f, d = dims.hidden_size, dims.intermediate_size, dims.head_dim
+
+        def draw(n, k):
+            return (torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * std).bfloat16()
+
+        layers = []
+        for _ in range(dims.num_hidden_layers):
+            q, k, v = draw(dims.num_attention_heads * d, h), draw(dims.num_key_value_heads * d, h), draw(dims.num_key_value_heads * d, h)
+            o = draw(h, dims.num_attention_heads * d)
+            gate, up, down = draw(f, h), draw(f, h), draw(h, f)
+            qkv_w, o_w, gu_w, down_w = cls._shard_layer_weights(q, k, v, o, gate, up, down, dims, tp)
+            del q, k, v, o, gate, up, down
+            ones = torch.ones(h, device=device, dtype=torch.bfloat16)
+            layers.append(DecoderLayer(
+                _make_linear(qkv_w, config, lut), _make_linear(o_w, config, lut),
+                _make_linear(gu_w, config, lut), _make_linear(down_w, config, lut), ones, ones.clone(),
+            ))
+        embed = draw(dims.vocab_size, h)
+        lm_head = draw(dims.vocab_size, h)
+        return cls(dims, layers, embed, torch.ones(h, device=device, dtype=torch.bfloat16), lm_head, tp)
+
+    @classmethod
+    def from_hf(cls, model, config: QuantisationConfig | None, device: torch.device,
+                tp: TensorParallel | None = None, lut: Tensor | None = None) -> "LlamaDecoder":
+        """Takes the weights of a transformers LlamaForCausalLM (any float dtype)."""
+        tp = tp or TensorParallel()
+        c = model.config
+        dims = LlamaDims(
+            name=getattr(c, "_name_or_path", "llama"), hidden_size=c.hidden_size, num_hidden_layers=c.num_hidden_layers,
+            num_attention_heads=c.num_attention_heads, num_key_value_heads=c.num_key_value_heads,
+            intermediate_size=c.intermediate_size, vocab_size=c.vocab_size,
+            head_dim=getattr(c, "head_dim", None) or c.hidden_size // c.num_attention_heads,
+            rope_theta=float(getattr(c, "rope_theta", None) or c.rope_parameters["rope_theta"]),
+            rms_norm_eps=c.rms_norm_eps,
+        )
+
+        def w(t):
+            return t.detach().to(device=device, dtype=torch.bfloat16)
+
+        layers = []
+        for hl in model.model.layers:
+            a, m = hl.self_attn, hl.mlp
+            qkv_w, o_w, gu_w, down_w = cls._shard_layer_weights(
+                w(a.q_proj.weight), w(a.k_proj.weight), w(a.v_proj.weight), w(a.o_proj.weight),
+                w(m.gate_proj.weight), w(m.up_proj.weight), w(m.down_proj.weight), dims, tp,
+            )
+            layers.append(DecoderLayer(
+                _make_linear(qkv_w, config, lut), _make_linear(o_w, config, lut),
+                _make_linear(gu_w, config, lut), _make_linear(down_w, config, lut),
+                w(hl.input_layernorm.weight), w(hl.post_attention_layernorm.weight),
+            ))
+        return cls(dims, layers, w(model.model.embed_tokens.weight), w(model.model.norm.weight), w(model.lm_head.weight), tp)
+
+    # ---- decode state -----------------------------------------------------------------
+
+    def allocate(self, batch: int, max_len: int) -> None:
+        """Static KV caches [layer][batch, kv_heads, max_len, 128] and activation buffers."""
+        dev, dt = self.final_norm.device, torch.bfloat16
+        h, f = self.dims.hidden_size, self.dims.intermediate_size // self.tp.size
+        self.batch, self.max_len = batch, max_len
+        self.k_cache = [torch.zeros((batch, self.kv_heads, max_len, 128), device=dev, dtype=dt) for _ in self.layers]
+        self.v_cache = [torch.zeros((batch, self.kv_heads, max_len, 128), device=dev, dtype=dt) for _ in self.layers]
+        self.hidden = torch.empty((batch, h), device=dev, dtype=dt)
+        self.normed = torch.empty((batch, h), device=dev, dtype=dt)
+        self.q = torch.empty((batch, self.q_heads * 128), device=dev, dtype=dt)
+        self.act = torch.empty((batch, f), device=dev, dtype=dt)
+        self.position = torch.zeros((), device=dev, dtype=torch.int64)
+        self.key_mask = torch.zeros((1, 1, 1, max_len), device=dev, dtype=torch.bool)
+
+    def fill_cache_synthetic(self, context: int, seed: int = 1) -> None:
+        """Benchmark aid: pretend `context` tokens have been decoded (random keys and values)."""
+        gen = torch.Generator(device=self.hidden.device).manual_seed(seed + self.tp.rank)
+        for kc, vc in zip(self.k_cache, self.v_cache):
+            kc[:, :, :context].copy_(torch.randn(kc[:, :, :context].shape, generator=gen, device=kc.device, dtype=torch.float32))
+            vc[:, :, :context].copy_(torch.randn(vc[:, :, :context].shape, generator=gen, device=vc.device, dtype=torch.float32))
+        self.position.fill_(context)
+        self.key_mask.zero_()
+        self.key_mask[..., :context] = True
+
+    # ---- one decode step --------------------------------------------------------------
+
+    def forward(self, tokens: Tensor) -> Tensor:
+        """tokens [batch] int64 at position `self.position` -> logits [batch, vocab]; advances the
+        position.  No host synchronisation, fixed shapes: capturable in a CUDA graph."""
+        dims, eps = self.dims, self.dims.rms_norm_eps
+        self.key_mask.view(-1).index_fill_(0, self.position.view(1), True)
+        torch.index_select(self.embed.weight, 0, tokens, out=self.hidden)
+        delta = None
+        for i, layer in enumerate(self.layers):
+            native.rmsnorm(self.hidden, delta, layer.input_norm, self.normed, eps)
+            qkv = layer.qkv(self.normed)
+            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads, dims.rope_theta)
+            attn = torch.nn.functional.scaled_dot_product_attention(
+                self.q.view(self.batch, self.q_heads, 1, 128), self.k_cache[i], self.v_cache[i],
+                attn_mask=self.key_mask, enable_gqa=True,
+            )
+            delta = layer.o(attn.view(self.batch, self.q_heads * 128))
+            self.tp.all_reduce(delta)
+            native.rmsnorm(self.hidden, delta, layer.post_norm, self.normed, eps)
+            gate_up = layer.gate_up(self.normed)
+            native.silu_mul(gate_up, self.act)
+            delta = layer.down(self.act)
+            self.tp.all_reduce(delta)
+        native.rmsnorm(self.hidden, delta, self.final_norm, self.normed, eps)
+        logits = self.lm_head(self.normed)
+        self.position += 1
+        return logits
+
+
+class Generator:
+    """Greedy decoding with the reference Generator's interface (src/fdk/models.py:225-259):
+    construct with a prompt (prefilled token by token through the decode step), call step() per
+    generated token, read `tokens`.  step() is capturable in a CUDA graph."""
+
+    def __init__(self, model: LlamaDecoder, prompt_ids: Tensor, steps: int, synthetic_context: int | None = None) -> None:
+        batch_size, prompt_n = prompt_ids.shape
+        context = prompt_n if synthetic_context is None else synthetic_context
+        max_length = context + steps + 1
+        self.model = model
+        device = model.final_norm.device
+        model.allocate(batch_size, max_length)
+        self.input_ids = torch.zeros((batch_size, max_length), dtype=torch.long, device=device)
+        with torch.no_grad():
+            if synthetic_context is None:
+                self.input_ids[:, :prompt_n] = prompt_ids
+                logits = None
+                for t in range(prompt_n):
+                    logits = model(self.input_ids[:, t].contiguous())
+            else:  # keys and values of a made-up context; only the last prompt token is run
+                self.input_ids[:, context - 1] = prompt_ids[:, -1]
+                model.fill_cache_synthetic(context - 1)
+                logits = model(self.input_ids[:, context - 1].contiguous())
+            self.last_token = logits.argmax(dim=-1)
+            self.input_ids[:, context] = self.last_token
+        self.last_index = torch.tensor(context, device=device)
+        self.last_logits = logits
+
+    def step(self) -> None:
+        with torch.no_grad():
+            logits = self.model(self.last_token)
+            self.last_logits = logits
+            self.last_token[...] = logits.argmax(dim=-1)
+            self.last_index += 1
+            token = self.last_token[:, None]
+            self.input_ids.scatter_(1, self.last_index[None, None].expand_as(token), token)
+
+    @property
+    def tokens(self) -> Tensor:
+        return self.input_ids[:, : self.last_index + 1]

@@ -322,3 +322,117 @@ def _quantisation_configs(
                 for kernel in kernels_:
                     if not (kernel.startswith("marlin") and b != 4):
                         yield QuantisationConfig(bits=b, block_size=block_size, kernel=kernel, skip=skip)
+
+
+# Decode benchmark (the reference's `benchmark` / `run_benchmark` / `_main`, models.py:313-605,
+# on the native decode loop of fdk.llama; random token ids stand in for the tokenizer, which
+# needs a gated download)
+
+
+@dataclass
+class BenchmarkSettings:
+    model: str
+    batch_size: int
+    quantisation: QuantisationConfig | None
+    reps: int
+    context: int = 2
+    tp: int = 1
+
+    def __str__(self) -> str:
+        q = (
+            f"b={self.quantisation.block_size} {self.quantisation.bits}-bit {self.quantisation.kernel}"
+            if self.quantisation is not None
+            else "16-bit"
+        )
+        return f"{self.model} batch={self.batch_size} ctx={self.context} tp={self.tp} {q}"
+
+
+def benchmark(model: nn.Module, batch_size: int, reps: int, context: int = 2, seed: int = 0) -> Result:
+    """Seconds per decode step of `model` (an fdk.llama.LlamaDecoder): one step per CUDA-graph
+    replay, `reps` replays, as the reference does; `context` tokens of synthetic KV cache."""
+    from . import bench, llama
+
+    device = model.final_norm.device
+    gen = torch.Generator(device=device).manual_seed(seed)
+    prompt_ids = torch.randint(0, model.dims.vocab_size, (batch_size, 1), generator=gen, device=device)
+    with torch.no_grad():
+        generator = llama.Generator(model, prompt_ids, reps + 4, synthetic_context=max(context, 1))
+        avg_time, avg_time_stderr = bench.measure_time(lambda _: generator.step(), inner_reps=1, outer_reps=reps)
+    return Result(
+        batch_size=batch_size,
+        bytes_rw=count_parameter_read_bytes(model),
+        ops=batch_size * count_ops(model),
+        avg_time=avg_time,
+        avg_time_stderr=avg_time_stderr,
+        output=[],
+    )
+
+
+def resolve_model_dims(name: str) -> LlamaDims:
+    """'custom-llama-4B' (reference shapes) or 'custom-llama-b200-4B' (the B200 measurement shapes)."""
+    assert name.startswith("custom-llama-"), f"only custom-llama-* models are built offline, got {name}"
+    return get_custom_llama_dims(name.replace("custom-llama-", ""))
+
+
+def _main() -> None:
+    import argparse
+    import os
+
+    import torch.distributed as dist
+
+    from . import bench, llama
+
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--model", default=["custom-llama-4B"], nargs="+",
+                        help=f"custom-llama-<size>, sizes {list(custom_llama_configs) + list(b200_llama_configs)}")
+    parser.add_argument("--batch-size", default=[1], type=int, nargs="+", help="Generation batch sizes")
+    parser.add_argument("--bits", default=[16, 4, 1], type=int, nargs="+", help="Quantisation bit widths")
+    parser.add_argument("--skip", default="^lm_head$", help="Regex of parameters to skip during quantisation")
+    parser.add_argument("--block-size", default=[64], type=int, nargs="+", help="Quantisation block sizes")
+    parser.add_argument("--kernel", default=["triton"], choices=["triton", "torch.compile", "marlin", "marlin-lut"],
+                        nargs="+", help="Kernel implementation(s) (ignored for 16-bit)")
+    parser.add_argument("--reps", type=int, default=100, help="Number of generation steps to measure")
+    parser.add_argument("--context", type=int, default=2, help="Tokens already in the KV cache")
+    args = parser.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    tp = llama.TensorParallel(rank, world, None)
+
+    log = bench.Log("models") if rank == 0 else None
+    for name in args.model:
+        dims = resolve_model_dims(name)
+        for batch_size in args.batch_size:
+            for config in _quantisation_configs(args.bits, args.block_size, args.kernel, args.skip):
+                if config is not None and config.kernel.startswith("marlin"):
+                    continue  # fp16 selectors are exercised at layer level, the decode loop is bf16
+                settings = BenchmarkSettings(name, batch_size, config, args.reps, args.context, world)
+                out = dict(**settings.__dict__)
+                if config is not None:
+                    out.update(config.__dict__)
+                del out["quantisation"]
+                try:
+                    model = llama.LlamaDecoder.random_init(dims, config, device, tp)
+                    result = benchmark(model, batch_size, args.reps, args.context)
+                    out.update(result.__dict__)
+                    if rank == 0:
+                        print(f"{str(settings):>60}:  {result}", file=sys.stderr)
+                    del model
+                except Exception as e:  # as the reference: log and carry on
+                    out.update(error=repr(e))
+                    if rank == 0:
+                        print(f"{str(settings):>60}:  ERROR {e}", file=sys.stderr)
+                torch.cuda.empty_cache()
+                if log is not None:
+                    log(out)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    _main()

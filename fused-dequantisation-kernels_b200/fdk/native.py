@@ -46,6 +46,9 @@ _SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_uint, ctypes.c_void_p],
     ),
+    "fdk_rmsnorm": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 2 + [ctypes.c_float, ctypes.c_void_p]),
+    "fdk_rope_append": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_void_p]),
+    "fdk_silu_mul": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 2 + [ctypes.c_void_p]),
     "fdk_workspace_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "fdk_linear_lut": (
         ctypes.c_int,
@@ -219,3 +222,40 @@ def linear_lut(
                 dtype_code(x.dtype), ws.data_ptr(), ws.numel(), FLAG_PDL if pdl else 0, _stream(),
             )
         )
+
+
+def rmsnorm(h: Tensor, delta: Tensor | None, weight: Tensor, out: Tensor, eps: float) -> None:
+    """h += delta (when given, in place), out = RMSNorm(h) * weight.  bf16 [rows, width]."""
+    _require_cuda(h, weight, out)
+    rows, width = h.shape
+    with torch.cuda.device(h.device):
+        check(
+            lib().fdk_rmsnorm(
+                h.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                rows, width, eps, _stream(),
+            )
+        )
+
+
+def rope_append(
+    qkv: Tensor, pos: Tensor, q_out: Tensor, k_cache: Tensor, v_cache: Tensor,
+    q_heads: int, kv_heads: int, theta: float,
+) -> None:
+    """Rotary embedding of the fused q|k|v projection at position `pos` (device int64 scalar),
+    k and v appended to the caches [rows, kv_heads, max_len, 128]."""
+    _require_cuda(qkv, pos, q_out, k_cache, v_cache)
+    assert pos.dtype == torch.int64
+    with torch.cuda.device(qkv.device):
+        check(
+            lib().fdk_rope_append(
+                qkv.data_ptr(), pos.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                qkv.shape[0], q_heads, kv_heads, 128, k_cache.shape[2], theta, _stream(),
+            )
+        )
+
+
+def silu_mul(gate_up: Tensor, out: Tensor) -> None:
+    _require_cuda(gate_up, out)
+    rows, width = out.shape
+    with torch.cuda.device(out.device):
+        check(lib().fdk_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, width, _stream()))

@@ -136,6 +136,29 @@ int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void
                    int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
                    unsigned flags, void* stream);
 
+/* ---- glue of the decode step around the quantised projections ------------------------
+ * The reference takes this arithmetic from transformers' LlamaForCausalLM, called from
+ * Generator.step (src/fdk/models.py:245-255); these three kernels replace about ten
+ * framework launches per layer.  bf16 only. */
+
+/* Residual add fused with RMSNorm: if delta != NULL, h[rows, width] += delta (bf16 add, in
+ * place); then out = weight * bf16(h * rsqrt(mean(h^2) + eps)) computed in fp32. */
+int fdk_rmsnorm(void* h, const void* delta, const void* weight, void* out, int rows, int width,
+                float eps, void* stream);
+
+/* Rotary embedding fused with the KV-cache append.  qkv [rows, (q_heads + 2 kv_heads) * 128] is
+ * the output of the fused q|k|v projection; *pos (device int64) is the token position.  q is
+ * rotated into q_out [rows, q_heads * 128]; k is rotated and v copied into k_cache / v_cache
+ * [rows, kv_heads, max_len, 128] at position *pos.  Rotate-half convention, cos/sin rounded to
+ * bf16 as the framework model does.  head_dim must be 128. */
+int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache,
+                    int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
+                    void* stream);
+
+/* out[rows, width] = silu(gate_up[:, :width]) * gate_up[:, width:], gate_up [rows, 2 width] being
+ * the output of the fused gate|up projection. */
+int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, void* stream);
+
 /* fdk_linear_lut for callers that cannot allocate device memory where they call it -- a
  * plugin inside a host runtime that owns all device allocations, or code running while a
  * stream capture forbids cudaMalloc.  Same arguments and results as fdk_linear_lut minus the
