@@ -11,6 +11,30 @@
 namespace fdk {
 namespace {
 
+// Every kernel here is launched with programmatic stream serialisation: it lets the next
+// kernel on the stream be scheduled at once, and itself waits for the previous kernel before
+// touching memory.  This only hides launch latency; ordering is that of the stream.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <class... KArgs, class... Args>
+int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FDK_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+  return FDK_OK;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -24,6 +48,7 @@ __global__ void rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restr
                                float eps) {
   extern __shared__ float row_cache[];  // width floats
   __shared__ float partial[32];
+  pdl_prologue();
   const int row = blockIdx.x;
   uint16_t* hr = h + (size_t)row * width;
   const uint16_t* dr = delta ? delta + (size_t)row * width : nullptr;
@@ -84,6 +109,7 @@ __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long 
                                    uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
                                    uint16_t* __restrict__ v_cache, int q_heads, int kv_heads, int max_len,
                                    float theta) {
+  pdl_prologue();
   const int row = blockIdx.y, head = blockIdx.x, i = threadIdx.x;  // i in 0..63: the pair (i, i + 64)
   const long long pos = *pos_ptr;
   const int heads_total = q_heads + 2 * kv_heads;
@@ -117,6 +143,7 @@ __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long 
 // out[row, j] = silu(gate_up[row, j]) * gate_up[row, width + j]
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out, int width,
                                 long long total) {
+  pdl_prologue();
   for (long long idx = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; idx < total;
        idx += (long long)gridDim.x * blockDim.x * 8) {
     const long long row = idx / width;
@@ -161,10 +188,8 @@ extern "C" int fdk_rmsnorm(void* h, const void* delta, const void* weight, void*
       configured[dev & 63] = true;
     }
   }
-  rmsnorm_kernel<<<rows, 256, smem, (cudaStream_t)stream>>>((uint16_t*)h, (const uint16_t*)delta,
-                                                             (const uint16_t*)weight, (uint16_t*)out, width, eps);
-  FDK_CUDA(cudaGetLastError());
-  return FDK_OK;
+  return launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream, (uint16_t*)h,
+                    (const uint16_t*)delta, (const uint16_t*)weight, (uint16_t*)out, width, eps);
 }
 
 extern "C" int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache,
@@ -174,11 +199,9 @@ extern "C" int fdk_rope_append(const void* qkv, const void* pos, void* q_out, vo
   FDK_CHECK_ARG(head_dim == 128, FDK_ERR_SHAPE, "head_dim=%d: only 128 is supported", head_dim);
   FDK_CHECK_ARG(rows > 0 && q_heads > 0 && kv_heads > 0 && max_len > 0, FDK_ERR_BAD_ARG, "non-positive size");
   dim3 grid(q_heads + 2 * kv_heads, rows);
-  rope_append_kernel<<<grid, 64, 0, (cudaStream_t)stream>>>((const uint16_t*)qkv, (const long long*)pos,
-                                                            (uint16_t*)q_out, (uint16_t*)k_cache,
-                                                            (uint16_t*)v_cache, q_heads, kv_heads, max_len, theta);
-  FDK_CUDA(cudaGetLastError());
-  return FDK_OK;
+  return launch_pdl(rope_append_kernel, grid, dim3(64), 0, (cudaStream_t)stream, (const uint16_t*)qkv,
+                    (const long long*)pos, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache, q_heads,
+                    kv_heads, max_len, theta);
 }
 
 extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, void* stream) {
@@ -188,7 +211,228 @@ extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width,
   const long long total = (long long)rows * width;
   long long blocks = (total / 8 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  silu_mul_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)gate_up, (uint16_t*)out, width, total);
-  FDK_CUDA(cudaGetLastError());
+  return launch_pdl(silu_mul_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream,
+                    (const uint16_t*)gate_up, (uint16_t*)out, width, total);
+}
+
+// ---- decode attention over the static KV cache ----------------------------------------------
+// One query token per batch row, grouped-query attention, head_dim 128, bf16 cache
+// [batch, kv_heads, max_len, 128].  Grid (splits, kv_heads, batch): a CTA of 4 warps takes one
+// slice of the context for all the query heads that share a KV head (so every key/value byte
+// is read once), keeps a running softmax per head, and leaves {max, sum, 128 weighted values}
+// per head in scratch; the last CTA of a (batch, kv head) to finish merges the slices and
+// writes the bf16 output.  HBM-bound at large batch (2 x 256 B per position per KV head).
+namespace fdk {
+namespace {
+
+constexpr int kAttnWarps = 8;
+constexpr int kMaxSplits = 64;
+constexpr int kMaxGroup = 8;
+
+template <int G>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+    decode_attention_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
+                            const uint16_t* __restrict__ v_cache, const long long* __restrict__ pos_ptr,
+                            uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
+                            int q_heads, int kv_heads, int max_len, int chunk) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float part[kAttnWarps][G][132];
+  __shared__ int is_last;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int len = (int)(*pos_ptr) + 1;  // the current token's key and value are already in the cache
+  const int p0 = split * chunk, p1 = min(len, p0 + chunk);
+
+  float qf[G][4], acc[G][4], mx[G], sum[G];
+  const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
+#pragma unroll
+  for (int j = 0; j < G; ++j) {
+    const uint2 qq = *reinterpret_cast<const uint2*>(q + ((size_t)b * q_heads + kvh * G + j) * 128 + lane * 4);
+    qf[j][0] = pair_lo<false>(qq.x) * scale; qf[j][1] = pair_hi<false>(qq.x) * scale;
+    qf[j][2] = pair_lo<false>(qq.y) * scale; qf[j][3] = pair_hi<false>(qq.y) * scale;
+    acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    mx[j] = -INFINITY;
+    sum[j] = 0.f;
+  }
+  const uint16_t* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
+  const uint16_t* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
+  // four positions per warp and iteration: their eight loads are in flight together
+  for (int pb = p0 + warp * 4; pb < p1; pb += kAttnWarps * 4) {
+    uint2 kk[4], vv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int p = min(pb + u, p1 - 1);  // clamped reads, masked below
+      kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
+      vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
+    }
+    float s[4][G];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float k0 = pair_lo<false>(kk[u].x), k1 = pair_hi<false>(kk[u].x), k2 = pair_lo<false>(kk[u].y), k3 = pair_hi<false>(kk[u].y);
+#pragma unroll
+      for (int j = 0; j < G; ++j) s[u][j] = qf[j][0] * k0 + qf[j][1] * k1 + qf[j][2] * k2 + qf[j][3] * k3;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < G; ++j) s[u][j] += __shfl_xor_sync(0xffffffffu, s[u][j], o);
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      float m_new = mx[j];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (pb + u >= p1) s[u][j] = -INFINITY;
+        m_new = fmaxf(m_new, s[u][j]);
+      }
+      const float corr = __expf(mx[j] - m_new);
+      mx[j] = m_new;
+      float l = sum[j] * corr, a0 = acc[j][0] * corr, a1 = acc[j][1] * corr, a2 = acc[j][2] * corr, a3 = acc[j][3] * corr;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float w = __expf(s[u][j] - m_new);  // exp(-inf) = 0 for masked positions
+        l += w;
+        a0 += w * pair_lo<false>(vv[u].x);
+        a1 += w * pair_hi<false>(vv[u].x);
+        a2 += w * pair_lo<false>(vv[u].y);
+        a3 += w * pair_hi<false>(vv[u].y);
+      }
+      sum[j] = l; acc[j][0] = a0; acc[j][1] = a1; acc[j][2] = a2; acc[j][3] = a3;
+    }
+  }
+  // merge the warps of the CTA (fixed order)
+#pragma unroll
+  for (int j = 0; j < G; ++j) {
+    *reinterpret_cast<float4*>(&part[warp][j][lane * 4]) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+    if (lane == 0) {
+      part[warp][j][128] = mx[j];
+      part[warp][j][129] = sum[j];
+    }
+  }
+  __syncthreads();
+  // threads 0..127: one output dimension each from here on
+  const int d = threadIdx.x & 127;
+  const bool writer = threadIdx.x < 128;
+  float* mine = scratch + (((size_t)b * kv_heads + kvh) * splits + split) * (G * 130);
+  if (writer) {
+    for (int j = 0; j < G; ++j) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) m = fmaxf(m, part[w][j][128]);
+      float l = 0.f, a = 0.f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) {
+        const float c = (part[w][j][128] == -INFINITY) ? 0.f : __expf(part[w][j][128] - m);
+        l += part[w][j][129] * c;
+        a += part[w][j][d] * c;
+      }
+      if (splits == 1) {
+        out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(a / l);
+      } else {
+        __stcg(mine + j * 130 + d, a);
+        if (d == 0) {
+          __stcg(mine + j * 130 + 128, m);
+          __stcg(mine + j * 130 + 129, l);
+        }
+      }
+    }
+  }
+  if (splits == 1) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int old = atomicAdd(counters + b * kv_heads + kvh, 1);
+    is_last = (old == splits - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // merge the slices: first the per-slice weights (one thread per (head, slice)), then the sums
+  __shared__ float coef[G][kMaxSplits];
+  __shared__ float denom[G];
+  const float* base = scratch + ((size_t)b * kv_heads + kvh) * splits * (G * 130);
+  for (int idx = threadIdx.x; idx < G * splits; idx += blockDim.x) {
+    const int j = idx / splits, s2 = idx - j * splits;
+    coef[j][s2] = __ldcg(base + s2 * (G * 130) + j * 130 + 128);  // the slice's max for now
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int j = threadIdx.x;
+    float m = -INFINITY;
+    for (int s2 = 0; s2 < splits; ++s2) m = fmaxf(m, coef[j][s2]);
+    float l = 0.f;
+    for (int s2 = 0; s2 < splits; ++s2) {
+      const float c = (coef[j][s2] == -INFINITY) ? 0.f : __expf(coef[j][s2] - m);
+      l += __ldcg(base + s2 * (G * 130) + j * 130 + 129) * c;
+      coef[j][s2] = c;
+    }
+    denom[j] = l;
+  }
+  __syncthreads();
+  if (writer) {
+    for (int j = 0; j < G; ++j) {
+      float a = 0.f;
+#pragma unroll 8
+      for (int s2 = 0; s2 < splits; ++s2) a += __ldcg(base + s2 * (G * 130) + j * 130 + d) * coef[j][s2];
+      out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(a / denom[j]);
+    }
+  }
+  if (threadIdx.x == 0) counters[b * kv_heads + kvh] = 0;
+}
+
+template <int G>
+int launch_attention(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
+                     void* scratch, void* counters, int batch, int q_heads, int kv_heads, int max_len,
+                     int splits, cudaStream_t stream) {
+  const int chunk = (max_len + splits - 1) / splits;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, kv_heads, batch);
+  cfg.blockDim = dim3(kAttnWarps * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G>, (const uint16_t*)q, (const uint16_t*)k_cache,
+                              (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
+                              (int*)counters, q_heads, kv_heads, max_len, chunk));
   return FDK_OK;
+}
+
+}  // namespace
+}  // namespace fdk
+
+extern "C" int fdk_decode_attention_scratch(int batch, int q_heads, int kv_heads, int splits,
+                                            size_t* scratch_bytes_host, size_t* counter_bytes_host) {
+  FDK_CHECK_ARG(scratch_bytes_host && counter_bytes_host, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(batch > 0 && q_heads > 0 && kv_heads > 0 && splits > 0 && q_heads % kv_heads == 0, FDK_ERR_BAD_ARG,
+                "bad sizes");
+  *scratch_bytes_host = (size_t)batch * q_heads * splits * 130 * sizeof(float);
+  *counter_bytes_host = (size_t)batch * kv_heads * sizeof(int);
+  return FDK_OK;
+}
+
+extern "C" int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache, const void* pos,
+                                    void* out, void* scratch, void* counters, int batch, int q_heads,
+                                    int kv_heads, int head_dim, int max_len, int splits, void* stream) {
+  FDK_CHECK_ARG(q && k_cache && v_cache && pos && out, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(head_dim == 128, FDK_ERR_SHAPE, "head_dim=%d: only 128 is supported", head_dim);
+  FDK_CHECK_ARG(batch > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= kMaxGroup, FDK_ERR_SHAPE,
+                "q_heads=%d must be 1..%d times kv_heads=%d", q_heads, kMaxGroup, kv_heads);
+  FDK_CHECK_ARG(splits >= 1 && splits <= kMaxSplits && max_len > 0, FDK_ERR_BAD_ARG, "splits=%d (1..%d), max_len=%d", splits, kMaxSplits, max_len);
+  FDK_CHECK_ARG(splits == 1 || (scratch && counters), FDK_ERR_WORKSPACE, "scratch and counters are needed when splits > 1");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (q_heads / kv_heads) {
+    case 1: return launch_attention<1>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 2: return launch_attention<2>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 3: return launch_attention<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 4: return launch_attention<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 5: return launch_attention<5>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 6: return launch_attention<6>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 7: return launch_attention<7>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    default: return launch_attention<8>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+  }
 }

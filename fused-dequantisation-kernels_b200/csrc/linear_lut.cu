@@ -355,7 +355,7 @@ __device__ __forceinline__ int ld_relaxed_s32(const int* p) {
 // runs once or twice per CTA, so its cost is mostly instruction fetches).  Returns false if a
 // bounded poll ran out.
 template <int NB, int WARPS, bool FP16>
-__device__ __noinline__ bool tile_finish(const LinearParams& p, float* slots, int rt, int c0, int c1) {
+__device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots, int rt, int c0, int c1) {
   constexpr int EMAX = 512 * NB;  // outputs of one row tile at TT = 4
   const int lane = threadIdx.x & 31;
   const int tt = p.slot_t, sw = 32 * tt;

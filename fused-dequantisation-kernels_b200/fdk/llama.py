@@ -7,8 +7,8 @@ written out -- embedding, [RMSNorm, fused q|k|v projection, rotary + KV append, 
 o projection, RMSNorm, fused gate|up projection, SiLU*up, down projection] x layers, final
 norm, lm_head (left in bf16, as the reference's default `skip="^lm_head$"` does), argmax --
 with every projection a `QuantisedLinear` running libfdk_b200's fused kernel (or a bf16
-`nn.Linear` for the 16-bit baseline) and the glue in three fused CUDA kernels.  Attention
-over the static KV cache uses torch's scaled_dot_product_attention.
+`nn.Linear` for the 16-bit baseline) and the glue -- norm + residual, rotary + cache append,
+split-context attention over the static KV cache, SiLU * up -- in four fused CUDA kernels.
 
 Tensor parallelism (not in the reference, which is single-GPU): Megatron-style.  q|k|v and
 gate|up are split by output rows (whole heads), o and down by input columns; block scales run
@@ -179,8 +179,11 @@ class LlamaDecoder(nn.Module):
         self.normed = torch.empty((batch, h), device=dev, dtype=dt)
         self.q = torch.empty((batch, self.q_heads * 128), device=dev, dtype=dt)
         self.act = torch.empty((batch, f), device=dev, dtype=dt)
+        self.attn = torch.empty((batch, self.q_heads * 128), device=dev, dtype=dt)
         self.position = torch.zeros((), device=dev, dtype=torch.int64)
-        self.key_mask = torch.zeros((1, 1, 1, max_len), device=dev, dtype=torch.bool)
+        # context slices per (batch row, KV head): a few hundred CTAs in all, at least 64 keys each
+        self.splits = max(1, min(max_len // 64, -(-512 // (batch * self.kv_heads)), 8))
+        self.attn_scratch, self.attn_counters = native.attention_scratch(batch, self.q_heads, self.kv_heads, self.splits, dev)
 
     def fill_cache_synthetic(self, context: int, seed: int = 1) -> None:
         """Benchmark aid: pretend `context` tokens have been decoded (random keys and values)."""
@@ -189,8 +192,6 @@ class LlamaDecoder(nn.Module):
             kc[:, :, :context].copy_(torch.randn(kc[:, :, :context].shape, generator=gen, device=kc.device, dtype=torch.float32))
             vc[:, :, :context].copy_(torch.randn(vc[:, :, :context].shape, generator=gen, device=vc.device, dtype=torch.float32))
         self.position.fill_(context)
-        self.key_mask.zero_()
-        self.key_mask[..., :context] = True
 
     # ---- one decode step --------------------------------------------------------------
 
@@ -198,18 +199,15 @@ class LlamaDecoder(nn.Module):
         """tokens [batch] int64 at position `self.position` -> logits [batch, vocab]; advances the
         position.  No host synchronisation, fixed shapes: capturable in a CUDA graph."""
         dims, eps = self.dims, self.dims.rms_norm_eps
-        self.key_mask.view(-1).index_fill_(0, self.position.view(1), True)
         torch.index_select(self.embed.weight, 0, tokens, out=self.hidden)
         delta = None
         for i, layer in enumerate(self.layers):
             native.rmsnorm(self.hidden, delta, layer.input_norm, self.normed, eps)
             qkv = layer.qkv(self.normed)
             native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads, dims.rope_theta)
-            attn = torch.nn.functional.scaled_dot_product_attention(
-                self.q.view(self.batch, self.q_heads, 1, 128), self.k_cache[i], self.v_cache[i],
-                attn_mask=self.key_mask, enable_gqa=True,
-            )
-            delta = layer.o(attn.view(self.batch, self.q_heads * 128))
+            native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
+                                    self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
+            delta = layer.o(self.attn)
             self.tp.all_reduce(delta)
             native.rmsnorm(self.hidden, delta, layer.post_norm, self.normed, eps)
             gate_up = layer.gate_up(self.normed)

@@ -95,6 +95,14 @@ class QuantisedLinear(nn.Module):
             self._tiled_key = key
         return self._tiled
 
+    def lut_bytes(self) -> bytes:
+        """Host copy of the table (made once): it travels with the kernel's launch parameters."""
+        key = (self.lut.data_ptr(), self.lut._version)
+        if getattr(self, "_lut_host_key", None) != key:
+            self._lut_host = native.host_lut(self.lut)
+            self._lut_host_key = key
+        return self._lut_host
+
     def forward(self, x: Tensor) -> Tensor:
         if x.ndim > 2:
             return self.forward(x.flatten(end_dim=-2)).unflatten(0, x.shape[:-1])
@@ -104,7 +112,8 @@ class QuantisedLinear(nn.Module):
         out = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=x.dtype)
         assert x.dtype == self.lut.dtype == self.scale.dtype
         native.linear_lut(
-            x.contiguous(), self.tiled(), self.lut, out, self.out_features, self.in_features, self.bits
+            x.contiguous(), self.tiled(), self.lut, out, self.out_features, self.in_features, self.bits,
+            pdl=True, lut_bytes=self.lut_bytes(),
         )
         return out
 

@@ -49,6 +49,8 @@ _SIGNATURES = {
     "fdk_rmsnorm": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 2 + [ctypes.c_float, ctypes.c_void_p]),
     "fdk_rope_append": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_void_p]),
     "fdk_silu_mul": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 2 + [ctypes.c_void_p]),
+    "fdk_decode_attention_scratch": (ctypes.c_int, [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_size_t)] * 2),
+    "fdk_decode_attention": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_int] * 6 + [ctypes.c_void_p]),
     "fdk_workspace_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "fdk_linear_lut": (
         ctypes.c_int,
@@ -259,3 +261,23 @@ def silu_mul(gate_up: Tensor, out: Tensor) -> None:
     rows, width = out.shape
     with torch.cuda.device(out.device):
         check(lib().fdk_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, width, _stream()))
+
+
+def attention_scratch(batch: int, q_heads: int, kv_heads: int, splits: int, device: torch.device) -> tuple[Tensor, Tensor]:
+    a, b = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    check(lib().fdk_decode_attention_scratch(batch, q_heads, kv_heads, splits, ctypes.byref(a), ctypes.byref(b)))
+    return (torch.empty(a.value // 4, dtype=torch.float32, device=device), torch.zeros(b.value // 4, dtype=torch.int32, device=device))
+
+
+def decode_attention(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, out: Tensor,
+                     scratch: Tensor, counters: Tensor, q_heads: int, kv_heads: int, splits: int) -> None:
+    """One query token per batch row against the KV cache [batch, kv_heads, max_len, 128], keys 0..pos."""
+    _require_cuda(q, k_cache, v_cache, pos, out)
+    with torch.cuda.device(q.device):
+        check(
+            lib().fdk_decode_attention(
+                q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                scratch.data_ptr(), counters.data_ptr(), q.shape[0], q_heads, kv_heads, 128, k_cache.shape[2],
+                splits, _stream(),
+            )
+        )

@@ -159,6 +159,19 @@ int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache
  * the output of the fused gate|up projection. */
 int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, void* stream);
 
+/* Decode attention: one query token per batch row against the static KV cache
+ * [batch, kv_heads, max_len, 128] (bf16), keys 0 .. *pos (device int64; the current token's
+ * key and value must already be appended), grouped-query (q_heads / kv_heads in 1..8).
+ * q, out: [batch, q_heads * 128].  The context is cut into `splits` slices handled by
+ * different CTAs; with splits > 1, `scratch` and zero-initialised `counters` of the sizes
+ * given by fdk_decode_attention_scratch are needed (counters are left zeroed).  Stands in for
+ * the attention of transformers' Llama over its StaticCache (src/fdk/models.py:238-251). */
+int fdk_decode_attention_scratch(int batch, int q_heads, int kv_heads, int splits,
+                                 size_t* scratch_bytes_host, size_t* counter_bytes_host);
+int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache, const void* pos,
+                         void* out, void* scratch, void* counters, int batch, int q_heads,
+                         int kv_heads, int head_dim, int max_len, int splits, void* stream);
+
 /* fdk_linear_lut for callers that cannot allocate device memory where they call it -- a
  * plugin inside a host runtime that owns all device allocations, or code running while a
  * stream capture forbids cudaMalloc.  Same arguments and results as fdk_linear_lut minus the

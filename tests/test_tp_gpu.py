@@ -1,0 +1,52 @@
+"""Tensor-parallel decode on real GPUs: logits of a 2-rank run equal those of a 1-rank run of
+the same model (same seed) up to bf16 noise.  Needs two CUDA devices; skipped otherwise.
+NVLS is switched off for the child processes."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parents[1]
+
+WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["FDK_PKG"])
+from fdk import llama, models
+world, rank = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+dims = models.LlamaDims("tiny", 512, 2, 4, 2, 1024, vocab_size=512)
+cfg = models.QuantisationConfig(4, 64)
+ids = torch.randint(0, 512, (2, 6), generator=torch.Generator().manual_seed(1)).to(dev)
+def run(tp):
+    model = llama.LlamaDecoder.random_init(dims, cfg, dev, tp, seed=7)
+    model.allocate(2, 8)
+    with torch.no_grad():
+        return torch.stack([model(ids[:, t].contiguous()).float() for t in range(6)], 1)
+sharded = run(llama.TensorParallel(rank, world))
+whole = run(llama.TensorParallel())
+err = (sharded - whole).pow(2).sum().div(whole.pow(2).sum()).sqrt().item()
+print(f"rank {rank} rel-RMS error {err:.3e}", flush=True)
+assert err < 2e-2, err
+dist.barrier()
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_decode_matches_single_rank(tmp_path):
+    script = tmp_path / "tp_worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, FDK_PKG=str(ROOT / "fused-dequantisation-kernels_b200"), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300), str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert res.stdout.count("rel-RMS error") == 2
