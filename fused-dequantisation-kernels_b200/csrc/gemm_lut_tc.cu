@@ -1,0 +1,404 @@
+// Fused dequantise + GEMM for batches of 17 and more rows, on the fifth-generation tensor
+// cores:  out[m, n] = x[m, k] . W[n, k]^T  with W = bf16(table value * block scale), the
+// reference's dense W (src/fdk/kernels.py:23-24) bit for bit, built tile by tile in shared
+// memory and never written to HBM.
+//
+// One CTA per 128 weight rows (the MMA M dimension; the batch is the MMA N dimension, so a
+// weight tile is dequantised once for the whole batch).  Six warps, specialised:
+//   warp 0      copy producer: per 64-column block, the two code slabs of the tile by
+//               cp.async.bulk and the [batch, 64] slice of x by a tiled TMA load
+//               (128-byte swizzle), into a ring of stages, completion on mbarriers;
+//   warps 2..5  dequantise: code bytes -> per-lane replicated table lookup -> multiply by the
+//               block scale in bf16 -> the 128 x 64 bf16 A tile of the stage, written in the
+//               K-major 128-byte-swizzled layout the MMA reads; afterwards the epilogue;
+//   warp 1      one thread issues tcgen05.mma (M = 128, N = batch padded to 16, K = 16, four
+//               per block) accumulating in tensor memory, and tcgen05.commit hands the stage
+//               back to the producer; it also owns the tensor-memory allocation.
+// Epilogue: tcgen05.ld brings the fp32 accumulators to registers (one tile row per thread),
+// converted to bf16 and stored transposed into out[batch, n].
+// Every barrier wait is bounded; a wait that runs out sets a status bit, and the kernel still
+// frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "fdk_common.cuh"
+#include "lut_table.cuh"
+
+namespace fdk {
+namespace {
+
+constexpr int kTcThreads = 192;
+constexpr int kTcTileRows = 128;
+constexpr int kTcMaxStages = 4;
+constexpr int kTcStatusTimeout = 1;
+constexpr int kTcStatusSmemLayout = 2;
+
+struct TcParams {
+  const uint8_t* tiled;
+  const void* lut;   // device byte table, or null when it travels in the parameters
+  uint16_t* out;
+  int* status;       // device-side error bits
+  int m, m_pad, n, k;
+  int row_tiles;     // 64-row tiles of the tiled buffer
+  int k_blocks;      // k / 64
+  int stages;
+  uint32_t tmem_cols;
+  uint32_t smem_base, table_addr, bar_addr, tmem_slot_addr;
+  uint32_t a_addr[kTcMaxStages], b_addr[kTcMaxStages], c_addr[kTcMaxStages];
+};
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                        // descriptor version
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ring32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// The 16 elements (eight bf16 pairs) that the 2*BITS code bytes `lo`,`hi` (and for 8 bits two
+// more words) of one row decode to, in element order.
+template <int BITS>
+__device__ __forceinline__ void decode_row16(const uint32_t (&w)[4], uint32_t lane_base, uint32_t (&v)[8]) {
+  if constexpr (BITS == 4) {
+    v[0] = lut32(entry_addr<4, 0>(w[0], lane_base)); v[1] = lut32(entry_addr<4, 1>(w[0], lane_base));
+    v[2] = lut32(entry_addr<4, 2>(w[0], lane_base)); v[3] = lut32(entry_addr<4, 3>(w[0], lane_base));
+    v[4] = lut32(entry_addr<4, 0>(w[1], lane_base)); v[5] = lut32(entry_addr<4, 1>(w[1], lane_base));
+    v[6] = lut32(entry_addr<4, 2>(w[1], lane_base)); v[7] = lut32(entry_addr<4, 3>(w[1], lane_base));
+  } else {  // 8 bits: sixteen single lookups, merged in pairs
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = prmt<0x7610>(lut32(entry_addr<8, 0>(w[i], lane_base)), lut32(entry_addr<8, 1>(w[i], lane_base)));
+      v[2 * i + 1] = prmt<0x7610>(lut32(entry_addr<8, 2>(w[i], lane_base)), lut32(entry_addr<8, 3>(w[i], lane_base)));
+    }
+  }
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kTcThreads, 1)
+    gemm_lut_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ InlineLut<BITS> inl,
+                       const __grid_constant__ CUtensorMap x_map) {
+  using L = Layout<BITS>;
+  using T = Table<BITS>;
+  static_assert(L::KSB == 1, "one 64-column block per slab");
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t raw = smem_addr(smem_raw);
+  if (raw != p.smem_base) {
+    if (threadIdx.x == 0) atomicOr(p.status, kTcStatusSmemLayout);
+    return;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int S = p.stages;
+  // barriers: tma_full[S], a_full[S], empty[S], accum_full
+  const uint32_t tma_full = p.bar_addr, a_full = p.bar_addr + 8 * S, empty = p.bar_addr + 16 * S,
+                 accum_full = p.bar_addr + 24 * S;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (p.tmem_slot_addr - raw));
+  const int tile = blockIdx.x;                    // 128 rows = 64-row tiles 2*tile, 2*tile + 1
+  const bool second_half = (2 * tile + 1) < p.row_tiles;
+  bool timed_out = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(tma_full + 8 * s, 1);
+      mbar_init(a_full + 8 * s, 4);  // one arrival per dequantising warp
+      mbar_init(empty + 8 * s, 1);
+    }
+    mbar_init(accum_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // tensor memory for the accumulator: 128 lanes x tmem_cols columns of fp32
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(p.tmem_slot_addr),
+                 "r"(p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp >= 2) {
+    if (p.lut == nullptr) {
+      fill_table<BITS>(p.table_addr, 128, [&](int i) { return inl.w[i]; }, threadIdx.x - 64);
+    } else {
+      fill_table<BITS>(p.table_addr, 128, [&](int i) { return __ldg(reinterpret_cast<const uint32_t*>(p.lut) + i); },
+                       threadIdx.x - 64);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- copy producer ----------------
+    if (lane == 0) {
+      const uint32_t code_bytes = L::kSlabBytes * (second_half ? 2 : 1);
+      const uint32_t x_bytes = (uint32_t)p.m_pad * 128;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int s = kb % S;
+        const uint32_t phase = (kb / S) & 1;
+        if (!mbar_wait(empty + 8 * s, phase ^ 1)) { timed_out = true; break; }
+        const uint32_t bar = tma_full + 8 * s;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(code_bytes + x_bytes) : "memory");
+        const uint8_t* slab0 = p.tiled + ((size_t)(2 * tile) * p.k_blocks + kb) * L::kSlabBytes;
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(p.c_addr[s]),
+                     "l"(slab0), "r"((uint32_t)L::kSlabBytes), "r"(bar)
+                     : "memory");
+        if (second_half) {
+          const uint8_t* slab1 = p.tiled + ((size_t)(2 * tile + 1) * p.k_blocks + kb) * L::kSlabBytes;
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           p.c_addr[s] + (uint32_t)L::kSlabBytes),
+                       "l"(slab1), "r"((uint32_t)L::kSlabBytes), "r"(bar)
+                       : "memory");
+        }
+        tma_load_2d(p.b_addr[s], &x_map, kb * 64, 0, bar);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = m_pad, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.m_pad >> 3) << 17) | ((128u >> 4) << 24);
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int s = kb % S;
+        const uint32_t phase = (kb / S) & 1;
+        if (!mbar_wait(tma_full + 8 * s, phase)) { timed_out = true; break; }
+        if (!mbar_wait(a_full + 8 * s, phase)) { timed_out = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          umma_bf16(tmem_base, umma_desc(p.a_addr[s] + j * 32), umma_desc(p.b_addr[s] + j * 32), idesc,
+                    (kb > 0 || j > 0) ? 1u : 0u);
+        }
+        umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(accum_full);
+    }
+  } else {
+    // ---------------- dequantise, then epilogue ----------------
+    const int dw = warp - 2;          // 0..3: sub-tiles 2 dw, 2 dw + 1 of the eight 16-row sub-tiles
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t lane_base = p.table_addr + lane * T::kEntryBytes;
+    for (int kb = 0; kb < p.k_blocks; ++kb) {
+      const int s = kb % S;
+      const uint32_t phase = (kb / S) & 1;
+      if (!mbar_wait(tma_full + 8 * s, phase)) { timed_out = true; break; }
+#pragma unroll
+      for (int uu = 0; uu < 2; ++uu) {
+        const int u = dw * 2 + uu, half = u >> 2, r = u & 3;
+        if (half == 1 && !second_half) continue;
+        const uint32_t slab = p.c_addr[s] + half * L::kSlabBytes;
+        const uint32_t scw = ring32(slab + L::kCodeBytes + g * 16 + r * 4);
+        const uint32_t s_lo = prmt<0x1010>(scw, 0u), s_hi = prmt<0x3232>(scw, 0u);  // scale of row g / g+8 in both halves
+        uint32_t wg[4], wh[4];
+        if constexpr (BITS == 4) {
+          const uint4 c = ring128(slab + (r * 32 + lane) * 16);
+          wg[0] = c.x; wg[1] = c.y; wh[0] = c.z; wh[1] = c.w;
+          wg[2] = wg[3] = wh[2] = wh[3] = 0;
+        } else {
+          const uint4 cg = ring128(slab + ((r * 2) * 32 + lane) * 16), ch = ring128(slab + ((r * 2 + 1) * 32 + lane) * 16);
+          wg[0] = cg.x; wg[1] = cg.y; wg[2] = cg.z; wg[3] = cg.w;
+          wh[0] = ch.x; wh[1] = ch.y; wh[2] = ch.z; wh[3] = ch.w;
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t v[8];
+          decode_row16<BITS>(hh == 0 ? wg : wh, lane_base, v);
+          const uint32_t sc = hh == 0 ? s_lo : s_hi;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = mul_bf16x2(v[i], sc);
+          const int row = 16 * u + g + 8 * hh;  // row % 8 == g
+          const uint32_t row_addr = p.a_addr[s] + row * 128;
+          const uint32_t c0 = ((2 * t) ^ g) * 16, c1 = ((2 * t + 1) ^ g) * 16;
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + c0), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + c1), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a_full + 8 * s) : "memory");
+    }
+    // epilogue: this warp reads the 32 accumulator rows of its tensor-memory lane quarter
+    if (!mbar_wait(accum_full, 0)) timed_out = true;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int quarter = warp & 3;
+    const int row = tile * kTcTileRows + quarter * 32 + lane;
+    for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+      uint32_t acc[16];
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+          : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]), "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7]),
+            "=r"(acc[8]), "=r"(acc[9]), "=r"(acc[10]), "=r"(acc[11]), "=r"(acc[12]), "=r"(acc[13]), "=r"(acc[14]), "=r"(acc[15])
+          : "r"(taddr)
+          : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (row < p.n) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int b = c0 + j;
+          if (b < p.m) p.out[(size_t)b * p.n + row] = from_float<false>(__uint_as_float(acc[j]));
+        }
+      }
+    }
+  }
+  if (timed_out && lane == 0) atomicOr(p.status, kTcStatusTimeout);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    FDK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+    FDK_CHECK_ARG(qres == cudaDriverEntryPointSuccess && sym != nullptr, FDK_ERR_CUDA, "cuTensorMapEncodeTiled not found");
+    fn = (EncodeTiledFn)sym;
+  }
+  *out = fn;
+  return FDK_OK;
+}
+
+inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Places the stage buffers in the two free regions around the 64 KB-aligned table (below it and
+// above it), largest first.  Returns the dynamic shared memory size, or 0 if `stages` do not fit.
+template <int BITS>
+size_t plan_tc_smem(uint32_t base, uint32_t limit, int stages, TcParams& p) {
+  using L = Layout<BITS>;
+  using T = Table<BITS>;
+  uint32_t lo = round_up(base, 1024);
+  p.smem_base = base;
+  p.bar_addr = lo;
+  p.tmem_slot_addr = lo + 8 * (3 * kTcMaxStages + 1);
+  lo += 1024;
+  const uint32_t table = round_up(lo, 65536);
+  p.table_addr = table;
+  uint32_t hi = table + T::kBytes;
+  const uint32_t end = base + limit;
+  auto place = [&](uint32_t bytes, uint32_t align, uint32_t* out) -> bool {
+    uint32_t a = round_up(lo, align);
+    if (a + bytes <= table) { *out = a; lo = a + bytes; return true; }
+    a = round_up(hi, align);
+    if (a + bytes <= end) { *out = a; hi = a + bytes; return true; }
+    return false;
+  };
+  p.stages = stages;
+  const uint32_t b_bytes = (uint32_t)p.m_pad * 128;
+  for (int s = 0; s < stages; ++s) if (!place(b_bytes, 1024, &p.b_addr[s])) return 0;
+  for (int s = 0; s < stages; ++s) if (!place(16384, 1024, &p.a_addr[s])) return 0;
+  for (int s = 0; s < stages; ++s) if (!place(2 * L::kSlabBytes, 128, &p.c_addr[s])) return 0;
+  return hi - base;
+}
+
+template <int BITS>
+int launch_tc(TcParams p, const void* lut_host, const CUtensorMap& map, int tiles, cudaStream_t stream) {
+  InlineLut<BITS> inl;
+  if (lut_host != nullptr) {
+    memcpy(inl.w, lut_host, sizeof(inl.w));
+    p.lut = nullptr;
+  } else {
+    memset(inl.w, 0, sizeof(inl.w));
+  }
+  uint32_t base = 0;
+  if (int st = dynamic_smem_base(&base)) return st;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  size_t smem = 0;
+  for (int s = kTcMaxStages; s >= 1 && smem == 0; --s) smem = plan_tc_smem<BITS>(base, (uint32_t)di.max_smem_optin, s, p);
+  FDK_CHECK_ARG(smem != 0, FDK_ERR_CUDA, "no shared-memory plan fits %d bytes", di.max_smem_optin);
+  auto kernel = gemm_lut_tc_kernel<BITS>;
+  static size_t configured[64] = {};
+  int dev = 0;
+  FDK_CUDA(cudaGetDevice(&dev));
+  if (configured[dev & 63] < smem) {
+    FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev & 63] = smem;
+  }
+  kernel<<<tiles, kTcThreads, smem, stream>>>(p, inl, map);
+  FDK_CUDA(cudaGetLastError());
+  return FDK_OK;
+}
+
+}  // namespace
+
+// Batches above 16 rows, bf16, 4- or 8-bit codes.  Called by fdk_linear_lut.
+int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out, int m, int n,
+                int k, int bits, int* status, cudaStream_t stream) {
+  EncodeTiledFn encode = nullptr;
+  if (int st = encode_fn(&encode)) return st;
+  const TiledDims d = tiled_dims(n, k, bits);
+  for (int m0 = 0; m0 < m; m0 += 256) {
+    const int mc = (m - m0) < 256 ? (m - m0) : 256;
+    TcParams p{};
+    p.tiled = (const uint8_t*)tiled;
+    p.lut = lut;
+    p.out = (uint16_t*)out + (size_t)m0 * n;
+    p.status = status;
+    p.m = mc;
+    p.m_pad = (mc + 15) / 16 * 16;
+    p.n = n;
+    p.k = k;
+    p.row_tiles = d.row_tiles;
+    p.k_blocks = k / kBlock;
+    uint32_t cols = 32;
+    while ((int)cols < p.m_pad) cols *= 2;
+    p.tmem_cols = cols;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)mc};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)p.m_pad};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)((const uint16_t*)x + (size_t)m0 * k), dims,
+                        strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FDK_CHECK_ARG(r == CUDA_SUCCESS, FDK_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    const int tiles = (n + kTcTileRows - 1) / kTcTileRows;
+    int st = (bits == 4) ? launch_tc<4>(p, lut_host, map, tiles, stream) : launch_tc<8>(p, lut_host, map, tiles, stream);
+    if (st) return st;
+  }
+  return FDK_OK;
+}
+
+}  // namespace fdk

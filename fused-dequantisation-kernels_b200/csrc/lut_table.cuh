@@ -1,0 +1,197 @@
+// Device helpers shared by the fused kernels: shared-memory addressing, bulk asynchronous
+// copies with bounded barrier waits, the per-lane replicated lookup table and the
+// m16n8k16 MMA wrapper.
+#pragma once
+#include <type_traits>
+
+#include "fdk_common.cuh"
+
+namespace fdk {
+
+constexpr uint32_t kWaitLimit = 1u << 22;  // try_wait rounds before giving up (seconds, not microseconds)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ uint4 ldg_l1(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "n"(SEL));
+  return d;
+}
+
+// Table lookups: pure functions of the address once the table is filled (it never
+// changes afterwards), so the compiler may schedule them freely.
+__device__ __forceinline__ uint32_t lut32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lut64(uint32_t addr) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lut128(uint32_t addr) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+// Ring reads: ordered after the barrier wait that precedes them.
+__device__ __forceinline__ uint4 ring128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Waits for the phase with the given parity; gives up after kWaitLimit rounds or two seconds,
+// whichever comes first.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  unsigned long long t0 = 0;
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((i & 1023u) == 1023u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) return false;
+    }
+  }
+  return false;
+}
+
+template <bool FP16>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                         const float (&c)[4]) {
+  if constexpr (FP16) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+  } else {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+  }
+}
+
+template <int I>
+__device__ __forceinline__ uint32_t word_of(const uint4& v) {
+  if constexpr (I == 0) return v.x;
+  else if constexpr (I == 1) return v.y;
+  else if constexpr (I == 2) return v.z;
+  else return v.w;
+}
+__device__ __forceinline__ uint32_t word_at(const uint4& v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+
+// ---- lookup tables in shared memory -----------------------------------------
+// Per-lane replicas: entry e of lane l lives at  base + e * kStride + l * kEntryBytes,
+// so that the 32 lanes of a warp always hit 32 different banks (or, for 8/16-byte
+// entries, every quarter / half warp does).  For the 256-byte stride the base is
+// 64 KB aligned inside the shared window: the address of entry `byte` is then the
+// lane's base with `byte` dropped into bits 8..15, which is a single PRMT.
+template <int BITS>
+struct Table {
+  static constexpr int kEntries = (BITS == 3) ? 64 : 256;
+  static constexpr int kEntryBytes = (BITS == 2) ? 8 : (BITS == 1 ? 16 : 4);
+  static constexpr int kStride = (BITS == 1) ? 512 : 256;
+  static constexpr int kBytes = kEntries * kStride;
+  static constexpr bool kAligned64K = (BITS != 1);
+};
+
+// The byte table may travel inside the kernel parameters (no memory latency at all) or be
+// read from device memory.  16-bit entries, packed two per word.
+template <int BITS>
+struct InlineLut {
+  static constexpr int kWords = (BITS == 3) ? 4 : 256 * (8 / BITS) / 2;
+  uint32_t w[kWords];
+};
+
+// Fills the per-lane replicated table.  A plain loop on purpose: code that runs once per
+// launch costs mostly instruction fetches, so it is kept short rather than unrolled.
+// word(i) returns 32-bit word i of the source table.
+template <int BITS, class WordFn>
+__device__ __forceinline__ void fill_table(uint32_t table_base, int threads, WordFn word, int tid) {
+  using T = Table<BITS>;
+#pragma unroll 1
+  for (int idx = tid; idx < T::kEntries * 32; idx += threads) {
+    const int e = idx >> 5, l = idx & 31;
+    const uint32_t addr = table_base + e * T::kStride + l * T::kEntryBytes;
+    if constexpr (BITS == 4) {
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(word(e)) : "memory");
+    } else if constexpr (BITS == 2) {
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(word(2 * e)), "r"(word(2 * e + 1)) : "memory");
+    } else if constexpr (BITS == 1) {
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(word(4 * e)), "r"(word(4 * e + 1)),
+                   "r"(word(4 * e + 2)), "r"(word(4 * e + 3))
+                   : "memory");
+    } else if constexpr (BITS == 8) {
+      const uint32_t pair = word(e >> 1);
+      const uint32_t h = (e & 1) ? (pair >> 16) : (pair & 0xFFFFu);
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(h | (h << 16)) : "memory");
+    } else {  // 3 bits: pair table from the 8-entry codebook, first code in the high 3 index bits
+      auto code = [&](int c) {
+        const uint32_t pair = word(c >> 1);
+        return (c & 1) ? (pair >> 16) : (pair & 0xFFFFu);
+      };
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(code(e >> 3) | (code(e & 7) << 16)) : "memory");
+    }
+  }
+}
+
+// Address of the table entry selected by byte J of `w` (lane_base = table base + lane offset).
+template <int BITS, int J>
+__device__ __forceinline__ uint32_t entry_addr(uint32_t w, uint32_t lane_base) {
+  if constexpr (BITS == 1) {
+    uint32_t b = prmt<0x4404u | (J << 4)>(w, 0u);  // byte << 8
+    return lane_base + (b << 1);                    // stride 512
+  } else {
+    return prmt<0x7604u | (J << 4)>(w, lane_base);  // bits 8..15 <- byte
+  }
+}
+
+template <int BITS, class WordFn>
+__device__ __forceinline__ void fill_table(uint32_t table_base, WordFn word) {
+  fill_table<BITS>(table_base, (int)blockDim.x, word, (int)threadIdx.x);
+}
+
+// Tensor-core GEMM for batches above 16 rows (gemm_lut_tc.cu): bf16, 4- or 8-bit codes.
+int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out, int m, int n,
+                int k, int bits, int* status, cudaStream_t stream);
+
+// The dynamic shared memory address seen by kernels without static shared memory, asked of
+// the device once (linear_lut.cu).
+int dynamic_smem_base(uint32_t* out);
+
+}  // namespace fdk

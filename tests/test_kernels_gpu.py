@@ -177,3 +177,30 @@ def test_error_statuses_on_device(native):
     assert args(x.data_ptr(), None, 0) == 6
     assert args(x.data_ptr(), ws.data_ptr(), ws.numel()) == 0
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("m,n,k", [(17, 128, 64), (32, 192, 256), (64, 1024, 1024), (200, 4096, 4096), (192, 768, 4096), (256, 2048, 3072), (300, 256, 512)])
+def test_tensor_core_gemm_matches_oracle(native, bits, m, n, k):
+    """Batches above 16 rows run the tcgen05 kernel, whose W is the reference's bf16 W bit for
+    bit; its outputs differ from the oracle's only by fp32 summation order and the last bf16
+    rounding."""
+    codes, lut, scale, x = random_problem(n, k, bits, m, seed=m + n + k + bits)
+    expected = O.mm_dense(x, O.dequantise(codes, lut, scale))
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    native.linear_lut(from_bits(x), tiled, from_bits(lut), out, n, k, bits)
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    err = O.rmsen(O.bf16_to_f32(expected), O.bf16_to_f32(to_bits(out)))
+    assert err < 4e-3, f"rmsen={err}"
+    mismatched = np.mean(to_bits(out) != expected)
+    assert mismatched < 0.05  # a few last-bit roundings at most
+
+
+def test_reference_mm_test_recipe(native):
+    """test_mm_4b_lut8 of the reference (src/fdk/kernels.py:492-502) through the operator API."""
+    from fdk import bench
+
+    bench.test_mm_4b_lut8()
+    bench.test_mv_4b_lut8()
