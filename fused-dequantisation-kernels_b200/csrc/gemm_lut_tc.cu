@@ -28,7 +28,9 @@
 namespace fdk {
 namespace {
 
-constexpr int kTcThreads = 192;
+constexpr int kTcDequantWarps = 8;
+constexpr int kTcThreads = 64 + 32 * kTcDequantWarps;
+constexpr int kTcMaxSplits = 8;
 constexpr int kTcTileRows = 128;
 constexpr int kTcMaxStages = 4;
 constexpr int kTcStatusTimeout = 1;
@@ -43,6 +45,10 @@ struct TcParams {
   int row_tiles;     // 64-row tiles of the tiled buffer
   int k_blocks;      // k / 64
   int stages;
+  int splits;        // CTAs sharing one 128-row tile, each with a contiguous range of 64-column blocks
+  float* partial;    // [tile][split - 1][m_pad][128] fp32 sums of the non-owning CTAs
+  int* flags;        // [tile][kTcMaxSplits] tag of the last published partial
+  int* uses;         // [tile] how often the tile has been finished through this workspace
   uint32_t tmem_cols;
   uint32_t smem_base, table_addr, bar_addr, tmem_slot_addr;
   uint32_t a_addr[kTcMaxStages], b_addr[kTcMaxStages], c_addr[kTcMaxStages];
@@ -127,14 +133,18 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   const uint32_t tma_full = p.bar_addr, a_full = p.bar_addr + 8 * S, empty = p.bar_addr + 16 * S,
                  accum_full = p.bar_addr + 24 * S;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (p.tmem_slot_addr - raw));
-  const int tile = blockIdx.x;                    // 128 rows = 64-row tiles 2*tile, 2*tile + 1
+  const int tile = blockIdx.x / p.splits;         // 128 rows = 64-row tiles 2*tile, 2*tile + 1
+  const int sp = blockIdx.x - tile * p.splits;    // this CTA's share of the 64-column blocks
+  const int kb_begin = (int)((long long)p.k_blocks * sp / p.splits);
+  const int kb_end = (int)((long long)p.k_blocks * (sp + 1) / p.splits);
+  const int n_kb = kb_end - kb_begin;
   const bool second_half = (2 * tile + 1) < p.row_tiles;
   bool timed_out = false;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(tma_full + 8 * s, 1);
-      mbar_init(a_full + 8 * s, 4);  // one arrival per dequantising warp
+      mbar_init(a_full + 8 * s, kTcDequantWarps);  // one arrival per dequantising warp
       mbar_init(empty + 8 * s, 1);
     }
     mbar_init(accum_full, 1);
@@ -149,10 +159,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   }
   if (warp >= 2) {
     if (p.lut == nullptr) {
-      fill_table<BITS>(p.table_addr, 128, [&](int i) { return inl.w[i]; }, threadIdx.x - 64);
+      fill_table<BITS>(p.table_addr, 32 * kTcDequantWarps, [&](int i) { return inl.w[i]; }, threadIdx.x - 64);
     } else {
-      fill_table<BITS>(p.table_addr, 128, [&](int i) { return __ldg(reinterpret_cast<const uint32_t*>(p.lut) + i); },
-                       threadIdx.x - 64);
+      fill_table<BITS>(p.table_addr, 32 * kTcDequantWarps,
+                       [&](int i) { return __ldg(reinterpret_cast<const uint32_t*>(p.lut) + i); }, threadIdx.x - 64);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -165,9 +175,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     if (lane == 0) {
       const uint32_t code_bytes = L::kSlabBytes * (second_half ? 2 : 1);
       const uint32_t x_bytes = (uint32_t)p.m_pad * 128;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        const int s = kb % S;
-        const uint32_t phase = (kb / S) & 1;
+      for (int i = 0; i < n_kb; ++i) {
+        const int kb = kb_begin + i;
+        const int s = i % S;
+        const uint32_t phase = (i / S) & 1;
         if (!mbar_wait(empty + 8 * s, phase ^ 1)) { timed_out = true; break; }
         const uint32_t bar = tma_full + 8 * s;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(code_bytes + x_bytes) : "memory");
@@ -190,16 +201,16 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     if (lane == 0) {
       // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = m_pad, M = 128
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.m_pad >> 3) << 17) | ((128u >> 4) << 24);
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        const int s = kb % S;
-        const uint32_t phase = (kb / S) & 1;
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % S;
+        const uint32_t phase = (i / S) & 1;
         if (!mbar_wait(tma_full + 8 * s, phase)) { timed_out = true; break; }
         if (!mbar_wait(a_full + 8 * s, phase)) { timed_out = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           umma_bf16(tmem_base, umma_desc(p.a_addr[s] + j * 32), umma_desc(p.b_addr[s] + j * 32), idesc,
-                    (kb > 0 || j > 0) ? 1u : 0u);
+                    (i > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
       }
@@ -207,17 +218,16 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     }
   } else {
     // ---------------- dequantise, then epilogue ----------------
-    const int dw = warp - 2;          // 0..3: sub-tiles 2 dw, 2 dw + 1 of the eight 16-row sub-tiles
+    const int dw = warp - 2;          // 0..7: one of the eight 16-row sub-tiles each
     const int g = lane >> 2, t = lane & 3;
     const uint32_t lane_base = p.table_addr + lane * T::kEntryBytes;
-    for (int kb = 0; kb < p.k_blocks; ++kb) {
-      const int s = kb % S;
-      const uint32_t phase = (kb / S) & 1;
+    for (int i = 0; i < n_kb; ++i) {
+      const int s = i % S;
+      const uint32_t phase = (i / S) & 1;
       if (!mbar_wait(tma_full + 8 * s, phase)) { timed_out = true; break; }
-#pragma unroll
-      for (int uu = 0; uu < 2; ++uu) {
-        const int u = dw * 2 + uu, half = u >> 2, r = u & 3;
-        if (half == 1 && !second_half) continue;
+      {
+        const int u = dw, half = u >> 2, r = u & 3;
+        if (!(half == 1 && !second_half)) {
         const uint32_t slab = p.c_addr[s] + half * L::kSlabBytes;
         const uint32_t scw = ring32(slab + L::kCodeBytes + g * 16 + r * 4);
         const uint32_t s_lo = prmt<0x1010>(scw, 0u), s_hi = prmt<0x3232>(scw, 0u);  // scale of row g / g+8 in both halves
@@ -244,31 +254,84 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + c0), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_addr + c1), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
         }
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a_full + 8 * s) : "memory");
     }
-    // epilogue: this warp reads the 32 accumulator rows of its tensor-memory lane quarter
-    if (!mbar_wait(accum_full, 0)) timed_out = true;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int quarter = warp & 3;
-    const int row = tile * kTcTileRows + quarter * 32 + lane;
-    for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
-      uint32_t acc[16];
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-          : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]), "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7]),
-            "=r"(acc[8]), "=r"(acc[9]), "=r"(acc[10]), "=r"(acc[11]), "=r"(acc[12]), "=r"(acc[13]), "=r"(acc[14]), "=r"(acc[15])
-          : "r"(taddr)
-          : "memory");
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < p.n) {
+    // epilogue (first four of these warps): each reads the 32 accumulator rows of its
+    // tensor-memory lane quarter.  A CTA that does not own the tile parks its fp32 sums in the
+    // workspace; the owner (share 0) adds the parked sums in share order and writes bf16.
+    if (dw < 4) {
+      if (!mbar_wait(accum_full, 0)) timed_out = true;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int quarter = warp & 3;
+      const int row_in_tile = quarter * 32 + lane;
+      const int row = tile * kTcTileRows + row_in_tile;
+      int tag = 0;
+      if (p.splits > 1) tag = ld_relaxed_s32(p.uses + tile) + 1;
+      if (sp == 0 && p.splits > 1) {  // wait until every other share has been published
+        for (int o = 1; o < p.splits; ++o) {
+          unsigned long long t0 = 0;
+          for (uint32_t spin = 0;; ++spin) {
+            int f;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(p.flags + tile * kTcMaxSplits + o) : "memory");
+            if (f == tag) break;
+            if ((spin & 255u) == 255u) {
+              unsigned long long now;
+              asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+              if (t0 == 0) t0 = now;
+              else if (now - t0 > 2000000000ull) { timed_out = true; break; }
+            }
+          }
+        }
+      }
+      for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
+        uint32_t acc[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]), "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7]),
+              "=r"(acc[8]), "=r"(acc[9]), "=r"(acc[10]), "=r"(acc[11]), "=r"(acc[12]), "=r"(acc[13]), "=r"(acc[14]), "=r"(acc[15])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (sp != 0) {
+          float* mine = p.partial + ((size_t)(tile * (p.splits - 1) + sp - 1) * p.m_pad + c0) * 128 + row_in_tile;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int b = c0 + j;
-          if (b < p.m) p.out[(size_t)b * p.n + row] = from_float<false>(__uint_as_float(acc[j]));
+          for (int j = 0; j < 16; ++j) __stcg(mine + j * 128, __uint_as_float(acc[j]));
+        } else {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(acc[j]);
+          for (int o = 1; o < p.splits; ++o) {  // share order; the sixteen loads of a share are independent
+            const float* theirs = p.partial + ((size_t)(tile * (p.splits - 1) + o - 1) * p.m_pad + c0) * 128 + row_in_tile;
+            float t[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) t[j] = __ldcg(theirs + j * 128);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += t[j];
+          }
+          if (row < p.n) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int b = c0 + j;
+              if (b < p.m) p.out[(size_t)b * p.n + row] = from_float<false>(v[j]);
+            }
+          }
+        }
+      }
+      if (p.splits > 1) {
+        __threadfence();
+        // the four epilogue warps meet on a named barrier, then one thread publishes
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (dw == 0 && lane == 0) {
+          if (sp != 0) {
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + tile * kTcMaxSplits + sp), "r"(tag) : "memory");
+          } else {
+            p.uses[tile] = tag;  // the next use of this tile waits for tags one higher
+          }
         }
       }
     }
@@ -365,23 +428,40 @@ int launch_tc(TcParams p, const void* lut_host, const CUtensorMap& map, int tile
 
 // Batches above 16 rows, bf16, 4- or 8-bit codes.  Called by fdk_linear_lut.
 int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out, int m, int n,
-                int k, int bits, int* status, cudaStream_t stream) {
+                int k, int bits, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
   EncodeTiledFn encode = nullptr;
   if (int st = encode_fn(&encode)) return st;
   const TiledDims d = tiled_dims(n, k, bits);
+  const int tiles = (n + kTcTileRows - 1) / kTcTileRows;
+  const int k_blocks = k / kBlock;
+  // few tiles: several CTAs share a tile, each with its own range of 64-column blocks, so that
+  // the whole GPU is busy; all of them must be resident at once (the owner waits for the others)
+  int splits = 1;
+  if (tiles * 2 <= sm_count) {
+    splits = sm_count / tiles;
+    if (splits > kTcMaxSplits) splits = kTcMaxSplits;
+    if (splits > k_blocks / 4) splits = k_blocks / 4;
+    if (splits < 1) splits = 1;
+  }
+  if (splits > 1 && (workspace_bytes < kTcPartialOffset + (size_t)tiles * (splits - 1) * kTcPartialTileBytes || tiles > 2048))
+    splits = 1;  // a small (e.g. built-in) workspace: every CTA finishes its tile alone
   for (int m0 = 0; m0 < m; m0 += 256) {
     const int mc = (m - m0) < 256 ? (m - m0) : 256;
     TcParams p{};
     p.tiled = (const uint8_t*)tiled;
     p.lut = lut;
     p.out = (uint16_t*)out + (size_t)m0 * n;
-    p.status = status;
+    p.status = (int*)workspace + kStatusWord;
     p.m = mc;
     p.m_pad = (mc + 15) / 16 * 16;
     p.n = n;
     p.k = k;
     p.row_tiles = d.row_tiles;
-    p.k_blocks = k / kBlock;
+    p.k_blocks = k_blocks;
+    p.splits = splits;
+    p.flags = (int*)((uint8_t*)workspace + kTcFlagsOffset);
+    p.uses = (int*)((uint8_t*)workspace + kTcUsesOffset);
+    p.partial = (float*)((uint8_t*)workspace + kTcPartialOffset);
     uint32_t cols = 32;
     while ((int)cols < p.m_pad) cols *= 2;
     p.tmem_cols = cols;
@@ -394,8 +474,8 @@ int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* l
                         strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     FDK_CHECK_ARG(r == CUDA_SUCCESS, FDK_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
-    const int tiles = (n + kTcTileRows - 1) / kTcTileRows;
-    int st = (bits == 4) ? launch_tc<4>(p, lut_host, map, tiles, stream) : launch_tc<8>(p, lut_host, map, tiles, stream);
+    int st = (bits == 4) ? launch_tc<4>(p, lut_host, map, tiles * splits, stream)
+                         : launch_tc<8>(p, lut_host, map, tiles * splits, stream);
     if (st) return st;
   }
   return FDK_OK;

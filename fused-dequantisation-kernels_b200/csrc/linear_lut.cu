@@ -40,7 +40,6 @@ namespace {
 
 constexpr int kMaxStages = 4;
 
-constexpr int kStatusWord = 4095;        // counters[kStatusWord] collects device-side error bits
 constexpr int kStatusTimeout = 1;        // a bounded wait on a copy barrier ran out
 constexpr int kStatusSmemLayout = 2;     // shared window base differs from what the host planned for
 
@@ -173,20 +172,6 @@ struct EpilogueSync {
 };
 
 constexpr uint32_t kSpinLimit = 1u << 24;  // polls of a memory word before giving up
-
-__device__ __forceinline__ uint2 ld_relaxed_v2(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_v2(uint2* p, uint2 v) {
-  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
-}
-__device__ __forceinline__ int ld_relaxed_s32(const int* p) {
-  int v;
-  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 // Run by one warp.  `slots` is the slot set of this row tile: per warp one block of
 // E = NB * 4 * SW floats laid out [sub-tile][n-tile][t][g][4].  Plain loops on purpose (this
@@ -598,7 +583,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
 }
 
 // ---- host side ----------------------------------------------------------------------
-constexpr size_t kCounterBytes = 16384;  // 4095 row-tile counters + 1 status word
 
 }  // namespace
 
@@ -796,7 +780,7 @@ extern "C" int fdk_workspace_size(size_t* bytes_host) {
   FDK_CHECK_ARG(bytes_host != nullptr, FDK_ERR_BAD_ARG, "bytes_host is null");
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
-  *bytes_host = kCounterBytes + (size_t)di.sm_count * 1024 * sizeof(uint2);
+  *bytes_host = kWorkspaceBytes;
   return FDK_OK;
 }
 
@@ -832,6 +816,7 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   FDK_CHECK_ARG(di.cc_major == 10, FDK_ERR_ARCH, "device has compute capability %d.%d", di.cc_major, di.cc_minor);
   const TiledDims d = tiled_dims(n, k, bits);
   FDK_CHECK_ARG(d.row_tiles < kStatusWord, FDK_ERR_SHAPE, "n=%d exceeds %d rows", n, kStatusWord * kTileRows);
+  FDK_CHECK_ARG(di.sm_count <= 160, FDK_ERR_ARCH, "%d multiprocessors: the workspace layout provides for 160", di.sm_count);
   const size_t need = kCounterBytes + (size_t)di.sm_count * 1024 * sizeof(uint2);
   FDK_CHECK_ARG(workspace != nullptr && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
                 FDK_ERR_WORKSPACE, "workspace must be a 16-byte aligned buffer of at least %zu bytes", need);
@@ -852,7 +837,8 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   p.trace = g_trace;
 #endif
   if (m > 16 && dtype == FDK_DTYPE_BF16 && (bits == 4 || bits == 8)) {
-    return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, p.counters + kStatusWord, (cudaStream_t)stream);
+    return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, workspace, workspace_bytes, di.sm_count,
+                       (cudaStream_t)stream);
   }
   for (int m0 = 0; m0 < m; m0 += 16) {
     p.m = (m - m0) < 16 ? (m - m0) : 16;

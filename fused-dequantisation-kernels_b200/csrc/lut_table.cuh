@@ -186,9 +186,38 @@ __device__ __forceinline__ void fill_table(uint32_t table_base, WordFn word) {
   fill_table<BITS>(table_base, (int)blockDim.x, word, (int)threadIdx.x);
 }
 
+__device__ __forceinline__ uint2 ld_relaxed_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_v2(uint2* p, uint2 v) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ int ld_relaxed_s32(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+
+// ---- workspace layout (bytes) -----------------------------------------------------------------
+//   [0, 16 KB)            use counts of split row tiles (4095 ints) + the status word
+//   [16 KB, kGemvEnd)     tagged partial sums of the GEMV kernel, 8 KB per SM, room for 160 SMs
+//   then 8 KB of flags and 8 KB of tile use counts of the tensor-core GEMM
+//   then its fp32 partial tiles: up to 148 tiles of 128 rows x 256 batch columns
+constexpr size_t kCounterBytes = 16384;
+constexpr int kStatusWord = 4095;
+constexpr size_t kGemvEnd = kCounterBytes + (size_t)160 * 1024 * sizeof(uint2);
+constexpr size_t kTcFlagsOffset = kGemvEnd;
+constexpr size_t kTcUsesOffset = kGemvEnd + 8192;
+constexpr size_t kTcPartialOffset = kGemvEnd + 16384;
+constexpr size_t kTcPartialTileBytes = (size_t)128 * 256 * sizeof(float);
+constexpr size_t kWorkspaceBytes = kTcPartialOffset + 148 * kTcPartialTileBytes;
+
 // Tensor-core GEMM for batches above 16 rows (gemm_lut_tc.cu): bf16, 4- or 8-bit codes.
 int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out, int m, int n,
-                int k, int bits, int* status, cudaStream_t stream);
+                int k, int bits, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
 
 // The dynamic shared memory address seen by kernels without static shared memory, asked of
 // the device once (linear_lut.cu).
