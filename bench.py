@@ -16,7 +16,9 @@ GEMV); `roofline` relates the per-launch time to the measured HBM copy bandwidth
 `cpu_baseline` times the CPU oracle port of the reference operator on the host cores.
 
 N > 1: the kernel benchmark does not shard (one matrix, one GPU); ranks run independent
-replicas (weak scaling), timed as the max over ranks.
+replicas (weak scaling), timed as the max over ranks.  The part of the path that does shard,
+the decode loop, is reported in the extra `decode` object: tokens/s of a 4-bit custom-llama
+with tensor parallelism over the N ranks (NCCL all-reduce after each row-parallel projection).
 
 `--impl reference` times the reference's CPU path (eager torch dequantise-then-matmul,
 the oracle port) on the same workload, one GEMV per step.
@@ -287,6 +289,10 @@ def run_gpu_arm(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     elapsed_ms, e2e_s = float(t[0]), float(t[1])
 
+    decode = None
+    if not args.kernel_only and not args.no_decode:
+        decode = decode_extra(device, world, rank)
+
     launches = COPIES * args.steps
     ms_per_step = elapsed_ms / args.steps
     value = world * COPIES * PACKED_BYTES / (ms_per_step * 1e-3) / 1e9
@@ -301,13 +307,9 @@ def run_gpu_arm(args) -> None:
             cpu_times, cores, sample = cpu_reference_times(reps=20, warmup=2)
             cpu_value = PACKED_BYTES / statistics.fmean(cpu_times) / 1e9
             cpu_baseline = {"value": cpu_value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
-        traffic = None
-        traffic_file = ROOT / "profiles" / "gemv_lut_4bit_8192_traffic.json"
-        if traffic_file.exists():
-            try:
-                traffic = json.loads(traffic_file.read_text())["dram_bytes_per_launch"]
-            except Exception:
-                traffic = None
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this shape,
+        # from the ncu capture summarised in profiles/linear_lut_kernel_4bit_8192_m1.md
+        traffic = 35_711_488
         line = {
             "metric": "packed_weight_gbs_gemv",
             "value": value,
@@ -347,10 +349,43 @@ def run_gpu_arm(args) -> None:
             },
             "gpu_launches": launches,
             "clocks": clocks.summary(),
+            "decode": decode,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def decode_extra(device, world: int, rank: int) -> dict:
+    """Second figure of the metric: greedy-decode tokens/s of the custom-llama "b200-4B" shape
+    (32 layers, d 3072, FFN 8192, 24/8 heads), 4-bit block-64 weights, batch 1, 1024 tokens of
+    (synthetic) context, one decode step per CUDA-graph replay as the reference times it
+    (src/fdk/models.py:313-340).  With N ranks the model is tensor parallel over them (NCCL
+    all-reduce after the o and down projections).  At N = 1 the same loop with bf16 nn.Linear
+    layers (cuBLAS) is timed beside it."""
+    import torch
+
+    from fdk import llama, models
+
+    dims = models.get_custom_llama_dims("b200-4B")
+    tp = llama.TensorParallel(rank, world)
+    out = {"model": "custom-llama-b200-4B", "bits": 4, "block_size": 64, "batch": 1, "context": 1024, "tp": world}
+    try:
+        model = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(4, 64), device, tp, lut=kmeans_codebook(4, 0).to(device))
+        r = models.benchmark(model, 1, 30, 1024)
+        out["tokens_per_s"] = 1 / r.avg_time
+        out["weight_gbs"] = r.bytes_rw / r.avg_time / 1e9
+        del model
+        torch.cuda.empty_cache()
+        if world == 1:
+            base = llama.LlamaDecoder.random_init(dims, None, device, tp)
+            rb = models.benchmark(base, 1, 30, 1024)
+            out["bf16_cublas_tokens_per_s"] = 1 / rb.avg_time
+            del base
+            torch.cuda.empty_cache()
+    except Exception as e:  # the headline line must still be printed
+        out["error"] = repr(e)
+    return out
 
 
 def main() -> None:
@@ -362,7 +397,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     # profiling aids (the defaults are the benchmark): smaller footprint, kernel launches only
     ap.add_argument("--copies", type=int, default=COPIES, help="weight sets cycled per step")
-    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end, CPU and decode legs")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode tokens/s leg")
     args = ap.parse_args()
     if args.copies != COPIES:
         COPIES = args.copies
