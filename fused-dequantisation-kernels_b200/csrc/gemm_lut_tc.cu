@@ -365,34 +365,26 @@ int encode_fn(EncodeTiledFn* out) {
 
 inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
-// Places the stage buffers in the two free regions around the 64 KB-aligned table (below it and
-// above it), largest first.  Returns the dynamic shared memory size, or 0 if `stages` do not fit.
+// Shared memory: barriers, the table, then the stage buffers (1024-byte aligned for the
+// swizzled tiles).  Returns the dynamic size, or 0 if `stages` do not fit in `limit`.
 template <int BITS>
 size_t plan_tc_smem(uint32_t base, uint32_t limit, int stages, TcParams& p) {
   using L = Layout<BITS>;
   using T = Table<BITS>;
-  uint32_t lo = round_up(base, 1024);
+  uint32_t cursor = round_up(base, 128);
   p.smem_base = base;
-  p.bar_addr = lo;
-  p.tmem_slot_addr = lo + 8 * (3 * kTcMaxStages + 1);
-  lo += 1024;
-  const uint32_t table = round_up(lo, 65536);
-  p.table_addr = table;
-  uint32_t hi = table + T::kBytes;
-  const uint32_t end = base + limit;
-  auto place = [&](uint32_t bytes, uint32_t align, uint32_t* out) -> bool {
-    uint32_t a = round_up(lo, align);
-    if (a + bytes <= table) { *out = a; lo = a + bytes; return true; }
-    a = round_up(hi, align);
-    if (a + bytes <= end) { *out = a; hi = a + bytes; return true; }
-    return false;
-  };
+  p.bar_addr = cursor;
+  p.tmem_slot_addr = cursor + 8 * (3 * kTcMaxStages + 1);
+  cursor += 256;
+  p.table_addr = cursor;
+  cursor += T::kBytes;
   p.stages = stages;
   const uint32_t b_bytes = (uint32_t)p.m_pad * 128;
-  for (int s = 0; s < stages; ++s) if (!place(b_bytes, 1024, &p.b_addr[s])) return 0;
-  for (int s = 0; s < stages; ++s) if (!place(16384, 1024, &p.a_addr[s])) return 0;
-  for (int s = 0; s < stages; ++s) if (!place(2 * L::kSlabBytes, 128, &p.c_addr[s])) return 0;
-  return hi - base;
+  cursor = round_up(cursor, 1024);
+  for (int s = 0; s < stages; ++s) { p.b_addr[s] = cursor; cursor += b_bytes; }
+  for (int s = 0; s < stages; ++s) { p.a_addr[s] = cursor; cursor += 16384; }
+  for (int s = 0; s < stages; ++s) { p.c_addr[s] = cursor; cursor += round_up(2 * L::kSlabBytes, 128); }
+  return (cursor - base <= limit) ? cursor - base : 0;
 }
 
 template <int BITS>

@@ -134,14 +134,14 @@ __device__ __forceinline__ void build_fragments(const uint4 (&code)[Layout<BITS>
     for (int f = 0; f < 16; ++f) {
       const int o = 6 * f;  // bit offset of the field
       const int wi = o >> 5, sh = o & 31;
-      uint32_t v;  // field moved to bits 8..13
+      uint32_t v;  // field moved to bits 7..12: field * 128, the table stride
       if (sh + 6 <= 32) {
-        v = (sh >= 8) ? (w[wi] >> (sh - 8)) : (w[wi] << (8 - sh));
+        v = (sh >= 7) ? (w[wi] >> (sh - 7)) : (w[wi] << (7 - sh));
       } else {
-        v = __funnelshift_r(w[wi], w[wi + 1], sh - 8);
+        v = __funnelshift_r(w[wi], w[wi + 1], sh - 7);
       }
       const int p = f & 7, half = f >> 3;
-      a[p >> 1][(p & 1) * 2 + half] = lut32((v & 0x3F00u) | lane_base);
+      a[p >> 1][(p & 1) * 2 + half] = lut32((v & 0x1F80u) + lane_base);
     }
   }
 }
@@ -284,7 +284,7 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
 constexpr int kXRowPad = 16;  // x rows in a stage are 16 bytes apart from a 128-byte multiple: no bank conflicts
 
 template <int BITS, int NB, int WARPS, bool FP16>
-__global__ void __launch_bounds__(WARPS * 32, 1)
+__global__ void __launch_bounds__(WARPS * 32, 2)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
   using T = Table<BITS>;
@@ -645,26 +645,6 @@ size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
   p.xres_row = xres_row;
   p.xres_addr = resident ? cursor : 0;
   cursor += xres_bytes;
-  if (T::kAligned64K) {
-    const uint32_t table = align_up(cursor, 65536);
-    p.table_addr = table;
-    uint32_t above = table + T::kBytes;
-    // below the table: reduction slots if they fit, then as many stages as fit
-    if (cursor + slot_bytes <= table) {
-      p.slots_addr = cursor;
-      cursor += slot_bytes;
-    } else {
-      p.slots_addr = above;
-      above += slot_bytes;
-    }
-    cursor = align_up(cursor, 128);
-    p.stage_a_addr = cursor;
-    p.stage_a_count = (table - cursor) / stage_bytes;
-    if (p.stage_a_count > n_stages) p.stage_a_count = n_stages;
-    p.stage_b_addr = above;
-    above += (n_stages - p.stage_a_count) * stage_bytes;
-    return above - base;
-  }
   p.slots_addr = cursor;
   cursor = align_up(cursor + slot_bytes, 128);
   p.table_addr = cursor;
@@ -701,10 +681,13 @@ int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int 
   return FDK_OK;
 }
 
-// Picks the widest CTA that still leaves two ring stages per warp (one being consumed, one
-// in flight); failing that, the widest that fits at all.
+// CTAs are sized so that two fit on an SM (12 or 8 warps, at most half the shared memory):
+// with one CTA per SM the other half is free for the NEXT kernel on the stream, which under
+// programmatic dependent launch starts its table fill and weight prefetch while this one is
+// still running; a large matrix takes both halves itself (two CTAs per SM).  A plan that does
+// not fit half an SM (the 1-bit table alone is 128 KB) gets the whole SM.
 template <int BITS, int NB, bool FP16>
-int launch(LinearParams p, const void* lut_host, int grid, unsigned flags, cudaStream_t stream) {
+int launch(LinearParams p, const void* lut_host, int sm_count, unsigned flags, cudaStream_t stream) {
   InlineLut<BITS> inl;
   if (lut_host != nullptr) {
     memcpy(inl.w, lut_host, sizeof(inl.w));
@@ -716,12 +699,13 @@ int launch(LinearParams p, const void* lut_host, int grid, unsigned flags, cudaS
   if (int st = dynamic_smem_base(&base)) return st;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
-  constexpr int kWide = (NB == 1) ? 24 : 16;
-  constexpr int kMid = (NB == 1) ? 16 : 8;
-  constexpr int kNarrow = (NB == 1) ? 8 : 4;
-  const int widths[3] = {kWide, kMid, kNarrow};
+  constexpr int kWide = (NB == 1) ? 12 : 8;
+  constexpr int kNarrow = 4;
+  const size_t half_sm = ((size_t)di.max_smem_optin + 1024) / 2 - 1024;  // two CTAs, 1 KB reserved each
+  const int widths[2] = {kWide, kNarrow};
   int best_w = 0, best_s = 0;
   size_t best_smem = 0;
+  bool two_per_sm = true;
 #ifdef FDK_TRACE
   static const char* env_s = getenv("FDK_STAGES");
   static const char* env_w = getenv("FDK_WARPS");
@@ -731,26 +715,37 @@ int launch(LinearParams p, const void* lut_host, int grid, unsigned flags, cudaS
     best_smem = plan_smem<BITS, NB>(base, want_w, atoi(env_s), q);
     best_w = want_w;
     best_s = atoi(env_s);
+    two_per_sm = best_smem <= half_sm;
   }
 #endif
-  for (int want = 2; want >= 1 && !best_w; --want) {
-    for (int wi = 0; wi < 3 && !best_w; ++wi) {
-      for (int s = kMaxStages; s >= want; --s) {
-        LinearParams q = p;
-        size_t smem = plan_smem<BITS, NB>(base, widths[wi], s, q);
-        if (smem <= (size_t)di.max_smem_optin) {
-          best_w = widths[wi];
-          best_s = s;
-          best_smem = smem;
-          break;
+  for (int pass = 0; pass < 2 && !best_w; ++pass) {  // first half an SM, then all of it
+    const size_t limit = pass == 0 ? half_sm : (size_t)di.max_smem_optin;
+    for (int want = 2; want >= 1 && !best_w; --want) {
+      for (int wi = 0; wi < 2 && !best_w; ++wi) {
+        for (int s = kMaxStages; s >= want; --s) {
+          LinearParams q = p;
+          size_t smem = plan_smem<BITS, NB>(base, widths[wi], s, q);
+          if (smem <= limit) {
+            best_w = widths[wi];
+            best_s = s;
+            best_smem = smem;
+            two_per_sm = pass == 0;
+            break;
+          }
         }
       }
     }
   }
   FDK_CHECK_ARG(best_w != 0, FDK_ERR_CUDA, "no shared-memory plan fits %d bytes", di.max_smem_optin);
   plan_smem<BITS, NB>(base, best_w, best_s, p);
+  // grid: one CTA per SM, or two when each would still have plenty of slabs (NB == 1 only: the
+  // workspace holds one 4 KB partial per CTA for up to 320 CTAs)
+  int grid = sm_count;
+  if (two_per_sm && NB == 1 && p.total >= 2 * best_w * sm_count) grid = 2 * sm_count;
+  if (grid > p.total) grid = p.total;
+  p.base = p.total / grid;
+  p.rem = p.total % grid;
   if (best_w == kWide) return launch_variant<BITS, NB, kWide, FP16>(p, inl, best_smem, grid, flags, stream);
-  if (best_w == kMid) return launch_variant<BITS, NB, kMid, FP16>(p, inl, best_smem, grid, flags, stream);
   return launch_variant<BITS, NB, kNarrow, FP16>(p, inl, best_smem, grid, flags, stream);
 }
 
@@ -830,9 +825,7 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   p.k = k;
   p.k_slabs = d.k_slabs;
   p.total = d.row_tiles * d.k_slabs;
-  const int grid = p.total < di.sm_count ? p.total : di.sm_count;
-  p.base = p.total / grid;
-  p.rem = p.total % grid;
+  const int grid = di.sm_count;  // the launcher turns this into one or two CTAs per SM
 #ifdef FDK_TRACE
   p.trace = g_trace;
 #endif

@@ -116,18 +116,16 @@ __device__ __forceinline__ uint32_t word_at(const uint4& v, int i) {
 }
 
 // ---- lookup tables in shared memory -----------------------------------------
-// Per-lane replicas: entry e of lane l lives at  base + e * kStride + l * kEntryBytes,
-// so that the 32 lanes of a warp always hit 32 different banks (or, for 8/16-byte
-// entries, every quarter / half warp does).  For the 256-byte stride the base is
-// 64 KB aligned inside the shared window: the address of entry `byte` is then the
-// lane's base with `byte` dropped into bits 8..15, which is a single PRMT.
+// Per-lane replicas: entry e of lane l lives at  base + e * kStride + l * kEntryBytes with
+// kStride = 32 * kEntryBytes, so that the 32 lanes of a warp always hit 32 different banks
+// (or, for 8/16-byte entries, every quarter / half warp does) whatever code bytes they hold.
+// A lookup address is one PRMT (extract the code byte) and one shift-add.
 template <int BITS>
 struct Table {
   static constexpr int kEntries = (BITS == 3) ? 64 : 256;
   static constexpr int kEntryBytes = (BITS == 2) ? 8 : (BITS == 1 ? 16 : 4);
-  static constexpr int kStride = (BITS == 1) ? 512 : 256;
-  static constexpr int kBytes = kEntries * kStride;
-  static constexpr bool kAligned64K = (BITS != 1);
+  static constexpr int kStride = 32 * kEntryBytes;
+  static constexpr int kBytes = kEntries * kStride;  // 32 KB (4- and 8-bit), 64 KB, 128 KB (1-bit), 8 KB (3-bit)
 };
 
 // The byte table may travel inside the kernel parameters (no memory latency at all) or be
@@ -173,12 +171,8 @@ __device__ __forceinline__ void fill_table(uint32_t table_base, int threads, Wor
 // Address of the table entry selected by byte J of `w` (lane_base = table base + lane offset).
 template <int BITS, int J>
 __device__ __forceinline__ uint32_t entry_addr(uint32_t w, uint32_t lane_base) {
-  if constexpr (BITS == 1) {
-    uint32_t b = prmt<0x4404u | (J << 4)>(w, 0u);  // byte << 8
-    return lane_base + (b << 1);                    // stride 512
-  } else {
-    return prmt<0x7604u | (J << 4)>(w, lane_base);  // bits 8..15 <- byte
-  }
+  const uint32_t b = prmt<0x4440u | J>(w, 0u);  // the byte alone
+  return lane_base + b * (uint32_t)Table<BITS>::kStride;
 }
 
 template <int BITS, class WordFn>
