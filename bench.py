@@ -360,21 +360,32 @@ def decode_extra(device, world: int, rank: int) -> dict:
     """Second figure of the metric: greedy-decode tokens/s of the custom-llama "b200-4B" shape
     (32 layers, d 3072, FFN 8192, 24/8 heads), 4-bit block-64 weights, batch 1, 1024 tokens of
     (synthetic) context, one decode step per CUDA-graph replay as the reference times it
-    (src/fdk/models.py:313-340).  With N ranks the model is tensor parallel over them (NCCL
-    all-reduce after the o and down projections).  At N = 1 the same loop with bf16 nn.Linear
-    layers (cuBLAS) is timed beside it."""
+    (src/fdk/models.py:313-340).  With N ranks the model is tensor parallel over them: the o and
+    down projections push their partial sums to every rank from the kernel and the next RMSNorm
+    adds them; the same run with NCCL all-reduces instead is timed beside it.  At N = 1 the
+    same loop with bf16 nn.Linear layers (cuBLAS) is timed beside it."""
     import torch
 
     from fdk import llama, models
 
     dims = models.get_custom_llama_dims("b200-4B")
-    tp = llama.TensorParallel(rank, world)
+    tp = llama.TensorParallel(rank, world, fused=True)
     out = {"model": "custom-llama-b200-4B", "bits": 4, "block_size": 64, "batch": 1, "context": 1024, "tp": world}
     try:
         model = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(4, 64), device, tp, lut=kmeans_codebook(4, 0).to(device))
         r = models.benchmark(model, 1, 30, 1024)
         out["tokens_per_s"] = 1 / r.avg_time
         out["weight_gbs"] = r.bytes_rw / r.avg_time / 1e9
+        if world > 1:
+            from fdk import native
+
+            out["tp_reduce"] = "fused push" if model.exchange is not None else "nccl"
+            if model.exchange is not None:
+                out["exchange_status"] = native.tp_exchange_status(model.exchange)
+            model.close()
+            model.tp = llama.TensorParallel(rank, world)
+            rn = models.benchmark(model, 1, 30, 1024)
+            out["nccl_tokens_per_s"] = 1 / rn.avg_time
         del model
         torch.cuda.empty_cache()
         if world == 1:

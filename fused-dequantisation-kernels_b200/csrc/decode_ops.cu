@@ -6,7 +6,10 @@
 // transformers' LlamaForCausalLM (src/fdk/models.py:238-251); the formulas below follow that
 // model's definition (RMSNorm in fp32 with the weight applied after the cast, rotate-half
 // rotary embedding with cos/sin rounded to the activation type).
+#include <cstring>
+
 #include "fdk_common.cuh"
+#include "tp_exchange.cuh"
 
 namespace fdk {
 namespace {
@@ -41,23 +44,98 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Where the partial sums of a tensor-parallel push are found (this rank's exchange buffer).
+struct ReduceSource {
+  const uint2* stage;  // words {two partial sums, tag} [2][tp][slot / 2]
+  uint32_t* seq;       // reduces completed so far
+  int* done;           // CTAs of this reduce that have finished
+  int* status;
+  long long slot;
+  int tp;
+};
+
+__device__ __forceinline__ uint4 ld_words(const uint2* p) {  // two staging words
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// Reads the two words again until both carry `tag` (bounded: two seconds).
+__device__ __forceinline__ void settle(uint4& v, const uint2* p, uint32_t tag, int* status) {
+  unsigned long long t0 = 0;
+  for (uint32_t i = 0; v.y != tag || v.w != tag; ++i) {
+    v = ld_words(p);
+    if ((i & 63u) == 63u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) {
+        atomicOr(status, 1);
+        v = make_uint4(0u, tag, 0u, tag);
+      }
+    }
+  }
+}
+
 // out[row] = weight * bf16(h[row] * rsqrt(mean(h[row]^2) + eps)), with h += delta first when
-// delta is given (h is the residual stream, updated in place).
+// delta is given (h is the residual stream, updated in place).  REDUCE: delta is the sum over
+// ranks (fp32, rank order, rounded to bf16) of the partial sums of the latest push, after
+// every rank's arrival flag has been seen (bounded wait).
+template <bool REDUCE>
 __global__ void rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ delta,
                                const uint16_t* __restrict__ weight, uint16_t* __restrict__ out, int width,
-                               float eps) {
+                               float eps, ReduceSource src) {
   extern __shared__ float row_cache[];  // width floats
   __shared__ float partial[32];
   pdl_prologue();
   const int row = blockIdx.x;
   uint16_t* hr = h + (size_t)row * width;
   const uint16_t* dr = delta ? delta + (size_t)row * width : nullptr;
+  uint32_t c = 0;           // number of the push being reduced
+  const uint2* words = nullptr;
+  if constexpr (REDUCE) {
+    c = *reinterpret_cast<const volatile uint32_t*>(src.seq);
+    words = src.stage + ((size_t)(c & 1u) * src.tp * src.slot + (size_t)row * width) / 2;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
     uint4 hv = *reinterpret_cast<const uint4*>(hr + i);
     uint32_t* hw = reinterpret_cast<uint32_t*>(&hv);
-    if (dr) {
-      uint4 dv = *reinterpret_cast<const uint4*>(dr + i);
+    if (dr || REDUCE) {
+      uint4 dv;
+      if constexpr (REDUCE) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4 v[2 * kTpMaxRanks];  // all ranks' words in flight at once
+#pragma unroll
+        for (int j = 0; j < kTpMaxRanks; ++j) {
+          if (j < src.tp) {
+            const uint2* w = words + ((size_t)j * src.slot + i) / 2;
+            v[2 * j] = ld_words(w);
+            v[2 * j + 1] = ld_words(w + 2);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kTpMaxRanks; ++j) {  // added in rank order
+          if (j < src.tp) {
+            const uint2* w = words + ((size_t)j * src.slot + i) / 2;
+            settle(v[2 * j], w, c + 1u, src.status);
+            settle(v[2 * j + 1], w + 2, c + 1u, src.status);
+            const uint4 lo = v[2 * j], hi = v[2 * j + 1];
+            acc[0] += pair_lo<false>(lo.x); acc[1] += pair_hi<false>(lo.x);
+            acc[2] += pair_lo<false>(lo.z); acc[3] += pair_hi<false>(lo.z);
+            acc[4] += pair_lo<false>(hi.x); acc[5] += pair_hi<false>(hi.x);
+            acc[6] += pair_lo<false>(hi.z); acc[7] += pair_hi<false>(hi.z);
+          }
+        }
+        uint32_t* dwm = reinterpret_cast<uint32_t*>(&dv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          dwm[j] = (uint32_t)from_float<false>(acc[2 * j]) | ((uint32_t)from_float<false>(acc[2 * j + 1]) << 16);
+      } else {
+        dv = *reinterpret_cast<const uint4*>(dr + i);
+      }
       const uint32_t* dw = reinterpret_cast<const uint32_t*>(&dv);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -99,6 +177,15 @@ __global__ void rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restr
       ow[j] = (uint32_t)from_float<false>(a) | ((uint32_t)from_float<false>(b) << 16);
     }
     *reinterpret_cast<uint4*>(orow + i) = ov;
+  }
+  if constexpr (REDUCE) {  // the last CTA to get here counts this reduce as done
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (atomicAdd(src.done, 1) == (int)gridDim.x - 1) {
+        *src.done = 0;
+        *reinterpret_cast<volatile uint32_t*>(src.seq) = c + 1u;
+      }
+    }
   }
 }
 
@@ -171,8 +258,8 @@ __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* 
 
 using namespace fdk;
 
-extern "C" int fdk_rmsnorm(void* h, const void* delta, const void* weight, void* out, int rows, int width,
-                           float eps, void* stream) {
+static int rmsnorm_launch(void* h, const void* delta, const fdk_tp_exchange* ex, const void* weight, void* out,
+                          int rows, int width, float eps, void* stream) {
   FDK_CHECK_ARG(h && weight && out, FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(rows > 0 && width > 0 && width % 8 == 0 && width <= 16384, FDK_ERR_SHAPE,
                 "rows=%d, width=%d (width must be a multiple of 8, at most 16384)", rows, width);
@@ -184,12 +271,92 @@ extern "C" int fdk_rmsnorm(void* h, const void* delta, const void* weight, void*
     int dev = 0;
     FDK_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {
-      FDK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      FDK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      FDK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
       configured[dev & 63] = true;
     }
   }
-  return launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream, (uint16_t*)h,
-                    (const uint16_t*)delta, (const uint16_t*)weight, (uint16_t*)out, width, eps);
+  ReduceSource src{};
+  if (ex == nullptr) {
+    return launch_pdl(rmsnorm_kernel<false>, dim3(rows), dim3(256), smem, (cudaStream_t)stream, (uint16_t*)h,
+                      (const uint16_t*)delta, (const uint16_t*)weight, (uint16_t*)out, width, eps, src);
+  }
+  FDK_CHECK_ARG(ex->tp >= 1 && ex->tp <= kTpMaxRanks && ex->rank >= 0 && ex->rank < ex->tp, FDK_ERR_BAD_ARG,
+                "tp=%d, rank=%d", ex->tp, ex->rank);
+  FDK_CHECK_ARG(ex->slot_elems % 8 == 0 && (long long)rows * width <= ex->slot_elems, FDK_ERR_SHAPE,
+                "rows=%d x width=%d exceeds slots of %lld elements", rows, width, ex->slot_elems);
+  uint8_t* local = (uint8_t*)ex->buffers[ex->rank];
+  FDK_CHECK_ARG(local != nullptr && ((uintptr_t)local & 255) == 0, FDK_ERR_ALIGN,
+                "the exchange buffer must be a 256-byte aligned device pointer");
+  src.stage = (const uint2*)(local + kTpStageOffset);
+  src.seq = (uint32_t*)(local + kTpSeqOffset);
+  src.done = (int*)(local + kTpDoneOffset);
+  src.status = (int*)(local + kTpStatusOffset);
+  src.slot = ex->slot_elems;
+  src.tp = ex->tp;
+  return launch_pdl(rmsnorm_kernel<true>, dim3(rows), dim3(256), smem, (cudaStream_t)stream, (uint16_t*)h,
+                    (const uint16_t*)nullptr, (const uint16_t*)weight, (uint16_t*)out, width, eps, src);
+}
+
+extern "C" int fdk_rmsnorm(void* h, const void* delta, const void* weight, void* out, int rows, int width,
+                           float eps, void* stream) {
+  return rmsnorm_launch(h, delta, nullptr, weight, out, rows, width, eps, stream);
+}
+
+extern "C" int fdk_rmsnorm_reduce(void* h, const fdk_tp_exchange* ex, const void* weight, void* out, int rows,
+                                  int width, float eps, void* stream) {
+  FDK_CHECK_ARG(ex != nullptr, FDK_ERR_BAD_ARG, "exchange is null");
+  return rmsnorm_launch(h, nullptr, ex, weight, out, rows, width, eps, stream);
+}
+
+// ---- exchange buffers: device allocations shared between the ranks' processes by CUDA IPC ----
+extern "C" size_t fdk_tp_exchange_bytes(int tp, long long slot_elems) {
+  if (tp < 1 || tp > kTpMaxRanks || slot_elems <= 0) return 0;
+  return tp_exchange_bytes(tp, slot_elems);
+}
+
+extern "C" int fdk_tp_buffer_create(size_t bytes, void** ptr_host, unsigned char* handle_host) {
+  FDK_CHECK_ARG(bytes > 0 && ptr_host && handle_host, FDK_ERR_BAD_ARG, "null pointer or zero size");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are exchanged as 64 bytes");
+  void* ptr = nullptr;
+  FDK_CUDA(cudaMalloc(&ptr, bytes));
+  FDK_CUDA(cudaMemset(ptr, 0, bytes));
+  FDK_CUDA(cudaDeviceSynchronize());
+  cudaIpcMemHandle_t handle;
+  FDK_CUDA(cudaIpcGetMemHandle(&handle, ptr));
+  memcpy(handle_host, &handle, sizeof(handle));
+  *ptr_host = ptr;
+  return FDK_OK;
+}
+
+extern "C" int fdk_tp_buffer_open(const unsigned char* handle_host, void** ptr_host) {
+  FDK_CHECK_ARG(handle_host && ptr_host, FDK_ERR_BAD_ARG, "null pointer");
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, handle_host, sizeof(handle));
+  void* ptr = nullptr;
+  FDK_CUDA(cudaIpcOpenMemHandle(&ptr, handle, cudaIpcMemLazyEnablePeerAccess));
+  *ptr_host = ptr;
+  return FDK_OK;
+}
+
+extern "C" int fdk_tp_buffer_close(void* ptr) {
+  FDK_CHECK_ARG(ptr != nullptr, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CUDA(cudaIpcCloseMemHandle(ptr));
+  return FDK_OK;
+}
+
+extern "C" int fdk_tp_buffer_destroy(void* ptr) {
+  FDK_CHECK_ARG(ptr != nullptr, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CUDA(cudaFree(ptr));
+  return FDK_OK;
+}
+
+extern "C" int fdk_tp_exchange_status(const fdk_tp_exchange* ex, int* status_host) {
+  FDK_CHECK_ARG(ex && status_host && ex->rank >= 0 && ex->rank < kTpMaxRanks && ex->buffers[ex->rank],
+                FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CUDA(cudaMemcpy(status_host, (const uint8_t*)ex->buffers[ex->rank] + kTpStatusOffset, sizeof(int),
+                      cudaMemcpyDeviceToHost));
+  return FDK_OK;
 }
 
 extern "C" int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache,

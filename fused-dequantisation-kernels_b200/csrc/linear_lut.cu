@@ -34,6 +34,7 @@
 
 #include "fdk_common.cuh"
 #include "lut_table.cuh"
+#include "tp_exchange.cuh"
 
 namespace fdk {
 namespace {
@@ -68,6 +69,11 @@ struct LinearParams {
   uint32_t xres_addr;     // all of x staged once per CTA at this address (0: x rows come with each slab)
   uint32_t xres_row;      // bytes between its rows
   uint32_t xres_bar;      // barrier of that one copy
+  // tensor-parallel push (tp > 0): outputs go to every rank's exchange buffer instead of `out`
+  int tp, rank;
+  uint2* peer_stage[8];     // staging words {two 16-bit outputs, tag} [2][tp][slot / 2] of each rank, as mapped here
+  const uint32_t* seq;      // local count of reduces done so far = number of this push
+  long long stage_slot;     // elements of one (half, rank) slot
 #ifdef FDK_TRACE
   unsigned long long* trace;  // [grid][warps][8] cycle counts (development builds only)
 #endif
@@ -178,7 +184,7 @@ constexpr uint32_t kSpinLimit = 1u << 24;  // polls of a memory word before givi
 // runs once or twice per CTA, so its cost is mostly instruction fetches).  Returns false if a
 // bounded poll ran out.
 template <int NB, int WARPS, bool FP16>
-__device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots, int rt, int c0, int c1) {
+__device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots, int rt, int c0, int c1, uint32_t push_seq) {
   constexpr int EMAX = 512 * NB;  // outputs of one row tile at TT = 4
   const int lane = threadIdx.x & 31;
   const int tt = p.slot_t, sw = 32 * tt;
@@ -259,17 +265,45 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
     }
   }
 
-  // 3. write the outputs: element (blk, tq, lane) with blk = sub-tile * NB + n-tile
+  // 3. write the outputs: element (blk, tq, lane) with blk = sub-tile * NB + n-tile.  In a
+  //    tensor-parallel push they are first gathered as bf16 in the slot block of warp 1 (summed
+  //    above, free now), [batch row][64 tile rows], then stored into this rank's slot of the
+  //    current half of every rank's exchange buffer (plain peer stores) as 8-byte words {two
+  //    outputs, tag}: a word is valid once its tag is that of this push, so no fence, flag or
+  //    second crossing of the link is needed.
   {
     const int g = lane >> 2, c = lane & 3;
+    uint16_t* gathered = reinterpret_cast<uint16_t*>(slots + E);
 #pragma unroll 1
     for (int blk = 0; blk < kSubTiles * NB; ++blk) {
       const int r = blk / NB, nb = blk - r * NB;
-      const int row = rt * kTileRows + 16 * r + g + 8 * (c >> 1);
+      const int lrow = 16 * r + g + 8 * (c >> 1);
+      const int row = rt * kTileRows + lrow;
 #pragma unroll 1
       for (int tq = 0; tq < tt; ++tq) {
         const int b = 8 * nb + 2 * tq + (c & 1);
-        if (row < p.n && b < p.m) p.out[(size_t)b * p.n + row] = from_float<FP16>(slots[blk * sw + tq * 32 + lane]);
+        if (row < p.n && b < p.m) {
+          const uint16_t v = from_float<FP16>(slots[blk * sw + tq * 32 + lane]);
+          if (p.tp == 0) p.out[(size_t)b * p.n + row] = v;
+          else gathered[b * kTileRows + lrow] = v;
+        }
+      }
+    }
+    if (p.tp > 0) {
+      __syncwarp();
+      const uint32_t tag = push_seq + 1u;
+      const size_t base = ((size_t)((push_seq & 1u) * p.tp + p.rank) * p.stage_slot + (size_t)rt * kTileRows) / 2;
+#pragma unroll 1
+      for (int ch = lane; ch < p.m * (kTileRows / 4); ch += 32) {  // four outputs and two tags per store
+        const int b = ch / (kTileRows / 4), part = ch % (kTileRows / 4);
+        const uint2 d = *reinterpret_cast<const uint2*>(gathered + b * kTileRows + part * 4);
+        const size_t off = base + ((size_t)b * p.n) / 2 + part * 2;
+#pragma unroll 1
+        for (int j = 0; j < p.tp; ++j) {
+          asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p.peer_stage[j] + off), "r"(d.x),
+                       "r"(tag), "r"(d.y), "r"(tag)
+                       : "memory");
+        }
       }
     }
   }
@@ -391,6 +425,8 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // everything above touched only weights; x, out and the workspace follow stream order
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // number of this push = reduces completed before this launch (the reduce kernel counts)
+  const uint32_t push_seq = p.tp > 0 ? (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq)) : 0u;
   __syncwarp();
   if (p.xres_addr != 0 && warp == 0) {  // small x: one copy per batch row for the whole kernel
     if (lane == 0) {
@@ -463,7 +499,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
       if (old == W - 1) {  // every warp of the CTA has deposited: this warp finishes the tile
         __threadfence_block();
         FDK_T(long long tf = clock64();)
-        if (!tile_finish<NB, WARPS, FP16>(p, my_slots, cur_rt, c0, c1)) timed_out = true;
+        if (!tile_finish<NB, WARPS, FP16>(p, my_slots, cur_rt, c0, c1, push_seq)) timed_out = true;
         FDK_T(tr_finish += clock64() - tf;)
         __syncwarp();
         if (lane == 0) {
@@ -794,13 +830,13 @@ extern "C" int fdk_workspace_status(const void* workspace, int* status_host) {
   return FDK_OK;
 }
 
-extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void* lut_host,
-                              void* out, int m, int n, int k, int bits, int dtype, void* workspace,
-                              size_t workspace_bytes, unsigned flags, void* stream) {
+static int linear_lut_impl(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
+                           int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
+                           unsigned flags, const fdk_tp_exchange* ex, void* stream) {
   FDK_CHECK_ARG(m > 0 && n > 0 && k > 0, FDK_ERR_BAD_ARG, "m=%d, n=%d, k=%d must be positive", m, n, k);
   FDK_CHECK_ARG(bits_supported(bits), FDK_ERR_SHAPE, "bits=%d not in {1,2,3,4,8}", bits);
   FDK_CHECK_ARG(k % kBlock == 0, FDK_ERR_SHAPE, "k=%d must be a multiple of 64", k);
-  FDK_CHECK_ARG(x && tiled && (lut || lut_host) && out, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(x && tiled && (lut || lut_host) && (out || ex), FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(dtype == FDK_DTYPE_BF16 || dtype == FDK_DTYPE_F16, FDK_ERR_BAD_ARG, "dtype=%d", dtype);
   FDK_CHECK_ARG((flags & ~FDK_FLAG_PDL) == 0, FDK_ERR_BAD_ARG, "unknown flags 0x%x", flags);
   FDK_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)tiled & 15) == 0 && ((uintptr_t)lut & 15) == 0 &&
@@ -826,17 +862,30 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
   p.k_slabs = d.k_slabs;
   p.total = d.row_tiles * d.k_slabs;
   const int grid = di.sm_count;  // the launcher turns this into one or two CTAs per SM
-#ifdef FDK_TRACE
-  p.trace = g_trace;
-#endif
-  if (m > 16 && dtype == FDK_DTYPE_BF16 && (bits == 4 || bits == 8)) {
+  if (ex != nullptr) {
+    FDK_CHECK_ARG(ex->tp >= 1 && ex->tp <= kTpMaxRanks && ex->rank >= 0 && ex->rank < ex->tp, FDK_ERR_BAD_ARG,
+                  "tp=%d, rank=%d", ex->tp, ex->rank);
+    FDK_CHECK_ARG(m <= 16 && n % kTileRows == 0 && ex->slot_elems % 8 == 0 && (long long)m * n <= ex->slot_elems,
+                  FDK_ERR_SHAPE, "push of m=%d, n=%d into slots of %lld elements (m <= 16, n %% 64 == 0)", m, n,
+                  ex->slot_elems);
+    p.tp = ex->tp;
+    p.rank = ex->rank;
+    p.stage_slot = ex->slot_elems;
+    for (int j = 0; j < ex->tp; ++j) {
+      FDK_CHECK_ARG(ex->buffers[j] != nullptr && ((uintptr_t)ex->buffers[j] & 255) == 0, FDK_ERR_ALIGN,
+                    "exchange buffer %d must be a 256-byte aligned device pointer", j);
+      p.peer_stage[j] = (uint2*)((uint8_t*)ex->buffers[j] + kTpStageOffset);
+    }
+    p.seq = (const uint32_t*)((const uint8_t*)ex->buffers[ex->rank] + kTpSeqOffset);
+  }
+  if (ex == nullptr && m > 16 && dtype == FDK_DTYPE_BF16 && (bits == 4 || bits == 8)) {
     return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, workspace, workspace_bytes, di.sm_count,
                        (cudaStream_t)stream);
   }
   for (int m0 = 0; m0 < m; m0 += 16) {
     p.m = (m - m0) < 16 ? (m - m0) : 16;
     p.x = (const uint16_t*)x + (size_t)m0 * k;
-    p.out = (uint16_t*)out + (size_t)m0 * n;
+    p.out = out ? (uint16_t*)out + (size_t)m0 * n : nullptr;
     int st;
     switch (bits) {
       case 1: st = launch_bits<1>(p, lut_host, grid, dtype, flags, (cudaStream_t)stream); break;
@@ -848,6 +897,22 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
     if (st) return st;
   }
   return FDK_OK;
+}
+
+extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void* lut_host,
+                              void* out, int m, int n, int k, int bits, int dtype, void* workspace,
+                              size_t workspace_bytes, unsigned flags, void* stream) {
+  FDK_CHECK_ARG(out != nullptr, FDK_ERR_BAD_ARG, "null pointer");
+  return linear_lut_impl(x, tiled, lut, lut_host, out, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
+                         nullptr, stream);
+}
+
+extern "C" int fdk_linear_lut_push(const void* x, const void* tiled, const void* lut, const void* lut_host, int m,
+                                   int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
+                                   unsigned flags, const fdk_tp_exchange* ex, void* stream) {
+  FDK_CHECK_ARG(ex != nullptr, FDK_ERR_BAD_ARG, "exchange is null");
+  return linear_lut_impl(x, tiled, lut, lut_host, nullptr, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
+                         ex, stream);
 }
 
 // ---- entry point that allocates nothing ---------------------------------------------------

@@ -13,7 +13,9 @@ split-context attention over the static KV cache, SiLU * up -- in four fused CUD
 Tensor parallelism (not in the reference, which is single-GPU): Megatron-style.  q|k|v and
 gate|up are split by output rows (whole heads), o and down by input columns; block scales run
 along K inside a row, so sharding the bf16 weight and then quantising equals quantising and
-then sharding.  One NCCL all-reduce of the [batch, hidden] bf16 activation follows o and down.
+then sharding.  The [batch, hidden] partial sums of o and down are added over the ranks either
+by an NCCL all-reduce, or ("fused", batches up to 16) by the projection kernel storing them
+into every rank's exchange buffer over NVLink and the next RMSNorm kernel adding them up.
 Embedding, norms and lm_head are replicated.
 """
 
@@ -34,10 +36,21 @@ class TensorParallel:
     rank: int = 0
     size: int = 1
     group: "dist.ProcessGroup | None" = None
+    fused: bool = False  # push from the projection kernel + sum in the RMSNorm kernel, where possible
 
     def all_reduce(self, t: Tensor) -> None:
         if self.size > 1:
             dist.all_reduce(t, group=self.group)
+
+    def open_exchange(self, slot_elems: int, device: torch.device) -> "native.TpExchange":
+        """One exchange buffer per rank, each mapped by all the others (CUDA IPC; one node)."""
+        nbytes = native.tp_exchange_bytes(self.size, slot_elems)
+        mine, handle = native.tp_buffer_create(nbytes, device)
+        handles: list = [None] * self.size
+        dist.all_gather_object(handles, handle, group=self.group)
+        buffers = [mine if j == self.rank else native.tp_buffer_open(handles[j], device) for j in range(self.size)]
+        dist.barrier(group=self.group)
+        return native.make_exchange(self.size, self.rank, buffers, slot_elems)
 
 
 def shard_rows(n: int, tp: TensorParallel) -> slice:
@@ -184,6 +197,28 @@ class LlamaDecoder(nn.Module):
         # context slices per (batch row, KV head): a few hundred CTAs in all, at least 64 keys each
         self.splits = max(1, min(max_len // 64, -(-512 // (batch * self.kv_heads)), 8))
         self.attn_scratch, self.attn_counters = native.attention_scratch(batch, self.q_heads, self.kv_heads, self.splits, dev)
+        # fused push + reduce instead of NCCL: quantised row-parallel projections, batch <= 16
+        self.close()
+        can_push = all(
+            isinstance(m, QuantisedLinear) and m.kernel != "torch.compile" for l in self.layers for m in (l.o, l.down)
+        )
+        if self.tp.size > 1 and self.tp.fused and batch <= 16 and can_push and h % 64 == 0:
+            self.exchange = self.tp.open_exchange(16 * h, dev)
+
+    def close(self) -> None:
+        """Unmaps the other ranks' exchange buffers and frees this rank's (collective: every rank
+        calls it).  Without it they live until the process exits."""
+        ex = getattr(self, "exchange", None)
+        self.exchange = None
+        if ex is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.tp.group)
+        for j in range(ex.tp):
+            if j != ex.rank:
+                native.tp_buffer_close(ex.buffers[j])
+        dist.barrier(group=self.tp.group)
+        native.tp_buffer_destroy(ex.buffers[ex.rank])
 
     def fill_cache_synthetic(self, context: int, seed: int = 1) -> None:
         """Benchmark aid: pretend `context` tokens have been decoded (random keys and values)."""
@@ -200,6 +235,8 @@ class LlamaDecoder(nn.Module):
         position.  No host synchronisation, fixed shapes: capturable in a CUDA graph."""
         dims, eps = self.dims, self.dims.rms_norm_eps
         torch.index_select(self.embed.weight, 0, tokens, out=self.hidden)
+        if self.exchange is not None:
+            return self._forward_fused()
         delta = None
         for i, layer in enumerate(self.layers):
             native.rmsnorm(self.hidden, delta, layer.input_norm, self.normed, eps)
@@ -215,6 +252,30 @@ class LlamaDecoder(nn.Module):
             delta = layer.down(self.act)
             self.tp.all_reduce(delta)
         native.rmsnorm(self.hidden, delta, self.final_norm, self.normed, eps)
+        logits = self.lm_head(self.normed)
+        self.position += 1
+        return logits
+
+
+    def _forward_fused(self) -> Tensor:
+        """The same step with each row-parallel projection pushing its partial sums to all ranks
+        and the following RMSNorm adding them: no collective launches."""
+        dims, eps, ex = self.dims, self.dims.rms_norm_eps, self.exchange
+        for i, layer in enumerate(self.layers):
+            if i == 0:
+                native.rmsnorm(self.hidden, None, layer.input_norm, self.normed, eps)
+            else:
+                native.rmsnorm_reduce(self.hidden, ex, layer.input_norm, self.normed, eps)
+            qkv = layer.qkv(self.normed)
+            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads, dims.rope_theta)
+            native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
+                                    self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
+            layer.o.push(self.attn, ex)
+            native.rmsnorm_reduce(self.hidden, ex, layer.post_norm, self.normed, eps)
+            gate_up = layer.gate_up(self.normed)
+            native.silu_mul(gate_up, self.act)
+            layer.down.push(self.act, ex)
+        native.rmsnorm_reduce(self.hidden, ex, self.final_norm, self.normed, eps)
         logits = self.lm_head(self.normed)
         self.position += 1
         return logits

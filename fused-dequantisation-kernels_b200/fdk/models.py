@@ -117,6 +117,15 @@ class QuantisedLinear(nn.Module):
         )
         return out
 
+    def push(self, x: Tensor, exchange: "native.TpExchange") -> None:
+        """Row-parallel use in tensor-parallel decode: this rank's partial product goes straight
+        into every rank's exchange buffer (no output tensor); native.rmsnorm_reduce sums them."""
+        assert x.ndim == 2 and self.kernel != "torch.compile"
+        native.linear_lut_push(
+            x.contiguous(), self.tiled(), self.lut, exchange, self.out_features, self.in_features, self.bits,
+            pdl=True, lut_bytes=self.lut_bytes(),
+        )
+
     @classmethod
     def create(cls, weight: Tensor, c: QuantisationConfig, lut: Tensor | None = None) -> "QuantisedLinear":
         device = weight.device
@@ -402,6 +411,9 @@ def _main() -> None:
                         nargs="+", help="Kernel implementation(s) (ignored for 16-bit)")
     parser.add_argument("--reps", type=int, default=100, help="Number of generation steps to measure")
     parser.add_argument("--context", type=int, default=2, help="Tokens already in the KV cache")
+    parser.add_argument("--tp-reduce", default="fused", choices=["fused", "nccl"],
+                        help="Under torchrun: how the row-parallel projections' partial sums are added "
+                             "(fused = pushed from the kernel over NVLink, batches up to 16; else NCCL)")
     args = parser.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -411,7 +423,7 @@ def _main() -> None:
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    tp = llama.TensorParallel(rank, world, None)
+    tp = llama.TensorParallel(rank, world, None, fused=args.tp_reduce == "fused")
 
     log = bench.Log("models") if rank == 0 else None
     for name in args.model:
@@ -431,6 +443,9 @@ def _main() -> None:
                     out.update(result.__dict__)
                     if rank == 0:
                         print(f"{str(settings):>60}:  {result}", file=sys.stderr)
+                    if getattr(model, "exchange", None) is not None:
+                        out.update(tp_reduce="fused", exchange_status=native.tp_exchange_status(model.exchange))
+                    model.close()
                     del model
                 except Exception as e:  # as the reference: log and carry on
                     out.update(error=repr(e))

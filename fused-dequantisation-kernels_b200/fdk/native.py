@@ -31,7 +31,37 @@ class FdkError(RuntimeError):
 
 _lib: ctypes.CDLL | None = None
 
+TP_MAX_RANKS = 8
+
+
+class TpExchange(ctypes.Structure):
+    """`fdk_tp_exchange` of the C header."""
+
+    _fields_ = [
+        ("tp", ctypes.c_int),
+        ("rank", ctypes.c_int),
+        ("buffers", ctypes.c_void_p * TP_MAX_RANKS),
+        ("slot_elems", ctypes.c_longlong),
+    ]
+
+
 _SIGNATURES = {
+    "fdk_tp_exchange_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_longlong]),
+    "fdk_tp_buffer_create": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
+    "fdk_tp_buffer_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "fdk_tp_buffer_close": (ctypes.c_int, [ctypes.c_void_p]),
+    "fdk_tp_buffer_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "fdk_tp_exchange_status": (ctypes.c_int, [ctypes.POINTER(TpExchange), ctypes.POINTER(ctypes.c_int)]),
+    "fdk_linear_lut_push": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5
+        + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.POINTER(TpExchange), ctypes.c_void_p],
+    ),
+    "fdk_rmsnorm_reduce": (
+        ctypes.c_int,
+        [ctypes.c_void_p, ctypes.POINTER(TpExchange), ctypes.c_void_p, ctypes.c_void_p]
+        + [ctypes.c_int] * 2 + [ctypes.c_float, ctypes.c_void_p],
+    ),
     "fdk_version": (ctypes.c_int, []),
     "fdk_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "fdk_last_error_detail": (ctypes.c_char_p, []),
@@ -235,6 +265,85 @@ def rmsnorm(h: Tensor, delta: Tensor | None, weight: Tensor, out: Tensor, eps: f
             lib().fdk_rmsnorm(
                 h.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(), out.data_ptr(),
                 rows, width, eps, _stream(),
+            )
+        )
+
+
+# ---- tensor-parallel exchange -------------------------------------------------------------
+
+
+def tp_exchange_bytes(tp: int, slot_elems: int) -> int:
+    size = lib().fdk_tp_exchange_bytes(tp, slot_elems)
+    if size == 0:
+        raise FdkError(1, "bad argument", f"tp={tp}, slot_elems={slot_elems}")
+    return size
+
+
+def tp_buffer_create(nbytes: int, device: torch.device) -> tuple[int, bytes]:
+    """Zeroed device buffer that other processes can map -> (device pointer, 64-byte handle)."""
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    with torch.cuda.device(device):
+        check(lib().fdk_tp_buffer_create(nbytes, ctypes.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def tp_buffer_open(handle: bytes, device: torch.device) -> int:
+    ptr = ctypes.c_void_p()
+    with torch.cuda.device(device):
+        check(lib().fdk_tp_buffer_open(handle, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def tp_buffer_close(ptr: int) -> None:
+    check(lib().fdk_tp_buffer_close(ptr))
+
+
+def tp_buffer_destroy(ptr: int) -> None:
+    check(lib().fdk_tp_buffer_destroy(ptr))
+
+
+def make_exchange(tp: int, rank: int, buffers: list[int], slot_elems: int) -> TpExchange:
+    ex = TpExchange()
+    ex.tp, ex.rank, ex.slot_elems = tp, rank, slot_elems
+    for j, ptr in enumerate(buffers):
+        ex.buffers[j] = ptr
+    return ex
+
+
+def tp_exchange_status(ex: TpExchange) -> int:
+    out = ctypes.c_int(0)
+    check(lib().fdk_tp_exchange_status(ctypes.byref(ex), ctypes.byref(out)))
+    return out.value
+
+
+def linear_lut_push(
+    x: Tensor, tiled: Tensor, lut: Tensor, ex: TpExchange, n: int, k: int, bits: int,
+    pdl: bool = False, lut_bytes: bytes | None = None,
+) -> None:
+    """x[m, k] @ W.T stored into slot `ex.rank` of every rank's exchange buffer (m <= 16)."""
+    _require_cuda(x, tiled, lut)
+    m = x.shape[0]
+    ws = workspace(x.device)
+    if lut_bytes is None:
+        lut_bytes = host_lut(lut)
+    with torch.cuda.device(x.device):
+        check(
+            lib().fdk_linear_lut_push(
+                x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), lut_bytes, m, n, k, bits,
+                dtype_code(x.dtype), ws.data_ptr(), ws.numel(), FLAG_PDL if pdl else 0, ctypes.byref(ex), _stream(),
+            )
+        )
+
+
+def rmsnorm_reduce(h: Tensor, ex: TpExchange, weight: Tensor, out: Tensor, eps: float) -> None:
+    """h += sum over ranks of the latest push (in place), out = RMSNorm(h) * weight."""
+    _require_cuda(h, weight, out)
+    rows, width = h.shape
+    with torch.cuda.device(h.device):
+        check(
+            lib().fdk_rmsnorm_reduce(
+                h.data_ptr(), ctypes.byref(ex), weight.data_ptr(), out.data_ptr(), rows, width, eps, _stream(),
             )
         )
 

@@ -191,6 +191,57 @@ int fdk_linear_lut_static(const void* x, const void* tiled, const void* lut, con
                           void* out, int m, int n, int k, int bits, int dtype, unsigned flags,
                           void* stream);
 
+/* ---- tensor-parallel exchange: row-parallel projection fused with its all-reduce ----------
+ * The reference runs on one GPU (its src/ has no collective).  Here a row-parallel projection
+ * (o_proj, down_proj: each rank holds a K-slice of the weight and produces a partial sum of
+ * the whole output) can store its result straight into every rank's exchange buffer from the
+ * kernel's epilogue, and the RMSNorm that follows adds the ranks' partial sums in rank order
+ * while it adds the residual: no separate collective launch, one NVLink crossing.
+ *
+ * Every rank owns one exchange buffer of fdk_tp_exchange_bytes(tp, slot_elems) bytes, zeroed,
+ * and maps the buffers of the others (fdk_tp_buffer_*: CUDA IPC, all ranks on one node with
+ * peer access).  It holds two halves used alternately, each with one slot per rank of
+ * slot_elems partial sums, stored as 8-byte words {two 16-bit values, 32-bit tag}, and this
+ * rank's count of completed reduces.  A word is valid for the reduce once its tag is the
+ * number of the push, so a push needs no fence, flag or acknowledgement: one crossing of the
+ * link.  Rules:
+ *   - all ranks make the same sequence of push / reduce calls, each push followed by its
+ *     reduce on the same stream before the next push (the decode loop does);
+ *   - m <= 16, n a multiple of 64, m * n <= slot_elems;
+ *   - only plain stores to peer memory are used: no multicast of any kind.
+ * A reduce waits at most two seconds for a word of another rank, then records status 1 in
+ * the buffer (fdk_tp_exchange_status), takes the word as zero and carries on. */
+#define FDK_TP_MAX_RANKS 8
+typedef struct fdk_tp_exchange {
+  int tp;                          /* ranks, 1..FDK_TP_MAX_RANKS */
+  int rank;                        /* this rank */
+  void* buffers[FDK_TP_MAX_RANKS]; /* every rank's exchange buffer as mapped here; buffers[rank] is this rank's */
+  long long slot_elems;            /* 16-bit elements per slot, a multiple of 8 */
+} fdk_tp_exchange;
+
+size_t fdk_tp_exchange_bytes(int tp, long long slot_elems);
+/* Allocates `bytes` of zeroed device memory on the current device and writes its 64-byte IPC
+ * handle; the other ranks pass the handle to fdk_tp_buffer_open (which enables peer access)
+ * and later to fdk_tp_buffer_close; the owner frees with fdk_tp_buffer_destroy. */
+int fdk_tp_buffer_create(size_t bytes, void** ptr_host, unsigned char* handle_host);
+int fdk_tp_buffer_open(const unsigned char* handle_host, void** ptr_host);
+int fdk_tp_buffer_close(void* ptr);
+int fdk_tp_buffer_destroy(void* ptr);
+int fdk_tp_exchange_status(const fdk_tp_exchange* ex, int* status_host);
+
+/* fdk_linear_lut whose output [m, n] goes to slot `rank` of the current half of every rank's
+ * exchange buffer instead of `out`, each CTA storing the rows it finishes. */
+int fdk_linear_lut_push(const void* x, const void* tiled, const void* lut, const void* lut_host,
+                        int m, int n, int k, int bits, int dtype, void* workspace,
+                        size_t workspace_bytes, unsigned flags, const fdk_tp_exchange* ex,
+                        void* stream);
+
+/* fdk_rmsnorm whose `delta` is the sum over ranks (fp32, in rank order, rounded to bf16) of the
+ * partial sums of the latest push, each word waited for as it is needed.  rows, width must be
+ * the m, n of that push. */
+int fdk_rmsnorm_reduce(void* h, const fdk_tp_exchange* ex, const void* weight, void* out, int rows,
+                       int width, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,3 +93,18 @@ def test_host_layout_model_is_a_permutation():
         # no padding at this shape: the tiled buffer is a permutation of the source bytes
         src = np.concatenate([codes.ravel(), scale.view(np.uint8).ravel()])
         assert np.array_equal(np.sort(tiled), np.sort(src))
+
+
+def test_exchange_entry_points_validate_without_a_gpu(lib):
+    from fdk import native
+
+    assert lib.fdk_tp_exchange_bytes(2, 1024) == 256 + 2 * 2 * 1024 * 4
+    assert lib.fdk_tp_exchange_bytes(0, 1024) == 0 and lib.fdk_tp_exchange_bytes(9, 1024) == 0
+    assert lib.fdk_tp_exchange_bytes(2, 0) == 0
+    assert lib.fdk_linear_lut_push(None, None, None, None, 1, 64, 64, 4, 0, None, 0, 0, None, None) == 1
+    assert lib.fdk_rmsnorm_reduce(None, None, None, None, 1, 64, 1e-5, None) == 1
+    assert lib.fdk_tp_buffer_open(None, None) == 1
+    assert lib.fdk_tp_buffer_close(None) == 1 and lib.fdk_tp_buffer_destroy(None) == 1
+    ex = native.make_exchange(2, 1, [4096, 8192], 512)
+    assert (ex.tp, ex.rank, ex.slot_elems, ex.buffers[1]) == (2, 1, 512, 8192)
+    assert ctypes.sizeof(native.TpExchange) == 8 + 8 * 8 + 8

@@ -35,6 +35,37 @@ whole = run(llama.TensorParallel())
 err = (sharded - whole).pow(2).sum().div(whole.pow(2).sum()).sqrt().item()
 print(f"rank {rank} rel-RMS error {err:.3e}", flush=True)
 assert err < 2e-2, err
+# partial sums pushed from the projection kernel and added in the RMSNorm kernel
+from fdk import native
+tp = llama.TensorParallel(rank, world, fused=True)
+model = llama.LlamaDecoder.random_init(dims, cfg, dev, tp, seed=7)
+model.allocate(2, 64)
+assert model.exchange is not None
+with torch.no_grad():
+    pushed = torch.stack([model(ids[:, t].contiguous()).float() for t in range(6)], 1)
+    # and replayed from a CUDA graph: the push counter lives on the device
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        model(ids[:, 0].contiguous())
+    torch.cuda.synchronize()
+    model.position.fill_(3)
+    graph = torch.cuda.CUDAGraph()
+    tok = ids[:, 3].contiguous()
+    with torch.cuda.graph(graph):
+        logits = model(tok)
+    for t in (3, 4, 5):
+        model.position.fill_(t)
+        tok.copy_(ids[:, t])
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(logits.float(), pushed[:, t]), t
+err = (pushed - whole).pow(2).sum().div(whole.pow(2).sum()).sqrt().item()
+print(f"rank {rank} fused rel-RMS error {err:.3e} status {native.tp_exchange_status(model.exchange)}", flush=True)
+assert err < 2e-2, err
+assert native.tp_exchange_status(model.exchange) == 0
+gathered = [torch.empty_like(pushed) for _ in range(world)]
+dist.all_gather(gathered, pushed)
+assert all(torch.equal(g, pushed) for g in gathered), "ranks disagree"
 dist.barrier()
 dist.destroy_process_group()
 """
@@ -49,4 +80,4 @@ def test_two_rank_decode_matches_single_rank(tmp_path):
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300), str(script)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
-    assert res.stdout.count("rel-RMS error") == 2
+    assert res.stdout.count("fused rel-RMS error") == 2
