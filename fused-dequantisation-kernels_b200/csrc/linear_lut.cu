@@ -66,6 +66,7 @@ struct LinearParams {
   uint32_t stage_bytes;   // slab + this launch's x rows, rounded to 128
   uint32_t stages;        // ring stages per warp
   uint32_t slot_t;        // fragment column pairs kept per row in the reduction slots: ceil(min(m, 8) / 2)
+  uint32_t slot_sets;     // slot sets used in turn by consecutive row tiles: 2, or 1 where they are large
   uint32_t xres_addr;     // all of x staged once per CTA at this address (0: x rows come with each slab)
   uint32_t xres_row;      // bytes between its rows
   uint32_t xres_bar;      // barrier of that one copy
@@ -318,7 +319,7 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
 constexpr int kXRowPad = 16;  // x rows in a stage are 16 bytes apart from a 128-byte multiple: no bank conflicts
 
 template <int BITS, int NB, int WARPS, bool FP16>
-__global__ void __launch_bounds__(WARPS * 32, 2)
+__global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
   using T = Table<BITS>;
@@ -468,13 +469,14 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
   const uint32_t slot_set_floats = W * kSubTiles * NB * sw;
   auto flush_until = [&](int target) {
     while (cur_rt < target) {
-      const int seg = cur_rt - rt_first, set = seg & 1;
+      const int seg = cur_rt - rt_first;
+      const int set = p.slot_sets == 2 ? (seg & 1) : 0, turn = p.slot_sets == 2 ? (seg >> 1) : seg;
       float* my_slots = slots + set * slot_set_floats;
       // the slot set is free once the reduction of two row tiles ago has read it
       {
         volatile int* gen = &esync->gen[set];
         uint32_t spins = 0;
-        while (*gen != (seg >> 1)) {
+        while (*gen != turn) {
           if (++spins > kSpinLimit) {
             timed_out = true;
             break;
@@ -662,7 +664,11 @@ size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
   using T = Table<BITS>;
   const uint32_t n_stages = warps * stages;
   const uint32_t tt = ((p.m < 8 ? p.m : 8) + 1) / 2;
-  const uint32_t slot_bytes = 2 * warps * kSubTiles * NB * 32 * tt * sizeof(float);  // two sets
+  // two sets let a warp deposit its next row tile while the last one is being summed; large
+  // deposits (batches of five rows and more) get one set and more warps instead
+  const uint32_t sets = tt >= 3 ? 1 : 2;
+  p.slot_sets = sets;
+  const uint32_t slot_bytes = sets * warps * kSubTiles * NB * 32 * tt * sizeof(float);
   const uint32_t mbar_bytes = align_up(n_stages * 8 + 8 + sizeof(EpilogueSync), 128);  // barriers + epilogue sync words
   // x small enough is staged whole, once per CTA; otherwise its rows travel with each slab
   const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
@@ -735,13 +741,15 @@ int launch(LinearParams p, const void* lut_host, int sm_count, unsigned flags, c
   if (int st = dynamic_smem_base(&base)) return st;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
-  constexpr int kWide = (NB == 1) ? 12 : 8;
+  constexpr int kWide = 12;
+  constexpr int kMid = 8;
   constexpr int kNarrow = 4;
   const size_t half_sm = ((size_t)di.max_smem_optin + 1024) / 2 - 1024;  // two CTAs, 1 KB reserved each
-  const int widths[2] = {kWide, kNarrow};
+  const int widths[3] = {kWide, kMid, kNarrow};
   int best_w = 0, best_s = 0;
   size_t best_smem = 0;
   bool two_per_sm = true;
+  bool env_free = true;  // no plan forced from the environment (development builds)
 #ifdef FDK_TRACE
   static const char* env_s = getenv("FDK_STAGES");
   static const char* env_w = getenv("FDK_WARPS");
@@ -752,23 +760,31 @@ int launch(LinearParams p, const void* lut_host, int sm_count, unsigned flags, c
     best_w = want_w;
     best_s = atoi(env_s);
     two_per_sm = best_smem <= half_sm;
+    env_free = false;
   }
 #endif
-  for (int pass = 0; pass < 2 && !best_w; ++pass) {  // first half an SM, then all of it
-    const size_t limit = pass == 0 ? half_sm : (size_t)di.max_smem_optin;
-    for (int want = 2; want >= 1 && !best_w; --want) {
-      for (int wi = 0; wi < 2 && !best_w; ++wi) {
-        for (int s = kMaxStages; s >= want; --s) {
-          LinearParams q = p;
-          size_t smem = plan_smem<BITS, NB>(base, widths[wi], s, q);
-          if (smem <= limit) {
-            best_w = widths[wi];
-            best_s = s;
-            best_smem = smem;
-            two_per_sm = pass == 0;
-            break;
-          }
+  // Candidates: each width, in half an SM or all of it, with as many stages as fit.  The one
+  // that keeps the most warps on an SM wins (two CTAs count double where the grid can be
+  // doubled: NB == 1 and enough slabs); ties go to the half-SM plan, which leaves room for the
+  // next kernel's prologue.  Plans with a single stage are taken only if nothing else fits.
+  int best_score = -1;
+  for (int wi = 0; wi < 3 && env_free; ++wi) {
+    for (int pass = 0; pass < 2; ++pass) {
+      const size_t limit = pass == 0 ? half_sm : (size_t)di.max_smem_optin;
+      for (int s = kMaxStages; s >= 1; --s) {
+        LinearParams q = p;
+        const size_t smem = plan_smem<BITS, NB>(base, widths[wi], s, q);
+        if (smem > limit) continue;
+        const bool doubled = pass == 0 && NB == 1 && p.total >= 2 * widths[wi] * sm_count;
+        const int score = (s >= 2 ? 1000 : 0) + widths[wi] * (doubled ? 2 : 1) * 10 + (pass == 0 ? 1 : 0);
+        if (score > best_score) {
+          best_score = score;
+          best_w = widths[wi];
+          best_s = s;
+          best_smem = smem;
+          two_per_sm = pass == 0;
         }
+        break;  // fewer stages of the same plan are never better
       }
     }
   }
@@ -782,6 +798,7 @@ int launch(LinearParams p, const void* lut_host, int sm_count, unsigned flags, c
   p.base = p.total / grid;
   p.rem = p.total % grid;
   if (best_w == kWide) return launch_variant<BITS, NB, kWide, FP16>(p, inl, best_smem, grid, flags, stream);
+  if (best_w == kMid) return launch_variant<BITS, NB, kMid, FP16>(p, inl, best_smem, grid, flags, stream);
   return launch_variant<BITS, NB, kNarrow, FP16>(p, inl, best_smem, grid, flags, stream);
 }
 
