@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     esync->gen[0] = esync->gen[1] = 0;
     if (p.xres_addr) mbar_init(p.xres_bar, 1);
   }
-  const uint32_t lane_base = p.table_addr + lane * T::kEntryBytes;
+  const uint32_t lane_base = p.table_addr + T::lane_offset(lane);
 
 
   // my slab range
@@ -553,9 +553,19 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
         for (int nb = 0; nb < NB; ++nb) {
           float acc[4];
           const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+#ifdef FDK_SPLIT_CHAIN
+          float acc2[4];
+          mma16816<FP16>(acc, a[0], xb[nb][0], xb[nb][1], zero);
+          mma16816<FP16>(acc2, a[2], xb[nb][4], xb[nb][5], zero);
+          mma16816<FP16>(acc, a[1], xb[nb][2], xb[nb][3], acc);
+          mma16816<FP16>(acc2, a[3], xb[nb][6], xb[nb][7], acc2);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
+#else
           mma16816<FP16>(acc, a[0], xb[nb][0], xb[nb][1], zero);
 #pragma unroll
           for (int st = 1; st < 4; ++st) mma16816<FP16>(acc, a[st], xb[nb][2 * st], xb[nb][2 * st + 1], acc);
+#endif
           tot[R][nb][0] = fmaf(acc[0], s_lo, tot[R][nb][0]);
           tot[R][nb][1] = fmaf(acc[1], s_lo, tot[R][nb][1]);
           tot[R][nb][2] = fmaf(acc[2], s_hi, tot[R][nb][2]);
@@ -727,7 +737,7 @@ int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int 
 // with one CTA per SM the other half is free for the NEXT kernel on the stream, which under
 // programmatic dependent launch starts its table fill and weight prefetch while this one is
 // still running; a large matrix takes both halves itself (two CTAs per SM).  A plan that does
-// not fit half an SM (the 1-bit table alone is 128 KB) gets the whole SM.
+// not fit half an SM gets the whole SM.
 template <int BITS, int NB, bool FP16>
 int launch(LinearParams p, const void* lut_host, int sm_count, unsigned flags, cudaStream_t stream) {
   InlineLut<BITS> inl;
@@ -879,6 +889,9 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
   p.k_slabs = d.k_slabs;
   p.total = d.row_tiles * d.k_slabs;
   const int grid = di.sm_count;  // the launcher turns this into one or two CTAs per SM
+#ifdef FDK_TRACE
+  p.trace = g_trace;
+#endif
   if (ex != nullptr) {
     FDK_CHECK_ARG(ex->tp >= 1 && ex->tp <= kTpMaxRanks && ex->rank >= 0 && ex->rank < ex->tp, FDK_ERR_BAD_ARG,
                   "tp=%d, rank=%d", ex->tp, ex->rank);
@@ -895,8 +908,9 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
     }
     p.seq = (const uint32_t*)((const uint8_t*)ex->buffers[ex->rank] + kTpSeqOffset);
   }
-  if (ex == nullptr && m > 16 && dtype == FDK_DTYPE_BF16 && (bits == 4 || bits == 8)) {
-    return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, workspace, workspace_bytes, di.sm_count,
+  if (ex == nullptr && m > 16) {
+    return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, dtype == FDK_DTYPE_F16, workspace, workspace_bytes,
+                       di.sm_count,
                        (cudaStream_t)stream);
   }
   for (int m0 = 0; m0 < m; m0 += 16) {

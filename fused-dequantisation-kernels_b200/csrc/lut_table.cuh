@@ -116,16 +116,20 @@ __device__ __forceinline__ uint32_t word_at(const uint4& v, int i) {
 }
 
 // ---- lookup tables in shared memory -----------------------------------------
-// Per-lane replicas: entry e of lane l lives at  base + e * kStride + l * kEntryBytes with
-// kStride = 32 * kEntryBytes, so that the 32 lanes of a warp always hit 32 different banks
-// (or, for 8/16-byte entries, every quarter / half warp does) whatever code bytes they hold.
-// A lookup address is one PRMT (extract the code byte) and one shift-add.
+// Replicated so that lookups never conflict: entry e lives in the 128-byte row  base + 128 * e,
+// once per lane of the group of lanes that one shared-memory wavefront serves -- 32 lanes for
+// 4-byte entries, a half warp for 8-byte entries, a quarter warp for 16-byte entries -- at
+// offset (lane % kReplicas) * kEntryBytes.  Whatever code bytes the lanes hold, the lanes of a
+// wavefront read 128 different bytes' worth of banks.  A lookup address is one PRMT (extract
+// the code byte) and one multiply-add.
 template <int BITS>
 struct Table {
   static constexpr int kEntries = (BITS == 3) ? 64 : 256;
   static constexpr int kEntryBytes = (BITS == 2) ? 8 : (BITS == 1 ? 16 : 4);
-  static constexpr int kStride = 32 * kEntryBytes;
-  static constexpr int kBytes = kEntries * kStride;  // 32 KB (4- and 8-bit), 64 KB, 128 KB (1-bit), 8 KB (3-bit)
+  static constexpr int kReplicas = 128 / kEntryBytes;
+  static constexpr int kStride = 128;
+  static constexpr int kBytes = kEntries * kStride;  // 32 KB, or 8 KB for 3 bits
+  __device__ static __forceinline__ uint32_t lane_offset(int lane) { return (lane % kReplicas) * kEntryBytes; }
 };
 
 // The byte table may travel inside the kernel parameters (no memory latency at all) or be
@@ -136,15 +140,15 @@ struct InlineLut {
   uint32_t w[kWords];
 };
 
-// Fills the per-lane replicated table.  A plain loop on purpose: code that runs once per
+// Fills the replicated table.  A plain loop on purpose: code that runs once per
 // launch costs mostly instruction fetches, so it is kept short rather than unrolled.
 // word(i) returns 32-bit word i of the source table.
 template <int BITS, class WordFn>
 __device__ __forceinline__ void fill_table(uint32_t table_base, int threads, WordFn word, int tid) {
   using T = Table<BITS>;
 #pragma unroll 1
-  for (int idx = tid; idx < T::kEntries * 32; idx += threads) {
-    const int e = idx >> 5, l = idx & 31;
+  for (int idx = tid; idx < T::kEntries * T::kReplicas; idx += threads) {
+    const int e = idx / T::kReplicas, l = idx % T::kReplicas;
     const uint32_t addr = table_base + e * T::kStride + l * T::kEntryBytes;
     if constexpr (BITS == 4) {
       asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(word(e)) : "memory");
@@ -209,9 +213,9 @@ constexpr size_t kTcPartialOffset = kGemvEnd + 16384;
 constexpr size_t kTcPartialTileBytes = (size_t)128 * 256 * sizeof(float);
 constexpr size_t kWorkspaceBytes = kTcPartialOffset + 148 * kTcPartialTileBytes;
 
-// Tensor-core GEMM for batches above 16 rows (gemm_lut_tc.cu): bf16, 4- or 8-bit codes.
+// Tensor-core GEMM for batches above 16 rows (gemm_lut_tc.cu).
 int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out, int m, int n,
-                int k, int bits, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
+                int k, int bits, bool fp16, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
 
 // The dynamic shared memory address seen by kernels without static shared memory, asked of
 // the device once (linear_lut.cu).

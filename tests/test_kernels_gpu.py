@@ -128,8 +128,11 @@ def test_linear_lut_is_deterministic(native):
     assert native.device_status() == 0
 
 
-def test_linear_lut_fp16(native):
-    n, k, bits, m = 256, 512, 4, 3
+@pytest.mark.parametrize("n,k,m", [(256, 512, 3), (256, 512, 40), (1024, 2048, 200)])
+def test_linear_lut_fp16(native, n, k, m):
+    """fp16 activations, scales and table (the Marlin selectors' type): the GEMV kernel up to 16
+    rows, the tensor-core kernel above."""
+    bits = 4
     rng = np.random.default_rng(11)
     codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
     base = O.f32_to_f16(np.arange(-8, 8, dtype=np.float32))
@@ -179,14 +182,15 @@ def test_error_statuses_on_device(native):
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("bits", [4, 8])
-@pytest.mark.parametrize("m,n,k", [(17, 128, 64), (32, 192, 256), (64, 1024, 1024), (200, 4096, 4096), (192, 768, 4096), (256, 2048, 3072), (300, 256, 512)])
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("m,n,k", [(17, 128, 64), (32, 192, 256), (64, 1024, 1024), (200, 4096, 4096), (192, 768, 4096), (256, 2048, 3072), (300, 256, 512),
+                                   (24, 320, 192), (40, 64, 448), (256, 5120, 1728)])
 def test_tensor_core_gemm_matches_oracle(native, bits, m, n, k):
     """Batches above 16 rows run the tcgen05 kernel, whose W is the reference's bf16 W bit for
     bit; its outputs differ from the oracle's only by fp32 summation order and the last bf16
     rounding."""
     codes, lut, scale, x = random_problem(n, k, bits, m, seed=m + n + k + bits)
-    expected = O.mm_dense(x, O.dequantise(codes, lut, scale))
+    expected = O.mm_dense(x, oracle_dense(codes, lut, scale, bits, k))
     tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
     out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
     native.linear_lut(from_bits(x), tiled, from_bits(lut), out, n, k, bits)
