@@ -227,17 +227,19 @@ __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long 
   dst[i + 64] = o1;
 }
 
-// out[row, j] = silu(gate_up[row, j]) * gate_up[row, width + j]
+// out[row, j] = silu(gate) * up; the columns of gate_up alternate `group` gate values and the
+// `group` matching up values.
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out, int width,
-                                long long total) {
+                                int group, long long total) {
   pdl_prologue();
   for (long long idx = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8; idx < total;
        idx += (long long)gridDim.x * blockDim.x * 8) {
     const long long row = idx / width;
     const int col = (int)(idx - row * width);
-    const uint16_t* g = gate_up + row * 2 * width + col;
+    const int tile = col / group;
+    const uint16_t* g = gate_up + row * 2 * width + (size_t)tile * 2 * group + (col - tile * group);
     uint4 gv = *reinterpret_cast<const uint4*>(g);
-    uint4 uv = *reinterpret_cast<const uint4*>(g + width);
+    uint4 uv = *reinterpret_cast<const uint4*>(g + group);
     const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gv);
     const uint32_t* uw = reinterpret_cast<const uint32_t*>(&uv);
     uint4 ov;
@@ -371,15 +373,16 @@ extern "C" int fdk_rope_append(const void* qkv, const void* pos, void* q_out, vo
                     kv_heads, max_len, theta);
 }
 
-extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, void* stream) {
+extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, int group, void* stream) {
   FDK_CHECK_ARG(gate_up && out, FDK_ERR_BAD_ARG, "null pointer");
-  FDK_CHECK_ARG(rows > 0 && width > 0 && width % 8 == 0, FDK_ERR_SHAPE, "rows=%d, width=%d", rows, width);
+  FDK_CHECK_ARG(rows > 0 && width > 0 && group > 0 && group % 8 == 0 && width % group == 0, FDK_ERR_SHAPE,
+                "rows=%d, width=%d, group=%d (group a multiple of 8, width a multiple of group)", rows, width, group);
   FDK_CHECK_ARG((((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0, FDK_ERR_ALIGN, "pointers must be 16-byte aligned");
   const long long total = (long long)rows * width;
   long long blocks = (total / 8 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   return launch_pdl(silu_mul_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream,
-                    (const uint16_t*)gate_up, (uint16_t*)out, width, total);
+                    (const uint16_t*)gate_up, (uint16_t*)out, width, group, total);
 }
 
 // ---- decode attention over the static KV cache ----------------------------------------------

@@ -71,6 +71,7 @@ struct LinearParams {
   uint32_t xres_row;      // bytes between its rows
   uint32_t xres_bar;      // barrier of that one copy
   // tensor-parallel push (tp > 0): outputs go to every rank's exchange buffer instead of `out`
+  int silu;  // rows come as 32 gate + 32 up per tile; write silu(gate) * up, [m, n / 2]
   int tp, rank;
   uint2* peer_stage[8];     // staging words {two 16-bit outputs, tag} [2][tp][slot / 2] of each rank, as mapped here
   const uint32_t* seq;      // local count of reduces done so far = number of this push
@@ -285,8 +286,26 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
         const int b = 8 * nb + 2 * tq + (c & 1);
         if (row < p.n && b < p.m) {
           const uint16_t v = from_float<FP16>(slots[blk * sw + tq * 32 + lane]);
-          if (p.tp == 0) p.out[(size_t)b * p.n + row] = v;
-          else gathered[b * kTileRows + lrow] = v;
+          if (p.tp > 0) gathered[b * kTileRows + lrow] = v;
+          else if (!p.silu) p.out[(size_t)b * p.n + row] = v;
+        }
+      }
+    }
+    if (p.silu) {  // sub-tiles 0,1 hold gate rows, 2,3 the matching up rows
+      auto rnd = [](float v) { return to_float<FP16>(from_float<FP16>(v)); };
+#pragma unroll 1
+      for (int blk = 0; blk < 2 * NB; ++blk) {
+        const int r = blk / NB, nb = blk - r * NB;
+        const int col = rt * (kTileRows / 2) + 16 * r + g + 8 * (c >> 1);
+#pragma unroll 1
+        for (int tq = 0; tq < tt; ++tq) {
+          const int b = 8 * nb + 2 * tq + (c & 1);
+          if (b < p.m) {
+            const float gate = rnd(slots[blk * sw + tq * 32 + lane]);
+            const float up = rnd(slots[(blk + 2 * NB) * sw + tq * 32 + lane]);
+            const float act = rnd(gate / (1.f + __expf(-gate)));
+            p.out[(size_t)b * (p.n / 2) + col] = from_float<FP16>(act * up);
+          }
         }
       }
     }
@@ -865,7 +884,9 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
   FDK_CHECK_ARG(k % kBlock == 0, FDK_ERR_SHAPE, "k=%d must be a multiple of 64", k);
   FDK_CHECK_ARG(x && tiled && (lut || lut_host) && (out || ex), FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(dtype == FDK_DTYPE_BF16 || dtype == FDK_DTYPE_F16, FDK_ERR_BAD_ARG, "dtype=%d", dtype);
-  FDK_CHECK_ARG((flags & ~FDK_FLAG_PDL) == 0, FDK_ERR_BAD_ARG, "unknown flags 0x%x", flags);
+  FDK_CHECK_ARG((flags & ~(FDK_FLAG_PDL | FDK_FLAG_SILU_PAIRS)) == 0, FDK_ERR_BAD_ARG, "unknown flags 0x%x", flags);
+  FDK_CHECK_ARG(!(flags & FDK_FLAG_SILU_PAIRS) || (ex == nullptr && m <= 16 && n % kTileRows == 0), FDK_ERR_SHAPE,
+                "FDK_FLAG_SILU_PAIRS needs m <= 16 and n a multiple of 64 (m=%d, n=%d)", m, n);
   FDK_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)tiled & 15) == 0 && ((uintptr_t)lut & 15) == 0 &&
                     ((uintptr_t)out & 1) == 0,
                 FDK_ERR_ALIGN, "x, tiled and lut must be 16-byte aligned");
@@ -889,6 +910,7 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
   p.k_slabs = d.k_slabs;
   p.total = d.row_tiles * d.k_slabs;
   const int grid = di.sm_count;  // the launcher turns this into one or two CTAs per SM
+  p.silu = (flags & FDK_FLAG_SILU_PAIRS) ? 1 : 0;
 #ifdef FDK_TRACE
   p.trace = g_trace;
 #endif

@@ -31,6 +31,9 @@ from . import native
 from .models import LlamaDims, QuantisationConfig, QuantisedLinear
 
 
+PAIR_GROUP = 32  # gate / up rows alternate in groups of this many (see _shard_layer_weights)
+
+
 @dataclass
 class TensorParallel:
     rank: int = 0
@@ -113,7 +116,10 @@ class LlamaDecoder(nn.Module):
         ks = shard_rows(dims.num_key_value_heads, tp)
         qkv = torch.cat([q[qs.start * d: qs.stop * d], k[ks.start * d: ks.stop * d], v[ks.start * d: ks.stop * d]])
         fs = shard_rows(dims.intermediate_size, tp)
-        gate_up = torch.cat([gate[fs], up[fs]])
+        # rows in groups of 64: 32 gate rows, then the 32 matching up rows, so that one 64-row
+        # tile of the projection kernel holds both factors of 32 outputs of SiLU(gate) * up
+        assert (fs.stop - fs.start) % PAIR_GROUP == 0, "the FFN width per rank must be a multiple of 32"
+        gate_up = torch.stack([gate[fs].unflatten(0, (-1, PAIR_GROUP)), up[fs].unflatten(0, (-1, PAIR_GROUP))], dim=1).flatten(0, 2)
         o_s = o[:, qs.start * d: qs.stop * d].contiguous()
         down_s = down[:, fs].contiguous()
         return qkv, o_s, gate_up, down_s
@@ -205,6 +211,13 @@ class LlamaDecoder(nn.Module):
         if self.tp.size > 1 and self.tp.fused and batch <= 16 and can_push and h % 64 == 0:
             self.exchange = self.tp.open_exchange(16 * h, dev)
 
+    def _gated(self, layer: DecoderLayer) -> None:
+        """self.act = SiLU(gate) * up of self.normed."""
+        if isinstance(layer.gate_up, QuantisedLinear):
+            layer.gate_up.forward_silu_pairs(self.normed, self.act)
+        else:
+            native.silu_mul(layer.gate_up(self.normed), self.act, group=PAIR_GROUP)
+
     def close(self) -> None:
         """Unmaps the other ranks' exchange buffers and frees this rank's (collective: every rank
         calls it).  Without it they live until the process exits."""
@@ -247,8 +260,7 @@ class LlamaDecoder(nn.Module):
             delta = layer.o(self.attn)
             self.tp.all_reduce(delta)
             native.rmsnorm(self.hidden, delta, layer.post_norm, self.normed, eps)
-            gate_up = layer.gate_up(self.normed)
-            native.silu_mul(gate_up, self.act)
+            self._gated(layer)
             delta = layer.down(self.act)
             self.tp.all_reduce(delta)
         native.rmsnorm(self.hidden, delta, self.final_norm, self.normed, eps)
@@ -272,8 +284,7 @@ class LlamaDecoder(nn.Module):
                                     self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
             layer.o.push(self.attn, ex)
             native.rmsnorm_reduce(self.hidden, ex, layer.post_norm, self.normed, eps)
-            gate_up = layer.gate_up(self.normed)
-            native.silu_mul(gate_up, self.act)
+            self._gated(layer)
             layer.down.push(self.act, ex)
         native.rmsnorm_reduce(self.hidden, ex, self.final_norm, self.normed, eps)
         logits = self.lm_head(self.normed)

@@ -117,6 +117,18 @@ class QuantisedLinear(nn.Module):
         )
         return out
 
+    def forward_silu_pairs(self, x: Tensor, out: Tensor) -> None:
+        """For a fused gate|up projection whose rows alternate 32 gate rows and their 32 up rows:
+        out[m, n / 2] = silu(gate) * up, in the projection kernel itself up to 16 rows."""
+        assert x.ndim == 2 and self.out_features % 64 == 0
+        if self.kernel != "torch.compile" and x.shape[0] <= 16:
+            native.linear_lut(
+                x.contiguous(), self.tiled(), self.lut, out, self.out_features, self.in_features, self.bits,
+                pdl=True, lut_bytes=self.lut_bytes(), silu_pairs=True,
+            )
+        else:
+            native.silu_mul(self.forward(x), out, group=32)
+
     def push(self, x: Tensor, exchange: "native.TpExchange") -> None:
         """Row-parallel use in tensor-parallel decode: this rank's partial product goes straight
         into every rank's exchange buffer (no output tensor); native.rmsnorm_reduce sums them."""

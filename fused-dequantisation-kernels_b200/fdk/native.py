@@ -21,6 +21,7 @@ OK = 0
 DTYPE_BF16 = 0
 DTYPE_F16 = 1
 FLAG_PDL = 1
+FLAG_SILU_PAIRS = 2
 
 
 class FdkError(RuntimeError):
@@ -78,7 +79,7 @@ _SIGNATURES = {
     ),
     "fdk_rmsnorm": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 2 + [ctypes.c_float, ctypes.c_void_p]),
     "fdk_rope_append": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_void_p]),
-    "fdk_silu_mul": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 2 + [ctypes.c_void_p]),
+    "fdk_silu_mul": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "fdk_decode_attention_scratch": (ctypes.c_int, [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_size_t)] * 2),
     "fdk_decode_attention": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_int] * 6 + [ctypes.c_void_p]),
     "fdk_workspace_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
@@ -239,9 +240,10 @@ def host_lut(lut: Tensor) -> bytes:
 
 def linear_lut(
     x: Tensor, tiled: Tensor, lut: Tensor, out: Tensor, n: int, k: int, bits: int,
-    pdl: bool = False, lut_bytes: bytes | None = None,
+    pdl: bool = False, lut_bytes: bytes | None = None, silu_pairs: bool = False,
 ) -> None:
-    """out[m, n] = x[m, k] @ W.T, W never materialised.  Writes `out` in place."""
+    """out[m, n] = x[m, k] @ W.T, W never materialised.  Writes `out` in place.  silu_pairs: W's
+    rows alternate 32 gate rows and their 32 up rows, out[m, n / 2] = silu(gate) * up (m <= 16)."""
     _require_cuda(x, tiled, lut, out)
     m = x.shape[0]
     ws = workspace(x.device)
@@ -251,7 +253,8 @@ def linear_lut(
         check(
             lib().fdk_linear_lut(
                 x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), lut_bytes, out.data_ptr(), m, n, k, bits,
-                dtype_code(x.dtype), ws.data_ptr(), ws.numel(), FLAG_PDL if pdl else 0, _stream(),
+                dtype_code(x.dtype), ws.data_ptr(), ws.numel(),
+                (FLAG_PDL if pdl else 0) | (FLAG_SILU_PAIRS if silu_pairs else 0), _stream(),
             )
         )
 
@@ -365,11 +368,13 @@ def rope_append(
         )
 
 
-def silu_mul(gate_up: Tensor, out: Tensor) -> None:
+def silu_mul(gate_up: Tensor, out: Tensor, group: int | None = None) -> None:
+    """out = silu(gate) * up; gate_up's columns alternate `group` gates and `group` ups
+    (default: all gates, then all ups)."""
     _require_cuda(gate_up, out)
     rows, width = out.shape
     with torch.cuda.device(out.device):
-        check(lib().fdk_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, width, _stream()))
+        check(lib().fdk_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, width, width if group is None else group, _stream()))
 
 
 def attention_scratch(batch: int, q_heads: int, kv_heads: int, splits: int, device: torch.device) -> tuple[Tensor, Tensor]:

@@ -52,6 +52,11 @@ extern "C" {
                            weight prefetch may overlap the tail of the previous kernel
                            on the stream; x / out / workspace are only touched after
                            the previous kernel has completed.                          */
+#define FDK_FLAG_SILU_PAIRS 2u /* the weight rows come in groups of 64: 32 "gate" rows, then
+                           the 32 matching "up" rows; the kernel writes
+                           out[m, n / 2] = silu(gate) * up instead of the [m, n] products,
+                           with the roundings of fdk_linear_lut followed by fdk_silu_mul
+                           (group 32).  m <= 16, n a multiple of 64.                   */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int fdk_version(void);
@@ -155,9 +160,11 @@ int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache
                     int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
                     void* stream);
 
-/* out[rows, width] = silu(gate_up[:, :width]) * gate_up[:, width:], gate_up [rows, 2 width] being
- * the output of the fused gate|up projection. */
-int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, void* stream);
+/* out[rows, width] = silu(gate) * up, gate_up [rows, 2 width] being the output of the fused
+ * gate|up projection, whose columns alternate `group` gate values and the `group` matching up
+ * values (group = width: all gates, then all ups; group = 32: the row order that
+ * FDK_FLAG_SILU_PAIRS expects).  width must be a multiple of group, group of 8. */
+int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, int group, void* stream);
 
 /* Decode attention: one query token per batch row against the static KV cache
  * [batch, kv_heads, max_len, 128] (bf16), keys 0 .. *pos (device int64; the current token's

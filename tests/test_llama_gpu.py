@@ -89,3 +89,8 @@ def test_glue_kernels_against_torch():
     native.silu_mul(gu, act)
     ref = torch.nn.functional.silu(gu[:, :1024]) * gu[:, 1024:]
     assert (act.float() - ref.float()).abs().max() <= 2**-7 * ref.float().abs().max()
+    # the same values with gates and ups alternating in groups of 32 columns
+    paired = torch.stack([gu[:, :1024].unflatten(1, (-1, 32)), gu[:, 1024:].unflatten(1, (-1, 32))], dim=2).flatten(1).contiguous()
+    act2 = torch.empty_like(act)
+    native.silu_mul(paired, act2, group=32)
+    assert torch.equal(act2, act)
