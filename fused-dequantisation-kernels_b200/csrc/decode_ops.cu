@@ -376,18 +376,20 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   }
   const uint16_t* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
   const uint16_t* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
-  // four positions per warp and iteration: their eight loads are in flight together
-  for (int pb = p0 + warp * 4; pb < p1; pb += kAttnWarps * 4) {
-    uint2 kk[4], vv[4];
+  // U positions per warp and iteration, all their loads in flight together: with a slice of up
+  // to 8 * U keys a warp pays the memory latency once
+  constexpr int U = (G <= 4) ? 16 : 8;
+  for (int pb = p0 + warp * U; pb < p1; pb += kAttnWarps * U) {
+    uint2 kk[U], vv[U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int p = min(pb + u, p1 - 1);  // clamped reads, masked below
       kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
       vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
     }
-    float s[4][G];
+    float s[U][G];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const float k0 = pair_lo<false>(kk[u].x), k1 = pair_hi<false>(kk[u].x), k2 = pair_lo<false>(kk[u].y), k3 = pair_hi<false>(kk[u].y);
 #pragma unroll
       for (int j = 0; j < G; ++j) s[u][j] = qf[j][0] * k0 + qf[j][1] * k1 + qf[j][2] * k2 + qf[j][3] * k3;
@@ -395,14 +397,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int j = 0; j < G; ++j) s[u][j] += __shfl_xor_sync(0xffffffffu, s[u][j], o);
 #pragma unroll
     for (int j = 0; j < G; ++j) {
       float m_new = mx[j];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         if (pb + u >= p1) s[u][j] = -INFINITY;
         m_new = fmaxf(m_new, s[u][j]);
       }
@@ -410,7 +412,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       mx[j] = m_new;
       float l = sum[j] * corr, a0 = acc[j][0] * corr, a1 = acc[j][1] * corr, a2 = acc[j][2] * corr, a3 = acc[j][3] * corr;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const float w = __expf(s[u][j] - m_new);  // exp(-inf) = 0 for masked positions
         l += w;
         a0 += w * pair_lo<false>(vv[u].x);
