@@ -54,6 +54,31 @@ struct ReduceSource {
   int tp;
 };
 
+__device__ __forceinline__ uint4 ld_words(const uint2* p) {  // two staging words
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// Reads the two words again until both carry `tag` (bounded: two seconds).
+__device__ __forceinline__ void settle(uint4& v, const uint2* p, uint32_t tag, int* status) {
+  unsigned long long t0 = 0;
+  for (uint32_t i = 0; v.y != tag || v.w != tag; ++i) {
+    v = ld_words(p);
+    if ((i & 63u) == 63u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) {
+        atomicOr(status, 1);
+        v = make_uint4(0u, tag, 0u, tag);
+      }
+    }
+  }
+}
+
 // out[row] = weight * bf16(h[row] * rsqrt(mean(h[row]^2) + eps)), with h += delta first when
 // delta is given (h is the residual stream, updated in place).  REDUCE: delta is the sum over
 // ranks (fp32, rank order, rounded to bf16) of the partial sums of the latest push, after
@@ -81,7 +106,33 @@ __global__ void rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restr
     if (dr || REDUCE) {
       uint4 dv;
       if constexpr (REDUCE) {
-        dv = reduce_ranks(words, src.slot, src.tp, i, c, src.status);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4 v[2 * kTpMaxRanks];  // all ranks' words in flight at once
+#pragma unroll
+        for (int j = 0; j < kTpMaxRanks; ++j) {
+          if (j < src.tp) {
+            const uint2* w = words + ((size_t)j * src.slot + i) / 2;
+            v[2 * j] = ld_words(w);
+            v[2 * j + 1] = ld_words(w + 2);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kTpMaxRanks; ++j) {  // added in rank order
+          if (j < src.tp) {
+            const uint2* w = words + ((size_t)j * src.slot + i) / 2;
+            settle(v[2 * j], w, c + 1u, src.status);
+            settle(v[2 * j + 1], w + 2, c + 1u, src.status);
+            const uint4 lo = v[2 * j], hi = v[2 * j + 1];
+            acc[0] += pair_lo<false>(lo.x); acc[1] += pair_hi<false>(lo.x);
+            acc[2] += pair_lo<false>(lo.z); acc[3] += pair_hi<false>(lo.z);
+            acc[4] += pair_lo<false>(hi.x); acc[5] += pair_hi<false>(hi.x);
+            acc[6] += pair_lo<false>(hi.z); acc[7] += pair_hi<false>(hi.z);
+          }
+        }
+        uint32_t* dwm = reinterpret_cast<uint32_t*>(&dv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          dwm[j] = (uint32_t)from_float<false>(acc[2 * j]) | ((uint32_t)from_float<false>(acc[2 * j + 1]) << 16);
       } else {
         dv = *reinterpret_cast<const uint4*>(dr + i);
       }

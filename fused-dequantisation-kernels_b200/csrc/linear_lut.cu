@@ -72,20 +72,6 @@ struct LinearParams {
   uint32_t xres_bar;      // barrier of that one copy
   // tensor-parallel push (tp > 0): outputs go to every rank's exchange buffer instead of `out`
   int silu;  // rows come as 32 gate + 32 up per tile; write silu(gate) * up, [m, n / 2]
-  // x made in the prologue (x staged whole only): x = RMSNorm(h + delta) * norm_w, h + delta
-  // also written to norm_h_out (by CTA 0).  delta: a tensor, or the sum over the ranks of the
-  // latest tensor-parallel push (red_tp > 0), or nothing.
-  const uint16_t* norm_w;  // null: x is read from memory
-  const uint16_t* norm_h;
-  const uint16_t* norm_delta;
-  uint16_t* norm_h_out;
-  float norm_eps;
-  int red_tp;
-  const uint2* red_stage;
-  uint32_t* red_seq;
-  int* red_done;
-  int* red_status;
-  long long red_slot;
   int tp, rank;
   uint2* peer_stage[8];     // staging words {two 16-bit outputs, tag} [2][tp][slot / 2] of each rank, as mapped here
   const uint32_t* seq;      // local count of reduces done so far = number of this push
@@ -348,85 +334,10 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
   return ok;
 }
 
-// x = RMSNorm(h + delta) * w for every batch row, left in the CTA's staging area for x (rows
-// `xres_row` bytes apart); every CTA computes all of it, CTA 0 also writes h + delta out.
-// Arithmetic as in the stand-alone RMSNorm kernel: bf16 residual add, fp32 statistics,
-// bf16(bf16(h * inv) * w).  The caller's CTA barrier follows.
-__device__ __forceinline__ void norm_prologue(const LinearParams& p, uint8_t* xres, float* red) {
-  const int tid = threadIdx.x, threads = blockDim.x, lane = tid & 31, warp = tid >> 5, warps = threads >> 5;
-  uint32_t c = 0;
-  if (p.red_tp > 0) c = *reinterpret_cast<const volatile uint32_t*>(p.red_seq);  // the push being reduced
-#pragma unroll 1
-  for (int b = 0; b < p.m; ++b) {
-    float ss = 0.f;
-#pragma unroll 1
-    for (int i = tid * 8; i < p.k; i += threads * 8) {
-      uint4 hv = *reinterpret_cast<const uint4*>(p.norm_h + (size_t)b * p.k + i);
-      uint32_t* hw = reinterpret_cast<uint32_t*>(&hv);
-      if (p.red_tp > 0 || p.norm_delta != nullptr) {
-        uint4 dv;
-        if (p.red_tp > 0) {
-          const uint2* words = p.red_stage + ((size_t)(c & 1u) * p.red_tp * p.red_slot + (size_t)b * p.k) / 2;
-          dv = reduce_ranks(words, p.red_slot, p.red_tp, i, c, p.red_status);
-        } else {
-          dv = *reinterpret_cast<const uint4*>(p.norm_delta + (size_t)b * p.k + i);
-        }
-        const uint32_t* dw = reinterpret_cast<const uint32_t*>(&dv);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint16_t lo = from_float<false>(pair_lo<false>(hw[j]) + pair_lo<false>(dw[j]));
-          const uint16_t hi = from_float<false>(pair_hi<false>(hw[j]) + pair_hi<false>(dw[j]));
-          hw[j] = (uint32_t)lo | ((uint32_t)hi << 16);
-        }
-      }
-      *reinterpret_cast<uint4*>(xres + (size_t)b * p.xres_row + 2 * i) = hv;
-      if (blockIdx.x == 0) *reinterpret_cast<uint4*>(p.norm_h_out + (size_t)b * p.k + i) = hv;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float x0 = pair_lo<false>(hw[j]), x1 = pair_hi<false>(hw[j]);
-        ss += x0 * x0 + x1 * x1;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (lane == 0) red[b * warps + warp] = ss;
-  }
-  __syncthreads();
-#pragma unroll 1
-  for (int b = 0; b < p.m; ++b) {
-    float total = 0.f;
-    for (int w = 0; w < warps; ++w) total += red[b * warps + w];  // the same order in every thread and CTA
-    const float inv = rsqrtf(total / p.k + p.norm_eps);
-#pragma unroll 1
-    for (int i = tid * 8; i < p.k; i += threads * 8) {  // each thread revisits the elements it wrote
-      uint4* at = reinterpret_cast<uint4*>(xres + (size_t)b * p.xres_row + 2 * i);
-      uint4 hv = *at;
-      const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + i);
-      uint32_t* hw = reinterpret_cast<uint32_t*>(&hv);
-      const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wv);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = to_float<false>(from_float<false>(pair_lo<false>(hw[j]) * inv)) * pair_lo<false>(ww[j]);
-        const float bb = to_float<false>(from_float<false>(pair_hi<false>(hw[j]) * inv)) * pair_hi<false>(ww[j]);
-        hw[j] = (uint32_t)from_float<false>(a) | ((uint32_t)from_float<false>(bb) << 16);
-      }
-      *at = hv;
-    }
-  }
-  // every CTA has read the ranks' words by now: the last one out counts the reduce as done
-  if (p.red_tp > 0 && tid == 0) {
-    if (atomicAdd(p.red_done, 1) == (int)gridDim.x - 1) {
-      *p.red_done = 0;
-      *reinterpret_cast<volatile uint32_t*>(p.red_seq) = c + 1u;
-    }
-  }
-}
-
 // ---- the kernel -------------------------------------------------------------------
 constexpr int kXRowPad = 16;  // x rows in a stage are 16 bytes apart from a 128-byte multiple: no bank conflicts
-constexpr size_t kXResidentBytes = 36 * 1024;  // x up to this size is staged whole, once per CTA
 
-template <int BITS, int NB, int WARPS, bool FP16, bool NORM>
+template <int BITS, int NB, int WARPS, bool FP16>
 __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
@@ -537,9 +448,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
   // number of this push = reduces completed before this launch (the reduce kernel counts)
   const uint32_t push_seq = p.tp > 0 ? (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq)) : 0u;
   __syncwarp();
-  if constexpr (NORM) {  // x is computed here, by all threads (the host has made sure x is staged whole)
-    norm_prologue(p, smem_raw + (p.xres_addr - raw), reinterpret_cast<float*>(smem_raw + (p.slots_addr - raw)));
-  } else if (p.xres_addr != 0 && warp == 0) {  // small x: one copy per batch row for the whole kernel
+  if (p.xres_addr != 0 && warp == 0) {  // small x: one copy per batch row for the whole kernel
     if (lane == 0) {
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(p.xres_bar),
                    "r"((uint32_t)p.m * (uint32_t)p.k * 2u)
@@ -695,7 +604,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     }
   };
 
-  if (p.xres_addr != 0 && !NORM && it < c1) {
+  if (p.xres_addr != 0 && it < c1) {
     if (!mbar_wait(p.xres_bar, 0)) timed_out = true;
   }
   int s = 0;
@@ -792,7 +701,7 @@ size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
   const uint32_t mbar_bytes = align_up(n_stages * 8 + 8 + sizeof(EpilogueSync), 128);  // barriers + epilogue sync words
   // x small enough is staged whole, once per CTA; otherwise its rows travel with each slab
   const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
-  const bool resident = (size_t)p.m * xres_row <= kXResidentBytes;
+  const bool resident = (size_t)p.m * xres_row <= 36 * 1024;
   const uint32_t xres_bytes = resident ? align_up(p.m * xres_row, 128) : 0;
   const uint32_t stage_bytes =
       align_up(L::kSlabBytes + (resident ? 0 : p.m * (128 * L::KSB + kXRowPad)), 128);
@@ -821,20 +730,13 @@ size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
 template <int BITS, int NB, int WARPS, bool FP16>
 int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int grid, unsigned flags,
                    cudaStream_t stream) {
-  auto kernel = linear_lut_kernel<BITS, NB, WARPS, FP16, false>;
-  bool with_norm = false;
-  if constexpr (!FP16) {
-    if (p.norm_w != nullptr) {
-      kernel = linear_lut_kernel<BITS, NB, WARPS, FP16, true>;
-      with_norm = true;
-    }
-  }
-  static size_t configured[2][64] = {};
+  auto kernel = linear_lut_kernel<BITS, NB, WARPS, FP16>;
+  static size_t configured[64] = {};
   int dev = 0;
   FDK_CUDA(cudaGetDevice(&dev));
-  if (configured[with_norm][dev & 63] < smem) {
+  if (configured[dev & 63] < smem) {
     FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[with_norm][dev & 63] = smem;
+    configured[dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -976,11 +878,11 @@ extern "C" int fdk_workspace_status(const void* workspace, int* status_host) {
 
 static int linear_lut_impl(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
                            int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
-                           unsigned flags, const fdk_tp_exchange* ex, const fdk_norm_input* norm, void* stream) {
+                           unsigned flags, const fdk_tp_exchange* ex, void* stream) {
   FDK_CHECK_ARG(m > 0 && n > 0 && k > 0, FDK_ERR_BAD_ARG, "m=%d, n=%d, k=%d must be positive", m, n, k);
   FDK_CHECK_ARG(bits_supported(bits), FDK_ERR_SHAPE, "bits=%d not in {1,2,3,4,8}", bits);
   FDK_CHECK_ARG(k % kBlock == 0, FDK_ERR_SHAPE, "k=%d must be a multiple of 64", k);
-  FDK_CHECK_ARG((x || norm) && tiled && (lut || lut_host) && (out || ex), FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(x && tiled && (lut || lut_host) && (out || ex), FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(dtype == FDK_DTYPE_BF16 || dtype == FDK_DTYPE_F16, FDK_ERR_BAD_ARG, "dtype=%d", dtype);
   FDK_CHECK_ARG((flags & ~(FDK_FLAG_PDL | FDK_FLAG_SILU_PAIRS)) == 0, FDK_ERR_BAD_ARG, "unknown flags 0x%x", flags);
   FDK_CHECK_ARG(!(flags & FDK_FLAG_SILU_PAIRS) || (ex == nullptr && m <= 16 && n % kTileRows == 0), FDK_ERR_SHAPE,
@@ -1009,37 +911,6 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
   p.total = d.row_tiles * d.k_slabs;
   const int grid = di.sm_count;  // the launcher turns this into one or two CTAs per SM
   p.silu = (flags & FDK_FLAG_SILU_PAIRS) ? 1 : 0;
-  if (norm != nullptr) {
-    FDK_CHECK_ARG(norm->h && norm->weight && norm->h_out && norm->h_out != norm->h, FDK_ERR_BAD_ARG,
-                  "h, weight and h_out are needed, and h_out must not be h");
-    FDK_CHECK_ARG(!(norm->delta && norm->reduce), FDK_ERR_BAD_ARG, "delta and reduce exclude each other");
-    FDK_CHECK_ARG(dtype == FDK_DTYPE_BF16 && m <= 16 && (size_t)m * (2 * (size_t)k + kXRowPad) <= kXResidentBytes,
-                  FDK_ERR_SHAPE, "the fused norm takes bf16 and m * (2 k + 16) <= %zu bytes (m=%d, k=%d)",
-                  kXResidentBytes, m, k);
-    FDK_CHECK_ARG((((uintptr_t)norm->h | (uintptr_t)norm->delta | (uintptr_t)norm->weight | (uintptr_t)norm->h_out) & 15) == 0,
-                  FDK_ERR_ALIGN, "h, delta, weight and h_out must be 16-byte aligned");
-    p.norm_w = (const uint16_t*)norm->weight;
-    p.norm_h = (const uint16_t*)norm->h;
-    p.norm_delta = (const uint16_t*)norm->delta;
-    p.norm_h_out = (uint16_t*)norm->h_out;
-    p.norm_eps = norm->eps;
-    if (norm->reduce != nullptr) {
-      const fdk_tp_exchange* r = norm->reduce;
-      FDK_CHECK_ARG(r->tp >= 1 && r->tp <= kTpMaxRanks && r->rank >= 0 && r->rank < r->tp, FDK_ERR_BAD_ARG,
-                    "tp=%d, rank=%d", r->tp, r->rank);
-      FDK_CHECK_ARG(r->slot_elems % 8 == 0 && (long long)m * k <= r->slot_elems, FDK_ERR_SHAPE,
-                    "m=%d x k=%d exceeds slots of %lld elements", m, k, r->slot_elems);
-      uint8_t* local = (uint8_t*)r->buffers[r->rank];
-      FDK_CHECK_ARG(local != nullptr && ((uintptr_t)local & 255) == 0, FDK_ERR_ALIGN,
-                    "the exchange buffer must be a 256-byte aligned device pointer");
-      p.red_tp = r->tp;
-      p.red_slot = r->slot_elems;
-      p.red_stage = (const uint2*)(local + kTpStageOffset);
-      p.red_seq = (uint32_t*)(local + kTpSeqOffset);
-      p.red_done = (int*)(local + kTpDoneOffset);
-      p.red_status = (int*)(local + kTpStatusOffset);
-    }
-  }
 #ifdef FDK_TRACE
   p.trace = g_trace;
 #endif
@@ -1059,7 +930,7 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
     }
     p.seq = (const uint32_t*)((const uint8_t*)ex->buffers[ex->rank] + kTpSeqOffset);
   }
-  if (ex == nullptr && norm == nullptr && m > 16) {
+  if (ex == nullptr && m > 16) {
     return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, dtype == FDK_DTYPE_F16, workspace, workspace_bytes,
                        di.sm_count,
                        (cudaStream_t)stream);
@@ -1086,19 +957,7 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
                               size_t workspace_bytes, unsigned flags, void* stream) {
   FDK_CHECK_ARG(out != nullptr, FDK_ERR_BAD_ARG, "null pointer");
   return linear_lut_impl(x, tiled, lut, lut_host, out, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
-                         nullptr, nullptr, stream);
-}
-
-extern "C" int fdk_linear_lut_norm_fits(int m, int k) {
-  return m >= 1 && m <= 16 && k > 0 && (size_t)m * (2 * (size_t)k + kXRowPad) <= kXResidentBytes;
-}
-
-extern "C" int fdk_linear_lut_norm(const fdk_norm_input* in, const void* tiled, const void* lut, const void* lut_host,
-                                   void* out, int m, int n, int k, int bits, int dtype, void* workspace,
-                                   size_t workspace_bytes, unsigned flags, void* stream) {
-  FDK_CHECK_ARG(in != nullptr && out != nullptr, FDK_ERR_BAD_ARG, "null pointer");
-  return linear_lut_impl(nullptr, tiled, lut, lut_host, out, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
-                         nullptr, in, stream);
+                         nullptr, stream);
 }
 
 extern "C" int fdk_linear_lut_push(const void* x, const void* tiled, const void* lut, const void* lut_host, int m,
@@ -1106,7 +965,7 @@ extern "C" int fdk_linear_lut_push(const void* x, const void* tiled, const void*
                                    unsigned flags, const fdk_tp_exchange* ex, void* stream) {
   FDK_CHECK_ARG(ex != nullptr, FDK_ERR_BAD_ARG, "exchange is null");
   return linear_lut_impl(x, tiled, lut, lut_host, nullptr, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
-                         ex, nullptr, stream);
+                         ex, stream);
 }
 
 // ---- entry point that allocates nothing ---------------------------------------------------

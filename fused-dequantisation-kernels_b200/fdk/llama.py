@@ -97,7 +97,6 @@ class LlamaDecoder(nn.Module):
                  lm_head: Tensor, tp: TensorParallel):
         super().__init__()
         self.dims, self.tp = dims, tp
-        self.fuse_norm = True  # run RMSNorm inside the projection that follows it, where the batch allows
         self.layers = nn.ModuleList(layers)
         self.embed = nn.Embedding.from_pretrained(embed, freeze=True)
         self.final_norm = nn.Parameter(final_norm, requires_grad=False)
@@ -196,7 +195,6 @@ class LlamaDecoder(nn.Module):
         self.k_cache = [torch.zeros((batch, self.kv_heads, max_len, 128), device=dev, dtype=dt) for _ in self.layers]
         self.v_cache = [torch.zeros((batch, self.kv_heads, max_len, 128), device=dev, dtype=dt) for _ in self.layers]
         self.hidden = torch.empty((batch, h), device=dev, dtype=dt)
-        self.hidden2 = torch.empty((batch, h), device=dev, dtype=dt)  # the residual stream alternates between the two
         self.normed = torch.empty((batch, h), device=dev, dtype=dt)
         self.q = torch.empty((batch, self.q_heads * 128), device=dev, dtype=dt)
         self.act = torch.empty((batch, f), device=dev, dtype=dt)
@@ -213,6 +211,13 @@ class LlamaDecoder(nn.Module):
         )
         if self.tp.size > 1 and self.tp.fused and batch <= 16 and can_push and h % 64 == 0:
             self.exchange = self.tp.open_exchange(16 * h, dev)
+
+    def _gated(self, layer: DecoderLayer) -> None:
+        """self.act = SiLU(gate) * up of self.normed."""
+        if isinstance(layer.gate_up, QuantisedLinear):
+            layer.gate_up.forward_silu_pairs(self.normed, self.act)
+        else:
+            native.silu_mul(layer.gate_up(self.normed), self.act, group=PAIR_GROUP)
 
     def close(self) -> None:
         """Unmaps the other ranks' exchange buffers and frees this rank's (collective: every rank
@@ -241,66 +246,51 @@ class LlamaDecoder(nn.Module):
 
     def forward(self, tokens: Tensor) -> Tensor:
         """tokens [batch] int64 at position `self.position` -> logits [batch, vocab]; advances the
-        position.  No host synchronisation, fixed shapes: capturable in a CUDA graph.
-
-        Kernels per layer: [norm +] q|k|v projection, rotary + append, attention, o projection,
-        [norm +] gate|up projection [+ SiLU * up], down projection -- the bracketed steps run
-        inside the projection kernel where the batch allows, as separate kernels otherwise.
-        `delta` is what the next norm has to add to the residual stream first: the output of
-        the last row-parallel projection, as a tensor (all-reduced by NCCL under tensor
-        parallelism) or as the exchange the projection pushed its partial sums into."""
-        dims = self.dims
-        h = self.hidden
-        torch.index_select(self.embed.weight, 0, tokens, out=h)
+        position.  No host synchronisation, fixed shapes: capturable in a CUDA graph."""
+        dims, eps = self.dims, self.dims.rms_norm_eps
+        torch.index_select(self.embed.weight, 0, tokens, out=self.hidden)
+        if self.exchange is not None:
+            return self._forward_fused()
         delta = None
         for i, layer in enumerate(self.layers):
-            h, qkv = self._norm_project(h, delta, layer.input_norm, layer.qkv, gated=False)
+            native.rmsnorm(self.hidden, delta, layer.input_norm, self.normed, eps)
+            qkv = layer.qkv(self.normed)
             native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads, dims.rope_theta)
             native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
                                     self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
-            delta = self._row_parallel(layer.o, self.attn)
-            h, _ = self._norm_project(h, delta, layer.post_norm, layer.gate_up, gated=True)
-            delta = self._row_parallel(layer.down, self.act)
-        self._norm(h, delta, self.final_norm)
+            delta = layer.o(self.attn)
+            self.tp.all_reduce(delta)
+            native.rmsnorm(self.hidden, delta, layer.post_norm, self.normed, eps)
+            self._gated(layer)
+            delta = layer.down(self.act)
+            self.tp.all_reduce(delta)
+        native.rmsnorm(self.hidden, delta, self.final_norm, self.normed, eps)
         logits = self.lm_head(self.normed)
         self.position += 1
         return logits
 
-    def _row_parallel(self, linear: nn.Module, x: Tensor):
-        if self.exchange is not None:
-            linear.push(x, self.exchange)
-            return self.exchange
-        y = linear(x)
-        self.tp.all_reduce(y)
-        return y
 
-    def _norm(self, h: Tensor, delta, weight: Tensor) -> None:
-        """h += delta in place, self.normed = RMSNorm(h) * weight (a kernel of its own)."""
-        if isinstance(delta, native.TpExchange):
-            native.rmsnorm_reduce(h, delta, weight, self.normed, self.dims.rms_norm_eps)
-        else:
-            native.rmsnorm(h, delta, weight, self.normed, self.dims.rms_norm_eps)
-
-    def _norm_project(self, h: Tensor, delta, weight: Tensor, linear: nn.Module, gated: bool):
-        """-> (residual stream after adding delta, projection of its norm).  gated: the
-        projection is gate|up and its SiLU(gate) * up goes to self.act instead."""
-        eps = self.dims.rms_norm_eps
-        if self.fuse_norm and isinstance(linear, QuantisedLinear) and linear.takes_norm(self.batch):
-            h_out = self.hidden2 if h is self.hidden else self.hidden  # other CTAs still read h: write elsewhere
-            if gated:
-                linear.forward_norm(h, delta, weight, h_out, eps, self.act, silu_pairs=True)
-                return h_out, None
-            out = torch.empty((self.batch, linear.out_features), device=h.device, dtype=h.dtype)
-            linear.forward_norm(h, delta, weight, h_out, eps, out)
-            return h_out, out
-        self._norm(h, delta, weight)
-        if gated:
-            if isinstance(linear, QuantisedLinear):
-                linear.forward_silu_pairs(self.normed, self.act)
+    def _forward_fused(self) -> Tensor:
+        """The same step with each row-parallel projection pushing its partial sums to all ranks
+        and the following RMSNorm adding them: no collective launches."""
+        dims, eps, ex = self.dims, self.dims.rms_norm_eps, self.exchange
+        for i, layer in enumerate(self.layers):
+            if i == 0:
+                native.rmsnorm(self.hidden, None, layer.input_norm, self.normed, eps)
             else:
-                native.silu_mul(linear(self.normed), self.act, group=PAIR_GROUP)
-            return h, None
-        return h, linear(self.normed)
+                native.rmsnorm_reduce(self.hidden, ex, layer.input_norm, self.normed, eps)
+            qkv = layer.qkv(self.normed)
+            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads, dims.rope_theta)
+            native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
+                                    self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
+            layer.o.push(self.attn, ex)
+            native.rmsnorm_reduce(self.hidden, ex, layer.post_norm, self.normed, eps)
+            self._gated(layer)
+            layer.down.push(self.act, ex)
+        native.rmsnorm_reduce(self.hidden, ex, self.final_norm, self.normed, eps)
+        logits = self.lm_head(self.normed)
+        self.position += 1
+        return logits
 
 
 class Generator:

@@ -117,20 +117,6 @@ class QuantisedLinear(nn.Module):
         )
         return out
 
-    def takes_norm(self, rows: int) -> bool:
-        """Whether forward_norm can run the norm inside the projection kernel for this batch."""
-        return (self.kernel != "torch.compile" and self.lut.dtype == torch.bfloat16
-                and native.linear_lut_norm_fits(rows, self.in_features))
-
-    def forward_norm(self, h: Tensor, delta, weight: Tensor, h_out: Tensor, eps: float, out: Tensor,
-                     silu_pairs: bool = False) -> None:
-        """h_out = h + delta; out = self(RMSNorm(h_out) * weight) -- or, with silu_pairs (see
-        forward_silu_pairs), silu(gate) * up of that -- in one kernel.  Only where takes_norm()."""
-        native.linear_lut_norm(
-            h, delta, weight, h_out, eps, self.tiled(), self.lut, out, self.out_features, self.in_features,
-            self.bits, pdl=True, lut_bytes=self.lut_bytes(), silu_pairs=silu_pairs,
-        )
-
     def forward_silu_pairs(self, x: Tensor, out: Tensor) -> None:
         """For a fused gate|up projection whose rows alternate 32 gate rows and their 32 up rows:
         out[m, n / 2] = silu(gate) * up, in the projection kernel itself up to 16 rows."""

@@ -46,26 +46,7 @@ class TpExchange(ctypes.Structure):
     ]
 
 
-class NormInput(ctypes.Structure):
-    """`fdk_norm_input` of the C header."""
-
-    _fields_ = [
-        ("h", ctypes.c_void_p),
-        ("delta", ctypes.c_void_p),
-        ("reduce", ctypes.POINTER(TpExchange)),
-        ("weight", ctypes.c_void_p),
-        ("h_out", ctypes.c_void_p),
-        ("eps", ctypes.c_float),
-    ]
-
-
 _SIGNATURES = {
-    "fdk_linear_lut_norm_fits": (ctypes.c_int, [ctypes.c_int, ctypes.c_int]),
-    "fdk_linear_lut_norm": (
-        ctypes.c_int,
-        [ctypes.POINTER(NormInput)] + [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5
-        + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p],
-    ),
     "fdk_tp_exchange_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_longlong]),
     "fdk_tp_buffer_create": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
     "fdk_tp_buffer_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
@@ -273,40 +254,6 @@ def linear_lut(
             lib().fdk_linear_lut(
                 x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), lut_bytes, out.data_ptr(), m, n, k, bits,
                 dtype_code(x.dtype), ws.data_ptr(), ws.numel(),
-                (FLAG_PDL if pdl else 0) | (FLAG_SILU_PAIRS if silu_pairs else 0), _stream(),
-            )
-        )
-
-
-def linear_lut_norm_fits(m: int, k: int) -> bool:
-    """Whether linear_lut_norm takes a batch of m rows of k columns (x must fit shared memory whole)."""
-    return bool(lib().fdk_linear_lut_norm_fits(m, k))
-
-
-def linear_lut_norm(
-    h: Tensor, delta: "Tensor | TpExchange | None", weight: Tensor, h_out: Tensor, eps: float,
-    tiled: Tensor, lut: Tensor, out: Tensor, n: int, k: int, bits: int,
-    pdl: bool = False, lut_bytes: bytes | None = None, silu_pairs: bool = False,
-) -> None:
-    """h_out = h + delta;  out = (RMSNorm(h_out) * weight) @ W.T in one kernel.  delta: a tensor,
-    None, or a TpExchange (the sum over the ranks of the latest push into it)."""
-    _require_cuda(h, weight, h_out, tiled, lut, out)
-    m = h.shape[0]
-    ws = workspace(h.device)
-    if lut_bytes is None:
-        lut_bytes = host_lut(lut)
-    src = NormInput()
-    src.h, src.weight, src.h_out, src.eps = h.data_ptr(), weight.data_ptr(), h_out.data_ptr(), eps
-    if isinstance(delta, TpExchange):
-        src.reduce = ctypes.pointer(delta)
-    elif delta is not None:
-        _require_cuda(delta)
-        src.delta = delta.data_ptr()
-    with torch.cuda.device(h.device):
-        check(
-            lib().fdk_linear_lut_norm(
-                ctypes.byref(src), tiled.data_ptr(), lut.data_ptr(), lut_bytes, out.data_ptr(), m, n, k, bits,
-                dtype_code(h.dtype), ws.data_ptr(), ws.numel(),
                 (FLAG_PDL if pdl else 0) | (FLAG_SILU_PAIRS if silu_pairs else 0), _stream(),
             )
         )

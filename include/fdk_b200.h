@@ -249,29 +249,6 @@ int fdk_linear_lut_push(const void* x, const void* tiled, const void* lut, const
 int fdk_rmsnorm_reduce(void* h, const fdk_tp_exchange* ex, const void* weight, void* out, int rows,
                        int width, float eps, void* stream);
 
-/* fdk_linear_lut whose x is made inside the kernel:  hs = h + delta (bf16 add; delta may be
- * null), x = RMSNorm(hs) * weight with the arithmetic of fdk_rmsnorm, out = x . W^T; hs is also
- * written to h_out, which must not alias h.  `reduce` instead of `delta`: the sum over the
- * ranks of the latest push into that exchange, as fdk_rmsnorm_reduce takes it (this call then
- * counts as that push's reduce).  Saves the launch of the RMSNorm kernel in front of a
- * projection; every CTA recomputes the few KB of x.  Only where x is staged whole in shared
- * memory: bf16, m <= 16 and m * (2 k + 16) <= 36864 (fdk_linear_lut_norm_fits tells); otherwise
- * FDK_ERR_SHAPE, and the caller runs fdk_rmsnorm then fdk_linear_lut.  The rows of x may
- * differ from fdk_rmsnorm's in the last place (another order of the fp32 sum of squares).
- * No counterpart in the reference, whose norm is a separate framework kernel. */
-typedef struct fdk_norm_input {
-  const void* h;                 /* [m, k] residual stream */
-  const void* delta;             /* [m, k] added first, or null */
-  const fdk_tp_exchange* reduce; /* or: the ranks' partial sums of the latest push, or null */
-  const void* weight;            /* [k] */
-  void* h_out;                   /* [m, k] h + delta */
-  float eps;
-} fdk_norm_input;
-int fdk_linear_lut_norm_fits(int m, int k);
-int fdk_linear_lut_norm(const fdk_norm_input* in, const void* tiled, const void* lut,
-                        const void* lut_host, void* out, int m, int n, int k, int bits, int dtype,
-                        void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
-
 #ifdef __cplusplus
 }
 #endif

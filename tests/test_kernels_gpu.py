@@ -168,57 +168,6 @@ def test_linear_lut_silu_pairs_equals_two_steps(native, bits, m, n, k):
                           torch.empty((17, n // 2), dtype=torch.bfloat16, device="cuda"), n, k, bits, silu_pairs=True)
 
 
-@pytest.mark.parametrize("bits,m,n,k,with_delta,silu", [
-    (4, 1, 512, 3072, True, False), (4, 1, 1024, 8192, True, False), (4, 2, 256, 6144, False, False),
-    (2, 4, 512, 1024, True, False), (4, 5, 256, 3072, True, True), (1, 3, 128, 2048, True, False), (4, 1, 16384, 3072, True, True),
-])
-def test_linear_lut_norm_equals_two_steps(native, bits, m, n, k, with_delta, silu):
-    """RMSNorm (+ residual add) inside the projection kernel against fdk_rmsnorm followed by
-    fdk_linear_lut: the residual stream bit for bit, the products up to the last place of x
-    (the fp32 sum of squares is added in another order)."""
-    codes, lut, scale, _ = random_problem(n, k, bits, m, seed=n + k + m)
-    scale = O.f32_to_bf16(O.bf16_to_f32(scale) * np.float32(4.0))
-    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
-    d_lut = from_bits(lut)
-    gen = torch.Generator().manual_seed(k + m)
-    h = torch.randn((m, k), generator=gen).to(torch.bfloat16).cuda()
-    delta = torch.randn((m, k), generator=gen).to(torch.bfloat16).cuda() if with_delta else None
-    wn = (1 + 0.1 * torch.randn(k, generator=gen)).to(torch.bfloat16).cuda()
-    cols = n // 2 if silu else n
-
-    h_two = h.clone()
-    normed = torch.empty_like(h)
-    native.rmsnorm(h_two, delta, wn, normed, 1e-5)
-    want = torch.empty((m, cols), dtype=torch.bfloat16, device="cuda")
-    native.linear_lut(normed, tiled, d_lut, want, n, k, bits, silu_pairs=silu)
-
-    assert native.linear_lut_norm_fits(m, k)
-    h_out = torch.full_like(h, float("nan"))
-    got = torch.full((m, cols), float("nan"), dtype=torch.bfloat16, device="cuda")
-    native.linear_lut_norm(h, delta, wn, h_out, 1e-5, tiled, d_lut, got, n, k, bits, pdl=True, silu_pairs=silu)
-    torch.cuda.synchronize()
-    assert native.device_status() == 0
-    assert np.array_equal(to_bits(h_out), to_bits(h_two))
-    assert O.rmsen(O.bf16_to_f32(to_bits(want)), O.bf16_to_f32(to_bits(got))) < 1e-3
-    assert np.mean(to_bits(want) != to_bits(got)) < 0.05
-
-
-def test_linear_lut_norm_refuses_what_does_not_fit(native):
-    assert not native.linear_lut_norm_fits(16, 8192) and not native.linear_lut_norm_fits(17, 64)
-    n, k, m = 128, 8192, 16
-    codes, lut, scale, _ = random_problem(n, k, 4, m, seed=1)
-    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, 4, 64)
-    h = torch.zeros((m, k), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(native.FdkError) as e:
-        native.linear_lut_norm(h, None, h[0], torch.empty_like(h), 1e-5, tiled, from_bits(lut),
-                               torch.empty((m, n), dtype=torch.bfloat16, device="cuda"), n, k, 4)
-    assert e.value.status == 2
-    with pytest.raises(native.FdkError) as e:  # h_out must not be h
-        native.linear_lut_norm(h[:1], None, h[0], h[:1], 1e-5, tiled, from_bits(lut),
-                               torch.empty((1, n), dtype=torch.bfloat16, device="cuda"), n, k, 4)
-    assert e.value.status == 1
-
-
 def test_linear_lut_cuda_graph_capture(native):
     n, k, bits, m = 1024, 1024, 4, 1
     codes, lut, scale, x = random_problem(n, k, bits, m, seed=2)

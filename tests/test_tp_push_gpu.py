@@ -74,51 +74,6 @@ def test_push_then_reduce_equals_plain_path(native, bits, m, n, k, tp):
     assert native.device_status() == 0
 
 
-@pytest.mark.parametrize("m,n,k,tp", [(1, 3072, 1024, 2), (2, 1024, 512, 4), (1, 6144, 256, 8)])
-def test_reduce_inside_the_next_projection(native, m, n, k, tp):
-    """The pushed partial sums reduced by the next projection's own prologue (fdk_linear_lut_norm
-    with an exchange) instead of fdk_rmsnorm_reduce: the same residual stream bit for bit,
-    the same products up to the last place of x; push numbering stays in step."""
-    slot = 16 * n
-    bufs, exs = _exchange_buffers(native, tp, slot)
-    rng = np.random.default_rng(m + n)
-    problems = []
-    for r in range(tp):
-        codes, lut, scale, x = random_problem(n, k, 4, m, seed=5 * r + m)
-        problems.append((native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, 4, 64), from_bits(lut)))
-    n2 = 256  # the projection that follows: n columns in, n2 rows out
-    codes2, lut2, scale2, _ = random_problem(n2, n, 4, m, seed=99)
-    tiled2 = native.repack(torch.from_numpy(codes2).cuda(), from_bits(scale2), n2, n, 4, 64)
-    weight = (1 + 0.1 * torch.randn(n)).to(torch.bfloat16).cuda()
-    h_a = [torch.randn((m, n), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda() for _ in range(tp)]
-    h_b = [torch.empty_like(h_a[0]) for _ in range(tp)]
-    h_plain = h_a[0].clone()
-    for step in range(4):
-        xs = [from_bits(rng.integers(0x3C00, 0x4000, size=(m, k), dtype=np.uint16)) for _ in range(tp)]
-        total = torch.zeros((m, n), dtype=torch.float32, device="cuda")
-        for r in range(tp):
-            part = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-            native.linear_lut(xs[r], problems[r][0], problems[r][1], part, n, k, 4)
-            total += part.float()
-        normed = torch.empty_like(h_plain)
-        native.rmsnorm(h_plain, total.to(torch.bfloat16), weight, normed, 1e-5)
-        want = torch.empty((m, n2), dtype=torch.bfloat16, device="cuda")
-        native.linear_lut(normed, tiled2, from_bits(lut2), want, n2, n, 4)
-        for r in range(tp):
-            native.linear_lut_push(xs[r], problems[r][0], problems[r][1], exs[r], n, k, 4, pdl=True)
-        for r in range(tp):
-            got = torch.empty_like(want)
-            native.linear_lut_norm(h_a[r], exs[r], weight, h_b[r], 1e-5, tiled2, from_bits(lut2), got, n2, n, 4, pdl=True)
-            torch.cuda.synchronize()
-            assert np.array_equal(to_bits(h_b[r]), to_bits(h_plain)), (step, r)
-            assert np.mean(to_bits(got) != to_bits(want)) < 0.05, (step, r)
-        h_a, h_b = h_b, h_a
-    for r in range(tp):
-        assert native.tp_exchange_status(exs[r]) == 0
-        words = bufs[r][:256].view(torch.int32).cpu()
-        assert words[32].item() == 4 and words[33].item() == 0
-
-
 def test_push_argument_checks(native):
     n, k = 128, 64
     bufs, exs = _exchange_buffers(native, 2, 16 * n)
