@@ -572,19 +572,9 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
         for (int nb = 0; nb < NB; ++nb) {
           float acc[4];
           const float zero[4] = {0.f, 0.f, 0.f, 0.f};
-#ifdef FDK_SPLIT_CHAIN
-          float acc2[4];
-          mma16816<FP16>(acc, a[0], xb[nb][0], xb[nb][1], zero);
-          mma16816<FP16>(acc2, a[2], xb[nb][4], xb[nb][5], zero);
-          mma16816<FP16>(acc, a[1], xb[nb][2], xb[nb][3], acc);
-          mma16816<FP16>(acc2, a[3], xb[nb][6], xb[nb][7], acc2);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
-#else
           mma16816<FP16>(acc, a[0], xb[nb][0], xb[nb][1], zero);
 #pragma unroll
           for (int st = 1; st < 4; ++st) mma16816<FP16>(acc, a[st], xb[nb][2 * st], xb[nb][2 * st + 1], acc);
-#endif
           tot[R][nb][0] = fmaf(acc[0], s_lo, tot[R][nb][0]);
           tot[R][nb][1] = fmaf(acc[1], s_lo, tot[R][nb][1]);
           tot[R][nb][2] = fmaf(acc[2], s_hi, tot[R][nb][2]);
