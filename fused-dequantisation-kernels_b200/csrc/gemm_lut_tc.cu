@@ -146,7 +146,7 @@ __device__ __forceinline__ void decode_row16(const uint32_t (&w)[4], uint32_t la
 }
 
 template <int BITS, bool FP16>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
     gemm_lut_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ InlineLut<BITS> inl,
                        const __grid_constant__ CUtensorMap x_map) {
   using L = Layout<BITS>;
@@ -454,6 +454,7 @@ int encode_fn(EncodeTiledFn* out) {
 }
 
 inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+inline bool two_per_sm(int m_pad) { return m_pad <= 64; }
 
 // Shared memory: barriers, the table, then the stage buffers (1024-byte aligned for the
 // swizzled tiles).  Returns the dynamic size, or 0 if `stages` do not fit in `limit`.
@@ -495,7 +496,10 @@ int launch_tc(TcParams p, const void* lut_host, const CUtensorMap& map, int tile
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
   size_t smem = 0;
-  for (int s = kTcMaxStages; s >= 1 && smem == 0; --s) smem = plan_tc_smem<BITS>(base, (uint32_t)di.max_smem_optin, s, p);
+  // small batches: two CTAs per SM (twice the warps to hide the latencies of the per-block
+  // hand-offs), each within half the shared memory; tensor memory holds both accumulators
+  const uint32_t limit = two_per_sm(p.m_pad) ? ((uint32_t)di.max_smem_optin + 1024) / 2 - 1024 : (uint32_t)di.max_smem_optin;
+  for (int s = kTcMaxStages; s >= 1 && smem == 0; --s) smem = plan_tc_smem<BITS>(base, limit, s, p);
   FDK_CHECK_ARG(smem != 0, FDK_ERR_CUDA, "no shared-memory plan fits %d bytes", di.max_smem_optin);
   auto kernel = gemm_lut_tc_kernel<BITS, FP16>;
   static size_t configured[64] = {};
@@ -522,15 +526,18 @@ int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* l
   const int k_blocks = k / kBlock;
   // few tiles: several CTAs share a tile, each with its own range of 64-column blocks, so that
   // the whole GPU is busy; all of them must be resident at once (the owner waits for the others)
+  const int m_pad_max = ((m < 256 ? m : 256) + 15) / 16 * 16;
+  const int resident = sm_count * (two_per_sm(m_pad_max) ? 2 : 1);
   int splits = 1;
-  if (tiles * 2 <= sm_count) {
-    splits = sm_count / tiles;
+  if (tiles * 2 <= resident) {
+    splits = resident / tiles;
     if (splits > kTcMaxSplits) splits = kTcMaxSplits;
     if (splits > k_blocks / 4) splits = k_blocks / 4;
     if (splits < 1) splits = 1;
   }
-  if (splits > 1 && (workspace_bytes < kTcPartialOffset + (size_t)tiles * (splits - 1) * kTcPartialTileBytes || tiles > 2048))
-    splits = 1;  // a small (e.g. built-in) workspace: every CTA finishes its tile alone
+  // the parked partial tiles (128 rows x m_pad columns of fp32 each) must fit the workspace
+  const size_t partial_room = workspace_bytes > kTcPartialOffset ? workspace_bytes - kTcPartialOffset : 0;
+  while (splits > 1 && ((size_t)tiles * (splits - 1) * 128 * m_pad_max * sizeof(float) > partial_room || tiles > 2048)) --splits;
   for (int m0 = 0; m0 < m; m0 += 256) {
     const int mc = (m - m0) < 256 ? (m - m0) : 256;
     TcParams p{};
