@@ -1,33 +1,41 @@
 // Fused dequantise + GEMV / skinny GEMM for sm_100a:  out[m, n] = x[m, k] . W[n, k]^T,
 // W given as tiled low-bit codes + block scales + a lookup table (fdk_layout.cuh).
 //
-// Shape of the kernel (one persistent CTA per SM, up to 24 warps):
+// Shape of the kernel (persistent CTAs of 12, 8 or 4 warps, sized so that two fit on an SM):
 //   * The weight stream is cut into slabs (64 rows x 64*KSB columns, 2-6 KB).  The
 //     slabs of the whole matrix form one linear sequence (row tile major); CTA c owns
 //     a contiguous range of it ("stream-K"), its warps take slabs round-robin.  Every
 //     SM therefore streams the same number of bytes (+-1 slab) whatever N and K are.
+//     A large matrix runs two CTAs per SM; a small one runs one, and the other half of
+//     the SM is free for the next kernel on the stream, which under programmatic
+//     dependent launch fills its table and prefetches weights while this one runs.
 //   * Every warp owns a small ring of slab-sized stages in shared memory.  Lane 0
 //     fills them with one bulk asynchronous copy per slab (cp.async.bulk, completion
 //     on an mbarrier), so the data in flight costs no registers and the loads need
-//     no issue slots.  All waits on those barriers are bounded.
+//     no issue slots.  x is staged whole once per CTA when it is small, otherwise
+//     its rows travel with each slab.  All waits on the barriers are bounded.
 //   * Codes are turned into tensor-core A fragments by table lookup in shared memory:
-//     one code byte indexes a per-lane replica of the byte table, so a lookup is one
-//     PRMT (byte -> address) and one conflict-free LDS that returns 2 (4-bit), 4
-//     (2-bit) or 8 (1-bit) 16-bit weights already in fragment order.  x is the B
-//     operand (batch padded to 8 or 16 columns), read through L1.
+//     one code byte indexes a replicated byte table (lut_table.cuh), so a lookup is one
+//     PRMT (extract the byte), one multiply-add (address) and one conflict-free LDS
+//     that returns 2 (4-bit), 4 (2-bit) or 8 (1-bit) 16-bit weights already in
+//     fragment order.  The table itself arrives inside the kernel parameters.
 //   * mma.sync m16n8k16 accumulates one 64-block in fp32; the block scale multiplies
 //     the fp32 block sum (4 FMAs per 1024 weights), then running totals per row.
 //     The tensor pipe is used because the FMA work would otherwise compete with the
 //     lookups for issue slots; at m <= 16 it is far from being the limiter, so the
 //     synchronous MMA form is enough and keeps the weights in registers (a tcgen05
 //     MMA would need them written back to shared or tensor memory first).  What
-//     bounds the kernel besides HBM is the shared-memory pipe: one 128-byte wavefront
-//     per 32 code bytes looked up, plus the wavefronts that bring the codes in.
-//   * At a row-tile boundary the warps of a CTA reduce through shared memory in a
-//     fixed order.  A CTA that owns only part of a row tile's K range writes its
-//     partial sums to the workspace and bumps an arrival counter; the last arriver
-//     adds the partials in CTA order and writes the result.  No spinning, and the
-//     summation order never depends on timing, so results are reproducible.
+//     bounds the main loop is the shared-memory pipe: one 128-byte wavefront per 32
+//     code bytes looked up, plus the wavefronts that bring codes and x in.
+//   * At a row-tile boundary the warps of a CTA deposit their totals in shared memory
+//     and the last to arrive adds them in warp order (no CTA barrier).  A row tile
+//     split over several CTAs is finished by the CTA holding its first slabs: the
+//     others publish their sums to the workspace as {value, tag} words, which the
+//     finisher reads (bounded polling) and adds in CTA order.  The summation order
+//     never depends on timing, so results are reproducible bit for bit.
+//   * Epilogue variants: plain store; silu(gate) * up for a gate|up weight stored in
+//     32 + 32 row groups; or, in tensor-parallel decode, tagged stores of the partial
+//     sums into every rank's exchange buffer.
 #include <cstdlib>
 #include <cstring>
 #include <type_traits>

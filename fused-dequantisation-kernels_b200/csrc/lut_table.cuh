@@ -14,14 +14,6 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
 
-__device__ __forceinline__ uint4 ldg_l1(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
 template <uint32_t SEL>
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b) {
   uint32_t d;
