@@ -16,11 +16,12 @@ along K inside a row, so sharding the bf16 weight and then quantising equals qua
 then sharding.  The [batch, hidden] partial sums of o and down are added over the ranks either
 by an NCCL all-reduce, or ("fused", batches up to 16) by the projection kernel storing them
 into every rank's exchange buffer over NVLink and the next RMSNorm kernel adding them up.
-Embedding, norms and lm_head are replicated.
+Embedding and norms are replicated; lm_head is split by vocabulary rows and the logits gathered.
 """
 
 from __future__ import annotations
 
+import re
 from dataclasses import dataclass
 
 import torch
@@ -94,14 +95,21 @@ class LlamaDecoder(nn.Module):
     the device) or `from_hf` (weights of a transformers LlamaForCausalLM)."""
 
     def __init__(self, dims: LlamaDims, layers: list[DecoderLayer], embed: Tensor, final_norm: Tensor,
-                 lm_head: Tensor, tp: TensorParallel):
+                 lm_head: Tensor, tp: TensorParallel, config: QuantisationConfig | None = None,
+                 lut: Tensor | None = None):
         super().__init__()
         self.dims, self.tp = dims, tp
         self.layers = nn.ModuleList(layers)
         self.embed = nn.Embedding.from_pretrained(embed, freeze=True)
         self.final_norm = nn.Parameter(final_norm, requires_grad=False)
-        self.lm_head = nn.Linear(dims.hidden_size, dims.vocab_size, bias=False, device=embed.device, dtype=embed.dtype)
-        self.lm_head.weight = nn.Parameter(lm_head, requires_grad=False)
+        # lm_head: split by vocabulary rows over the ranks (logits are gathered), and quantised
+        # like the other projections unless the configuration's `skip` pattern matches its name
+        # (the reference's default "^lm_head$" does; src/fdk/models.py:27,144)
+        self.vocab_sharded = tp.size > 1 and dims.vocab_size % tp.size == 0
+        if self.vocab_sharded:
+            lm_head = lm_head[shard_rows(dims.vocab_size, tp)].contiguous()
+        skipped = config is None or (config.skip is not None and re.search(config.skip, "lm_head") is not None)
+        self.lm_head = _make_linear(lm_head, None if skipped else config, lut)
         self.q_heads = dims.num_attention_heads // tp.size
         self.kv_heads = dims.num_key_value_heads // tp.size
         assert dims.num_key_value_heads % tp.size == 0, "KV heads must split evenly over the ranks"
@@ -151,7 +159,7 @@ class LlamaDecoder(nn.Module):
             ))
         embed = draw(dims.vocab_size, h)
         lm_head = draw(dims.vocab_size, h)
-        return cls(dims, layers, embed, torch.ones(h, device=device, dtype=torch.bfloat16), lm_head, tp)
+        return cls(dims, layers, embed, torch.ones(h, device=device, dtype=torch.bfloat16), lm_head, tp, config, lut)
 
     @classmethod
     def from_hf(cls, model, config: QuantisationConfig | None, device: torch.device,
@@ -183,7 +191,8 @@ class LlamaDecoder(nn.Module):
                 _make_linear(gu_w, config, lut), _make_linear(down_w, config, lut),
                 w(hl.input_layernorm.weight), w(hl.post_attention_layernorm.weight),
             ))
-        return cls(dims, layers, w(model.model.embed_tokens.weight), w(model.model.norm.weight), w(model.lm_head.weight), tp)
+        return cls(dims, layers, w(model.model.embed_tokens.weight), w(model.model.norm.weight), w(model.lm_head.weight), tp,
+                   config, lut)
 
     # ---- decode state -----------------------------------------------------------------
 
@@ -265,9 +274,18 @@ class LlamaDecoder(nn.Module):
             delta = layer.down(self.act)
             self.tp.all_reduce(delta)
         native.rmsnorm(self.hidden, delta, self.final_norm, self.normed, eps)
-        logits = self.lm_head(self.normed)
+        logits = self._logits()
         self.position += 1
         return logits
+
+    def _logits(self) -> Tensor:
+        """lm_head of self.normed -> [batch, vocab]; the ranks' vocabulary slices are gathered."""
+        local = self.lm_head(self.normed)
+        if not self.vocab_sharded:
+            return local
+        gathered = torch.empty((self.tp.size,) + tuple(local.shape), device=local.device, dtype=local.dtype)
+        dist.all_gather_into_tensor(gathered, local.contiguous(), group=self.tp.group)
+        return gathered.permute(1, 0, 2).reshape(local.shape[0], -1)
 
 
     def _forward_fused(self) -> Tensor:
@@ -288,9 +306,10 @@ class LlamaDecoder(nn.Module):
             self._gated(layer)
             layer.down.push(self.act, ex)
         native.rmsnorm_reduce(self.hidden, ex, self.final_norm, self.normed, eps)
-        logits = self.lm_head(self.normed)
+        logits = self._logits()
         self.position += 1
         return logits
+
 
 
 class Generator:

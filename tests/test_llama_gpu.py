@@ -94,3 +94,24 @@ def test_glue_kernels_against_torch():
     act2 = torch.empty_like(act)
     native.silu_mul(paired, act2, group=32)
     assert torch.equal(act2, act)
+
+
+def test_lm_head_is_quantised_when_the_skip_pattern_does_not_match_it():
+    """The reference leaves lm_head in 16 bits by default (skip="^lm_head$") and quantises it
+    like any other projection when the pattern does not match (src/fdk/models.py:27,144)."""
+    from fdk import kernels, llama, models
+
+    dev = torch.device("cuda")
+    dims = models.LlamaDims("tiny", 256, 1, 2, 2, 512, vocab_size=1000)
+    kept = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(4, 64), dev, seed=3)
+    assert isinstance(kept.lm_head, torch.nn.Linear)
+    cfg = models.QuantisationConfig(4, 64, skip="^$")
+    model = llama.LlamaDecoder.random_init(dims, cfg, dev, seed=3)
+    assert isinstance(model.lm_head, models.QuantisedLinear) and model.lm_head.out_features == 1000
+    model.allocate(2, 8)
+    with torch.no_grad():
+        logits = model(torch.tensor([5, 7], device=dev))
+    head = model.lm_head
+    want = kernels.mm_lut_ref(model.normed, head.weight_data, head.lut, head.scale)
+    err = (logits.float() - want.float()).pow(2).sum().div(want.float().pow(2).sum()).sqrt().item()
+    assert err < 1e-2, err
