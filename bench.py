@@ -353,6 +353,11 @@ def run_gpu_arm(args) -> None:
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        # captured graphs that hold collectives must be gone before the communicator is
+        import gc
+
+        gc.collect()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 

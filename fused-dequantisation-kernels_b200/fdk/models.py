@@ -467,6 +467,11 @@ def _main() -> None:
                 if log is not None:
                     log(out)
     if world > 1:
+        # captured graphs that hold collectives must be gone before the communicator is
+        import gc
+
+        gc.collect()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 
