@@ -79,3 +79,23 @@ def test_shard_helpers_reject_uneven_splits():
     with pytest.raises(AssertionError):
         llama.shard_columns(96, llama.TensorParallel(0, 2))
     assert llama.shard_columns(6144, llama.TensorParallel(7, 8)) == slice(5376, 6144)
+
+
+def test_gate_up_rows_alternate_in_groups_of_32():
+    """The fused gate|up weight holds, per 64 rows, 32 gate rows and then the 32 matching up
+    rows (what FDK_FLAG_SILU_PAIRS and fdk_silu_mul with group 32 expect), for every rank."""
+    dims = models.LlamaDims("tiny", 128, 1, 4, 2, 256, vocab_size=64)
+    g = torch.Generator().manual_seed(1)
+    d = dims.head_dim
+    draw = lambda n, k: torch.randn((n, k), generator=g).bfloat16()
+    q, k, v, o = draw(4 * d, 128), draw(2 * d, 128), draw(2 * d, 128), draw(128, 4 * d)
+    gate, up, down = draw(256, 128), draw(256, 128), draw(128, 256)
+    for rank in range(2):
+        tp = llama.TensorParallel(rank, 2)
+        _, _, gu, down_s = llama.LlamaDecoder._shard_layer_weights(q, k, v, o, gate, up, down, dims, tp)
+        rows = llama.shard_rows(256, tp)
+        assert gu.shape == (2 * (rows.stop - rows.start), 128)
+        blocks = gu.unflatten(0, (-1, 2, llama.PAIR_GROUP))
+        assert torch.equal(blocks[:, 0].flatten(0, 1), gate[rows])
+        assert torch.equal(blocks[:, 1].flatten(0, 1), up[rows])
+        assert torch.equal(down_s, down[:, rows])
