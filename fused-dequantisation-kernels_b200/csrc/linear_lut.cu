@@ -928,7 +928,7 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
     }
     p.seq = (const uint32_t*)((const uint8_t*)ex->buffers[ex->rank] + kTpSeqOffset);
   }
-  if (ex == nullptr && m > 16) {
+  if (ex == nullptr && !(flags & FDK_FLAG_SILU_PAIRS) && m > 8) {
     return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, dtype == FDK_DTYPE_F16, workspace, workspace_bytes,
                        di.sm_count,
                        (cudaStream_t)stream);

@@ -205,7 +205,7 @@ constexpr size_t kTcPartialOffset = kGemvEnd + 16384;
 constexpr size_t kTcPartialTileBytes = (size_t)128 * 256 * sizeof(float);
 constexpr size_t kWorkspaceBytes = kTcPartialOffset + 148 * kTcPartialTileBytes;
 
-// Tensor-core GEMM for batches above 16 rows (gemm_lut_tc.cu).
+// Tensor-core GEMM for batches above 8 rows (gemm_lut_tc.cu).
 int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out, int m, int n,
                 int k, int bits, bool fp16, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
 

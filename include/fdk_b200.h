@@ -55,8 +55,9 @@ extern "C" {
 #define FDK_FLAG_SILU_PAIRS 2u /* the weight rows come in groups of 64: 32 "gate" rows, then
                            the 32 matching "up" rows; the kernel writes
                            out[m, n / 2] = silu(gate) * up instead of the [m, n] products,
-                           with the roundings of fdk_linear_lut followed by fdk_silu_mul
-                           (group 32).  m <= 16, n a multiple of 64.                   */
+                           with the roundings of fdk_linear_lut (as it is up to 8 rows)
+                           followed by fdk_silu_mul (group 32).  m <= 16, n a multiple
+                           of 64.                                                      */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int fdk_version(void);
@@ -181,8 +182,9 @@ int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache
 
 /* fdk_linear_lut for callers that cannot allocate device memory where they call it -- a
  * plugin inside a host runtime that owns all device allocations, or code running while a
- * stream capture forbids cudaMalloc.  Same arguments and results as fdk_linear_lut minus the
- * workspace: the scratch is an array inside the library image (1,327,104 bytes, enough for a
+ * stream capture forbids cudaMalloc.  Same arguments as fdk_linear_lut minus the workspace, same
+ * results (for 9 rows and more up to the order of the fp32 partial sums, the built-in scratch
+ * having no room for the tensor-core kernel's split tiles): the scratch is an array inside the library image (1,327,104 bytes, enough for a
  * GPU of up to 160 multiprocessors; a larger GPU is refused with FDK_ERR_WORKSPACE), held by
  * every GPU that loads the library until the process exits.  The call itself allocates
  * nothing, on the host or the device.
