@@ -7,6 +7,7 @@
 // model's definition (RMSNorm in fp32 with the weight applied after the cast, rotate-half
 // rotary embedding with cos/sin rounded to the activation type).
 #include <cstring>
+#include <type_traits>
 
 #include "fdk_common.cuh"
 #include "tp_exchange.cuh"
@@ -408,6 +409,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float part[kAttnWarps][G][132];
+  __shared__ float wbuf[kAttnWarps][16 * 4 > 8 * G ? 16 * 4 : 8 * G];  // softmax weights of a round, per warp: U * G
   __shared__ int is_last;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -445,26 +447,58 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 #pragma unroll
       for (int j = 0; j < G; ++j) s[u][j] = qf[j][0] * k0 + qf[j][1] * k1 + qf[j][2] * k2 + qf[j][3] * k3;
     }
+    // Sum the 32 lanes' partial dot products.  Not U * G butterflies (5 shuffles each): the
+    // position range is halved with the lane distance, so that after log2(U) rounds a group
+    // of 32 / U lanes holds the G totals of ONE position (u_own), at a fifth of the shuffles.
+    auto halve = [&](auto hc, int off) {
+      constexpr int H = decltype(hc)::value;
+      const bool upper = (lane & off) != 0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
+      for (int u = 0; u < H; ++u)
 #pragma unroll
-      for (int u = 0; u < U; ++u)
+        for (int j = 0; j < G; ++j) {
+          const float send = upper ? s[u][j] : s[u + H][j];
+          const float keep = upper ? s[u + H][j] : s[u][j];
+          s[u][j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    };
+    if constexpr (U == 16) {
+      halve(std::integral_constant<int, 8>{}, 16);
+      halve(std::integral_constant<int, 4>{}, 8);
+      halve(std::integral_constant<int, 2>{}, 4);
+      halve(std::integral_constant<int, 1>{}, 2);
+    } else {
+      halve(std::integral_constant<int, 4>{}, 16);
+      halve(std::integral_constant<int, 2>{}, 8);
+      halve(std::integral_constant<int, 1>{}, 4);
 #pragma unroll
-        for (int j = 0; j < G; ++j) s[u][j] += __shfl_xor_sync(0xffffffffu, s[u][j], o);
+      for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 2);
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 1);
+    const int u_own = lane / (32 / U);
+    const bool live = pb + u_own < p1;
+    float* wrow = wbuf[warp];
+    float corr[G];
 #pragma unroll
     for (int j = 0; j < G; ++j) {
-      float m_new = mx[j];
+      const float mine = live ? s[0][j] : -INFINITY;
+      float m_new = mine;
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (pb + u >= p1) s[u][j] = -INFINITY;
-        m_new = fmaxf(m_new, s[u][j]);
-      }
-      const float corr = __expf(mx[j] - m_new);
+      for (int o = 16; o > 0; o >>= 1) m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, o));
+      m_new = fmaxf(m_new, mx[j]);
+      corr[j] = __expf(mx[j] - m_new);
       mx[j] = m_new;
-      float l = sum[j] * corr, a0 = acc[j][0] * corr, a1 = acc[j][1] * corr, a2 = acc[j][2] * corr, a3 = acc[j][3] * corr;
+      wrow[u_own * G + j] = __expf(mine - m_new);  // exp(-inf) = 0 for masked positions; every lane of the group writes the same value
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      float l = sum[j] * corr[j], a0 = acc[j][0] * corr[j], a1 = acc[j][1] * corr[j], a2 = acc[j][2] * corr[j],
+            a3 = acc[j][3] * corr[j];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const float w = __expf(s[u][j] - m_new);  // exp(-inf) = 0 for masked positions
+        const float w = wrow[u * G + j];  // broadcast read
         l += w;
         a0 += w * pair_lo<false>(vv[u].x);
         a1 += w * pair_hi<false>(vv[u].x);
@@ -473,6 +507,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       }
       sum[j] = l; acc[j][0] = a0; acc[j][1] = a1; acc[j][2] = a2; acc[j][3] = a3;
     }
+    __syncwarp();  // the weights are read before the next round overwrites them
   }
   // merge the warps of the CTA (fixed order)
 #pragma unroll
