@@ -263,10 +263,12 @@ __global__ void __launch_bounds__(kTcThreads, 2)
         if (!mbar_wait(tma_full + 8 * s, phase)) { timed_out = true; break; }
         if (!mbar_wait(a_full + 8 * s, phase)) { timed_out = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // one descriptor pair per stage; the four K = 16 slices of the 64-column block lie 32
+        // bytes apart, i.e. 2 in the descriptors' 16-byte address units
+        const uint64_t a_desc = umma_desc(p.a_addr[s]), b_desc = umma_desc(p.b_addr[s]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          umma_bf16(tmem_base, umma_desc(p.a_addr[s] + j * 32), umma_desc(p.b_addr[s] + j * 32), idesc,
-                    (i > 0 || j > 0) ? 1u : 0u);
+          umma_bf16(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc, (i > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
       }
