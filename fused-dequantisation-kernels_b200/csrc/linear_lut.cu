@@ -193,7 +193,13 @@ constexpr uint32_t kSpinLimit = 1u << 24;  // polls of a memory word before givi
 // E = NB * 4 * SW floats laid out [sub-tile][n-tile][t][g][4].  Plain loops on purpose (this
 // runs once or twice per CTA, so its cost is mostly instruction fetches).  Returns false if a
 // bounded poll ran out.
-template <int NB, int WARPS, bool FP16>
+// EPI: what is done with a finished row tile -- kEpiStore: written to `out`; kEpiSilu:
+// silu(gate) * up written to `out`; kEpiPush: stored into every rank's exchange buffer.  A
+// template parameter so that the plain kernel carries none of the other two's code (code that
+// runs once per CTA costs mostly its instruction fetches).
+constexpr int kEpiStore = 0, kEpiSilu = 1, kEpiPush = 2;
+
+template <int NB, int WARPS, bool FP16, int EPI>
 __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots, int rt, int c0, int c1, uint32_t push_seq) {
   constexpr int EMAX = 512 * NB;  // outputs of one row tile at TT = 4
   const int lane = threadIdx.x & 31;
@@ -294,12 +300,12 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
         const int b = 8 * nb + 2 * tq + (c & 1);
         if (row < p.n && b < p.m) {
           const uint16_t v = from_float<FP16>(slots[blk * sw + tq * 32 + lane]);
-          if (p.tp > 0) gathered[b * kTileRows + lrow] = v;
-          else if (!p.silu) p.out[(size_t)b * p.n + row] = v;
+          if constexpr (EPI == kEpiPush) gathered[b * kTileRows + lrow] = v;
+          else if constexpr (EPI == kEpiStore) p.out[(size_t)b * p.n + row] = v;
         }
       }
     }
-    if (p.silu) {  // sub-tiles 0,1 hold gate rows, 2,3 the matching up rows
+    if constexpr (EPI == kEpiSilu) {  // sub-tiles 0,1 hold gate rows, 2,3 the matching up rows
       auto rnd = [](float v) { return to_float<FP16>(from_float<FP16>(v)); };
 #pragma unroll 1
       for (int blk = 0; blk < 2 * NB; ++blk) {
@@ -317,7 +323,7 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
         }
       }
     }
-    if (p.tp > 0) {
+    if constexpr (EPI == kEpiPush) {
       __syncwarp();
       const uint32_t tag = push_seq + 1u;
       const size_t base = ((size_t)((push_seq & 1u) * p.tp + p.rank) * p.stage_slot + (size_t)rt * kTileRows) / 2;
@@ -345,7 +351,7 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
 // ---- the kernel -------------------------------------------------------------------
 constexpr int kXRowPad = 16;  // x rows in a stage are 16 bytes apart from a 128-byte multiple: no bank conflicts
 
-template <int BITS, int NB, int WARPS, bool FP16>
+template <int BITS, int NB, int WARPS, bool FP16, int EPI>
 __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
@@ -454,7 +460,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
   // everything above touched only weights; x, out and the workspace follow stream order
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // number of this push = reduces completed before this launch (the reduce kernel counts)
-  const uint32_t push_seq = p.tp > 0 ? (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq)) : 0u;
+  const uint32_t push_seq = EPI == kEpiPush ? (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq)) : 0u;
   __syncwarp();
   if (p.xres_addr != 0 && warp == 0) {  // small x: one copy per batch row for the whole kernel
     if (lane == 0) {
@@ -528,7 +534,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
       if (old == W - 1) {  // every warp of the CTA has deposited: this warp finishes the tile
         __threadfence_block();
         FDK_T(long long tf = clock64();)
-        if (!tile_finish<NB, WARPS, FP16>(p, my_slots, cur_rt, c0, c1, push_seq)) timed_out = true;
+        if (!tile_finish<NB, WARPS, FP16, EPI>(p, my_slots, cur_rt, c0, c1, push_seq)) timed_out = true;
         FDK_T(tr_finish += clock64() - tf;)
         __syncwarp();
         if (lane == 0) {
@@ -728,13 +734,16 @@ size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
 template <int BITS, int NB, int WARPS, bool FP16>
 int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int grid, unsigned flags,
                    cudaStream_t stream) {
-  auto kernel = linear_lut_kernel<BITS, NB, WARPS, FP16>;
-  static size_t configured[64] = {};
+  const int epi = p.tp > 0 ? kEpiPush : (p.silu ? kEpiSilu : kEpiStore);
+  auto kernel = epi == kEpiPush   ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush>
+                : epi == kEpiSilu ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu>
+                                  : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore>;
+  static size_t configured[3][64] = {};
   int dev = 0;
   FDK_CUDA(cudaGetDevice(&dev));
-  if (configured[dev & 63] < smem) {
+  if (configured[epi][dev & 63] < smem) {
     FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[dev & 63] = smem;
+    configured[epi][dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
