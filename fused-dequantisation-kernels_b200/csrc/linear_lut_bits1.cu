@@ -1,0 +1,4 @@
+// The fused GEMV kernel for 1-bit codes.
+#include "linear_lut_kernel.cuh"
+
+template int fdk::launch_bits<1>(const fdk::LinearParams&, const void*, int, int, unsigned, cudaStream_t);
