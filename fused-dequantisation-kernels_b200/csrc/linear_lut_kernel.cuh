@@ -308,7 +308,7 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
 // ---- the kernel -------------------------------------------------------------------
 constexpr int kXRowPad = 16;  // x rows in a stage are 16 bytes apart from a 128-byte multiple: no bank conflicts
 
-template <int BITS, int NB, int WARPS, bool FP16, int EPI>
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, bool XRES>
 __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
   if (threadIdx.x == 0) {
     esync->count[0] = esync->count[1] = 0;
     esync->gen[0] = esync->gen[1] = 0;
-    if (p.xres_addr) mbar_init(p.xres_bar, 1);
+    if (XRES) mbar_init(p.xres_bar, 1);
   }
   const uint32_t lane_base = p.table_addr + T::lane_offset(lane);
 
@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
   auto issue_weights = [&](int i, int kpos, int s) {
     const uint32_t bar = bar_addr(s);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                 "r"((uint32_t)L::kSlabBytes + (p.xres_addr ? 0u : (uint32_t)p.m * x_bytes(kpos)))
+                 "r"((uint32_t)L::kSlabBytes + (XRES ? 0u : (uint32_t)p.m * x_bytes(kpos)))
                  : "memory");
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
   };
   // lanes 0..m-1: one x row each, for the same slab
   auto issue_x = [&](int kpos, int s) {
-    if (lane < p.m && p.xres_addr == 0) {
+    if (!XRES && lane < p.m) {
       asm volatile(
           "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
               stage_addr(s) + (uint32_t)L::kSlabBytes + lane * kXRow),
@@ -419,7 +419,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
   // number of this push = reduces completed before this launch (the reduce kernel counts)
   const uint32_t push_seq = EPI == kEpiPush ? (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq)) : 0u;
   __syncwarp();
-  if (p.xres_addr != 0 && warp == 0) {  // small x: one copy per batch row for the whole kernel
+  if (XRES && warp == 0) {  // small x: one copy per batch row for the whole kernel
     if (lane == 0) {
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(p.xres_bar),
                    "r"((uint32_t)p.m * (uint32_t)p.k * 2u)
@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
         const int b = min(g + 8 * nb, p.m - 1);  // lanes of unused batch columns read a live row
-        const uint32_t xa = p.xres_addr ? p.xres_addr + b * p.xres_row + (kpos * L::KSB + JB) * 128 + t * 32
+        const uint32_t xa = XRES ? p.xres_addr + b * p.xres_row + (kpos * L::KSB + JB) * 128 + t * 32
                                         : sa + L::kSlabBytes + b * kXRow + JB * 128 + t * 32;
         const uint4 lo = ring128(xa), hi = ring128(xa + 16);
         xb[nb][0] = lo.x; xb[nb][1] = lo.y; xb[nb][2] = lo.z; xb[nb][3] = lo.w;
@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     }
   };
 
-  if (p.xres_addr != 0 && it < c1) {
+  if (XRES && it < c1) {
     if (!mbar_wait(p.xres_bar, 0)) timed_out = true;
   }
   int s = 0;
@@ -661,15 +661,16 @@ template <int BITS, int NB, int WARPS, bool FP16>
 int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int grid, unsigned flags,
                    cudaStream_t stream) {
   const int epi = p.tp > 0 ? kEpiPush : (p.silu ? kEpiSilu : kEpiStore);
-  auto kernel = epi == kEpiPush   ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush>
-                : epi == kEpiSilu ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu>
-                                  : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore>;
-  static size_t configured[3][64] = {};
+  const bool xres = p.xres_addr != 0;
+  auto kernel = epi == kEpiPush   ? (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush, false>)
+                : epi == kEpiSilu ? (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu, false>)
+                                  : (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore, false>);
+  static size_t configured[6][64] = {};
   int dev = 0;
   FDK_CUDA(cudaGetDevice(&dev));
-  if (configured[epi][dev & 63] < smem) {
+  if (configured[2 * epi + xres][dev & 63] < smem) {
     FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[epi][dev & 63] = smem;
+    configured[2 * epi + xres][dev & 63] = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
