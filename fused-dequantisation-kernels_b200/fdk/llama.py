@@ -210,8 +210,9 @@ class LlamaDecoder(nn.Module):
         self.attn = torch.empty((batch, self.q_heads * 128), device=dev, dtype=dt)
         self.position = torch.zeros((), device=dev, dtype=torch.int64)
         # context slices per (batch row, KV head): about 128 keys each (a CTA's eight warps then
-        # load nearly all their keys in one go), as long as that stays within a few hundred CTAs
-        self.splits = max(1, min(max_len // 128, -(-512 // (batch * self.kv_heads)), 16))
+        # load nearly all their keys in one go), as long as that stays within one CTA per SM:
+        # more slices than that only add merge work (16 rows: 16 us unsliced, 32 us in 4 slices)
+        self.splits = max(1, min(max_len // 128, 148 // (batch * self.kv_heads), 16))
         self.attn_scratch, self.attn_counters = native.attention_scratch(batch, self.q_heads, self.kv_heads, self.splits, dev)
         # fused push + reduce instead of NCCL: quantised row-parallel projections, batch <= 16
         self.close()
