@@ -192,7 +192,8 @@ __global__ void rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restr
 
 // One CTA (64 threads) per (batch row, head of the fused q|k|v projection); head_dim = 128.
 // q heads: rotated, written to q_out.  k heads: rotated, written to the cache at *pos.
-// v heads: copied to the cache at *pos.
+// v heads: copied to the cache at *pos.  A position outside [0, max_len) -- one decode step
+// too many, a stale position buffer -- leaves the caches untouched (q is still written).
 __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long long* __restrict__ pos_ptr,
                                    uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
                                    uint16_t* __restrict__ v_cache, int q_heads, int kv_heads, int max_len,
@@ -200,9 +201,11 @@ __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long 
   pdl_prologue();
   const int row = blockIdx.y, head = blockIdx.x, i = threadIdx.x;  // i in 0..63: the pair (i, i + 64)
   const long long pos = *pos_ptr;
+  const bool in_cache = pos >= 0 && pos < max_len;
   const int heads_total = q_heads + 2 * kv_heads;
   const uint16_t* src = qkv + ((size_t)row * heads_total + head) * 128;
   if (head >= q_heads + kv_heads) {  // v
+    if (!in_cache) return;
     const int kvh = head - q_heads - kv_heads;
     uint16_t* dst = v_cache + (((size_t)row * kv_heads + kvh) * max_len + pos) * 128;
     dst[i] = src[i];
@@ -222,6 +225,7 @@ __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long 
   if (head < q_heads) {
     dst = q_out + ((size_t)row * q_heads + head) * 128;
   } else {
+    if (!in_cache) return;
     dst = k_cache + (((size_t)row * kv_heads + (head - q_heads)) * max_len + pos) * 128;
   }
   dst[i] = o0;
@@ -413,7 +417,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   __shared__ int is_last;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int len = (int)(*pos_ptr) + 1;  // the current token's key and value are already in the cache
+  // the current token's key and value are already in the cache; a position outside the cache is
+  // clamped (no key at all gives zeros)
+  const long long pos_now = *pos_ptr;
+  const int len = pos_now < 0 ? 0 : (pos_now >= max_len ? max_len : (int)pos_now + 1);
   const int p0 = split * chunk, p1 = min(len, p0 + chunk);
 
   float qf[G][4], acc[G][4], mx[G], sum[G];
@@ -536,7 +543,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
         a += part[w][j][d] * c;
       }
       if (splits == 1) {
-        out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(a / l);
+        out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(l > 0.f ? a / l : 0.f);
       } else {
         __stcg(mine + j * 130 + d, a);
         if (d == 0) {
@@ -583,7 +590,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       float a = 0.f;
 #pragma unroll 8
       for (int s2 = 0; s2 < splits; ++s2) a += __ldcg(base + s2 * (G * 130) + j * 130 + d) * coef[j][s2];
-      out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(a / denom[j]);
+      out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(denom[j] > 0.f ? a / denom[j] : 0.f);
     }
   }
   if (threadIdx.x == 0) counters[b * kv_heads + kvh] = 0;

@@ -1,6 +1,5 @@
 // C entry points of the fused GEMV / skinny GEMM (the kernel itself: linear_lut_kernel.cuh,
 // instantiated per code width in linear_lut_bits*.cu).
-#include <cstdlib>
 #include <cstring>
 
 #include "linear_lut_params.cuh"
@@ -39,11 +38,6 @@ int dynamic_smem_base(uint32_t* out) {
 }  // namespace fdk
 
 using namespace fdk;
-
-#ifdef FDK_TRACE
-static unsigned long long* g_trace = nullptr;
-extern "C" void fdk_debug_set_trace(void* p) { g_trace = (unsigned long long*)p; }
-#endif
 
 extern "C" int fdk_workspace_size(size_t* bytes_host) {
   FDK_CHECK_ARG(bytes_host != nullptr, FDK_ERR_BAD_ARG, "bytes_host is null");
@@ -101,11 +95,10 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
   p.k = k;
   p.k_slabs = d.k_slabs;
   p.total = d.row_tiles * d.k_slabs;
+  p.k_magic = d.k_slabs > 1 ? (uint32_t)((((uint64_t)1 << 32) + d.k_slabs - 1) / d.k_slabs) : 0u;
+  FDK_CHECK_ARG((uint64_t)p.total * d.k_slabs < ((uint64_t)1 << 32), FDK_ERR_SHAPE, "matrix of %d x %d slabs is too large", d.row_tiles, d.k_slabs);
   const int grid = di.sm_count;  // the launcher turns this into one or two CTAs per SM
   p.silu = (flags & FDK_FLAG_SILU_PAIRS) ? 1 : 0;
-#ifdef FDK_TRACE
-  p.trace = g_trace;
-#endif
   if (ex != nullptr) {
     FDK_CHECK_ARG(ex->tp >= 1 && ex->tp <= kTpMaxRanks && ex->rank >= 0 && ex->rank < ex->tp, FDK_ERR_BAD_ARG,
                   "tp=%d, rank=%d", ex->tp, ex->rank);

@@ -1,42 +1,48 @@
 // Fused dequantise + GEMV / skinny GEMM for sm_100a:  out[m, n] = x[m, k] . W[n, k]^T,
 // W given as tiled low-bit codes + block scales + a lookup table (fdk_layout.cuh).
 //
-// Shape of the kernel (persistent CTAs of 12, 8 or 4 warps, sized so that two fit on an SM):
+// Shape of the kernel (one persistent CTA per SM: 19 compute warps and one finisher warp for
+// batches up to 8 rows, 15 + 1 for 9 to 16 rows):
 //   * The weight stream is cut into slabs (64 rows x 64*KSB columns, 2-6 KB).  The
 //     slabs of the whole matrix form one linear sequence (row tile major); CTA c owns
-//     a contiguous range of it ("stream-K"), its warps take slabs round-robin.  Every
-//     SM therefore streams the same number of bytes (+-1 slab) whatever N and K are.
-//     A large matrix runs two CTAs per SM; a small one runs one, and the other half of
-//     the SM is free for the next kernel on the stream, which under programmatic
-//     dependent launch fills its table and prefetches weights while this one runs.
-//   * Every warp owns a small ring of slab-sized stages in shared memory.  Lane 0
-//     fills them with one bulk asynchronous copy per slab (cp.async.bulk, completion
-//     on an mbarrier), so the data in flight costs no registers and the loads need
-//     no issue slots.  x is staged whole once per CTA when it is small, otherwise
-//     its rows travel with each slab.  All waits on the barriers are bounded.
+//     a contiguous range of it ("stream-K"), its compute warps take slabs round-robin.
+//     Every SM therefore streams the same number of bytes (+-1 slab) whatever N and K are.
+//   * Weights go from global memory straight into registers: a lane's share of a slab
+//     is a handful of 16-byte vectors that are contiguous across the warp (512 B per
+//     load instruction, streaming loads that do not allocate in L1).  A warp holds two
+//     slabs of registers, used alternately: while it works on one, the loads of its next
+//     slab are in flight into the other, and L2 has been asked for the one after that
+//     (prefetch.global.L2, a line per lane).  The codes never pass through shared
+//     memory.  The first loads are issued before the kernel waits for its predecessor
+//     on the stream (programmatic dependent launch): they read weights only.
+//   * x is copied once per CTA into shared memory when it fits (after the wait),
+//     otherwise its fragments are read from L2 as they are needed.
 //   * Codes are turned into tensor-core A fragments by table lookup in shared memory:
-//     one code byte indexes a replicated byte table (lut_table.cuh), so a lookup is one
-//     PRMT (extract the byte), one multiply-add (address) and one conflict-free LDS
-//     that returns 2 (4-bit), 4 (2-bit) or 8 (1-bit) 16-bit weights already in
-//     fragment order.  The table itself arrives inside the kernel parameters.
+//     one code byte indexes a byte table replicated per lane (lut_table.cuh) whose rows
+//     are 256 bytes apart in a table that starts at a multiple of 64 KB of the shared
+//     window, so a lookup is one PRMT (the code byte dropped into bits 8..15 of the
+//     lane's table address) and one conflict-free LDS that returns 2 (4-bit), 4 (2-bit)
+//     or 8 (1-bit) 16-bit weights already in fragment order.  The table itself arrives
+//     inside the kernel parameters.
 //   * mma.sync m16n8k16 accumulates one 64-block in fp32; the block scale multiplies
 //     the fp32 block sum (4 FMAs per 1024 weights), then running totals per row.
 //     The tensor pipe is used because the FMA work would otherwise compete with the
-//     lookups for issue slots; at m <= 16 it is far from being the limiter, so the
-//     synchronous MMA form is enough and keeps the weights in registers (a tcgen05
-//     MMA would need them written back to shared or tensor memory first).  What
-//     bounds the main loop is the shared-memory pipe: one 128-byte wavefront per 32
-//     code bytes looked up, plus the wavefronts that bring codes and x in.
-//   * At a row-tile boundary the warps of a CTA deposit their totals in shared memory
-//     and the last to arrive adds them in warp order (no CTA barrier).  A row tile
-//     split over several CTAs is finished by the CTA holding its first slabs: the
-//     others publish their sums to the workspace as {value, tag} words, which the
-//     finisher reads (bounded polling) and adds in CTA order.  The summation order
-//     never depends on timing, so results are reproducible bit for bit.
+//     lookups for issue slots; the synchronous MMA form keeps the weights in registers
+//     (a tcgen05 MMA would need them written to shared or tensor memory first).  What
+//     bounds the main loop is instruction issue: about 130 lookup instructions, 16 MMAs
+//     and 24 scale instructions per 4096 weights.
+//   * At a row-tile boundary a compute warp deposits its totals in shared memory and moves
+//     on; the finisher warp adds the deposits in warp order and writes the outputs.  A row
+//     tile split over several CTAs is finished by the CTA holding its first slabs: the
+//     others publish their sums to the workspace as {value, tag} words, which that CTA's
+//     finisher fetches (bounded polling) while the compute warps are still busy, and adds
+//     in CTA order.  The summation order never depends on timing, so results are
+//     reproducible bit for bit.
 //   * Epilogue variants: plain store; silu(gate) * up for a gate|up weight stored in
 //     32 + 32 row groups; or, in tensor-parallel decode, tagged stores of the partial
-//     sums into every rank's exchange buffer.#pragma once
-#include <cstdlib>
+//     sums into every rank's exchange buffer.
+#pragma once
+#include <atomic>
 #include <cstring>
 #include <type_traits>
 
@@ -53,48 +59,48 @@ namespace {
 //   a[s][2] = row g,   elements 4s+2, 4s+3    a[s][3] = row g+8, elements 4s+2, 4s+3
 // (elements counted inside the lane's 16-element share of the block; x is read
 // with the same numbering, so the product does not depend on it).
-template <int BITS, int JB>
+template <int BITS, int JB, bool WIDE>
 __device__ __forceinline__ void build_fragments(const uint4 (&code)[Layout<BITS>::V], uint32_t lane_base,
                                                 uint32_t (&a)[4][4]) {
   if constexpr (BITS == 4) {
     const uint4& c = code[0];
-    a[0][0] = lut32(entry_addr<4, 0>(c.x, lane_base)); a[0][2] = lut32(entry_addr<4, 1>(c.x, lane_base));
-    a[1][0] = lut32(entry_addr<4, 2>(c.x, lane_base)); a[1][2] = lut32(entry_addr<4, 3>(c.x, lane_base));
-    a[2][0] = lut32(entry_addr<4, 0>(c.y, lane_base)); a[2][2] = lut32(entry_addr<4, 1>(c.y, lane_base));
-    a[3][0] = lut32(entry_addr<4, 2>(c.y, lane_base)); a[3][2] = lut32(entry_addr<4, 3>(c.y, lane_base));
-    a[0][1] = lut32(entry_addr<4, 0>(c.z, lane_base)); a[0][3] = lut32(entry_addr<4, 1>(c.z, lane_base));
-    a[1][1] = lut32(entry_addr<4, 2>(c.z, lane_base)); a[1][3] = lut32(entry_addr<4, 3>(c.z, lane_base));
-    a[2][1] = lut32(entry_addr<4, 0>(c.w, lane_base)); a[2][3] = lut32(entry_addr<4, 1>(c.w, lane_base));
-    a[3][1] = lut32(entry_addr<4, 2>(c.w, lane_base)); a[3][3] = lut32(entry_addr<4, 3>(c.w, lane_base));
+    a[0][0] = lut32(entry_addr<4, 0, WIDE>(c.x, lane_base)); a[0][2] = lut32(entry_addr<4, 1, WIDE>(c.x, lane_base));
+    a[1][0] = lut32(entry_addr<4, 2, WIDE>(c.x, lane_base)); a[1][2] = lut32(entry_addr<4, 3, WIDE>(c.x, lane_base));
+    a[2][0] = lut32(entry_addr<4, 0, WIDE>(c.y, lane_base)); a[2][2] = lut32(entry_addr<4, 1, WIDE>(c.y, lane_base));
+    a[3][0] = lut32(entry_addr<4, 2, WIDE>(c.y, lane_base)); a[3][2] = lut32(entry_addr<4, 3, WIDE>(c.y, lane_base));
+    a[0][1] = lut32(entry_addr<4, 0, WIDE>(c.z, lane_base)); a[0][3] = lut32(entry_addr<4, 1, WIDE>(c.z, lane_base));
+    a[1][1] = lut32(entry_addr<4, 2, WIDE>(c.z, lane_base)); a[1][3] = lut32(entry_addr<4, 3, WIDE>(c.z, lane_base));
+    a[2][1] = lut32(entry_addr<4, 0, WIDE>(c.w, lane_base)); a[2][3] = lut32(entry_addr<4, 1, WIDE>(c.w, lane_base));
+    a[3][1] = lut32(entry_addr<4, 2, WIDE>(c.w, lane_base)); a[3][3] = lut32(entry_addr<4, 3, WIDE>(c.w, lane_base));
   } else if constexpr (BITS == 2) {
     const uint4& c = code[0];
     const uint32_t wg = word_of<2 * JB>(c), wh = word_of<2 * JB + 1>(c);
     uint2 q;
-    q = lut64(entry_addr<2, 0>(wg, lane_base)); a[0][0] = q.x; a[0][2] = q.y;
-    q = lut64(entry_addr<2, 1>(wg, lane_base)); a[1][0] = q.x; a[1][2] = q.y;
-    q = lut64(entry_addr<2, 2>(wg, lane_base)); a[2][0] = q.x; a[2][2] = q.y;
-    q = lut64(entry_addr<2, 3>(wg, lane_base)); a[3][0] = q.x; a[3][2] = q.y;
-    q = lut64(entry_addr<2, 0>(wh, lane_base)); a[0][1] = q.x; a[0][3] = q.y;
-    q = lut64(entry_addr<2, 1>(wh, lane_base)); a[1][1] = q.x; a[1][3] = q.y;
-    q = lut64(entry_addr<2, 2>(wh, lane_base)); a[2][1] = q.x; a[2][3] = q.y;
-    q = lut64(entry_addr<2, 3>(wh, lane_base)); a[3][1] = q.x; a[3][3] = q.y;
+    q = lut64(entry_addr<2, 0, WIDE>(wg, lane_base)); a[0][0] = q.x; a[0][2] = q.y;
+    q = lut64(entry_addr<2, 1, WIDE>(wg, lane_base)); a[1][0] = q.x; a[1][2] = q.y;
+    q = lut64(entry_addr<2, 2, WIDE>(wg, lane_base)); a[2][0] = q.x; a[2][2] = q.y;
+    q = lut64(entry_addr<2, 3, WIDE>(wg, lane_base)); a[3][0] = q.x; a[3][2] = q.y;
+    q = lut64(entry_addr<2, 0, WIDE>(wh, lane_base)); a[0][1] = q.x; a[0][3] = q.y;
+    q = lut64(entry_addr<2, 1, WIDE>(wh, lane_base)); a[1][1] = q.x; a[1][3] = q.y;
+    q = lut64(entry_addr<2, 2, WIDE>(wh, lane_base)); a[2][1] = q.x; a[2][3] = q.y;
+    q = lut64(entry_addr<2, 3, WIDE>(wh, lane_base)); a[3][1] = q.x; a[3][3] = q.y;
   } else if constexpr (BITS == 1) {
     const uint32_t w = word_of<JB>(code[0]);  // bytes 0,1: row g; bytes 2,3: row g+8
     uint4 q;
-    q = lut128(entry_addr<1, 0>(w, lane_base)); a[0][0] = q.x; a[0][2] = q.y; a[1][0] = q.z; a[1][2] = q.w;
-    q = lut128(entry_addr<1, 1>(w, lane_base)); a[2][0] = q.x; a[2][2] = q.y; a[3][0] = q.z; a[3][2] = q.w;
-    q = lut128(entry_addr<1, 2>(w, lane_base)); a[0][1] = q.x; a[0][3] = q.y; a[1][1] = q.z; a[1][3] = q.w;
-    q = lut128(entry_addr<1, 3>(w, lane_base)); a[2][1] = q.x; a[2][3] = q.y; a[3][1] = q.z; a[3][3] = q.w;
+    q = lut128(entry_addr<1, 0, WIDE>(w, lane_base)); a[0][0] = q.x; a[0][2] = q.y; a[1][0] = q.z; a[1][2] = q.w;
+    q = lut128(entry_addr<1, 1, WIDE>(w, lane_base)); a[2][0] = q.x; a[2][2] = q.y; a[3][0] = q.z; a[3][2] = q.w;
+    q = lut128(entry_addr<1, 2, WIDE>(w, lane_base)); a[0][1] = q.x; a[0][3] = q.y; a[1][1] = q.z; a[1][3] = q.w;
+    q = lut128(entry_addr<1, 3, WIDE>(w, lane_base)); a[2][1] = q.x; a[2][3] = q.y; a[3][1] = q.z; a[3][3] = q.w;
   } else if constexpr (BITS == 8) {
     const uint4& cg = code[0];  // row g: 16 bytes = 16 elements
     const uint4& ch = code[1];  // row g+8
 #pragma unroll
     for (int st = 0; st < 4; ++st) {
       const uint32_t wg = word_at(cg, st), wh = word_at(ch, st);
-      a[st][0] = prmt<0x7610>(lut32(entry_addr<8, 0>(wg, lane_base)), lut32(entry_addr<8, 1>(wg, lane_base)));
-      a[st][2] = prmt<0x7610>(lut32(entry_addr<8, 2>(wg, lane_base)), lut32(entry_addr<8, 3>(wg, lane_base)));
-      a[st][1] = prmt<0x7610>(lut32(entry_addr<8, 0>(wh, lane_base)), lut32(entry_addr<8, 1>(wh, lane_base)));
-      a[st][3] = prmt<0x7610>(lut32(entry_addr<8, 2>(wh, lane_base)), lut32(entry_addr<8, 3>(wh, lane_base)));
+      a[st][0] = prmt<0x7610>(lut32(entry_addr<8, 0, WIDE>(wg, lane_base)), lut32(entry_addr<8, 1, WIDE>(wg, lane_base)));
+      a[st][2] = prmt<0x7610>(lut32(entry_addr<8, 2, WIDE>(wg, lane_base)), lut32(entry_addr<8, 3, WIDE>(wg, lane_base)));
+      a[st][1] = prmt<0x7610>(lut32(entry_addr<8, 0, WIDE>(wh, lane_base)), lut32(entry_addr<8, 1, WIDE>(wh, lane_base)));
+      a[st][3] = prmt<0x7610>(lut32(entry_addr<8, 2, WIDE>(wh, lane_base)), lut32(entry_addr<8, 3, WIDE>(wh, lane_base)));
     }
   } else {  // 3 bits: 96-bit little-endian group per block, pair field f at bits [6f, 6f+6)
     uint32_t w[3];
@@ -121,19 +127,22 @@ __device__ __forceinline__ void build_fragments(const uint4 (&code)[Layout<BITS>
 
 
 // ---- row-tile epilogue ----------------------------------------------------------
-// No CTA-wide barrier anywhere: a warp that has finished its slabs of a row tile deposits its
-// totals in shared memory and moves on; the LAST warp of the CTA to do so adds the deposits
-// up in warp order and finishes the tile (tile_finish).
-//
-// A row tile whose K range is split over several CTAs is finished by its OWNER, the CTA that
-// holds the tile's first slabs (for that CTA the tile is the last thing it works on).  The
-// other CTAs hold later slabs of the tile at the START of their ranges, so they are done with
-// it early: each stores its partial sums as {value, tag} 8-byte words into its own area of
-// the workspace and never waits.  The owner polls those words (bounded) until they carry this
-// use's tag, adds them to its own sums in CTA order, writes the outputs and bumps the tile's
-// use count.  tag = (use count + 1) * 4096 + row tile: a word left by an earlier launch or
-// another tile can never match.  No fences, no atomics, one memory round trip at the end;
-// and every sum has a fixed order, so results do not depend on timing.
+// The warps that stream weights ("compute warps") never finish a row tile themselves: when a
+// warp has worked through its slabs of a tile it deposits its totals in shared memory, bumps
+// the tile's deposit count and moves on.  One extra warp of the CTA, the FINISHER, does the
+// rest, so that every memory round trip of the epilogue runs beside the main loop instead of
+// inside it: it waits for the deposits of a tile, adds them in warp order and
+//   * writes the outputs, if the CTA holds the whole tile;
+//   * publishes the sums, if the CTA holds a later part of a tile that starts in another CTA
+//     (the tile is then the first thing the CTA works on): {value, tag} 8-byte words into the
+//     CTA's own area of the workspace, never waiting for anybody;
+//   * if the CTA holds the FIRST slabs of a tile that continues in the following CTAs (its
+//     OWNER; the tile is then the last thing the CTA works on): fetches the words of those CTAs
+//     -- as a rule published earlier, so the finisher has them before the compute warps are
+//     done -- adds them in CTA order, writes the outputs and bumps the tile's use count.
+// tag = (use count + 1) * 4096 + row tile: a word left by an earlier launch or another tile can
+// never match.  No fences, no atomics on global memory; every sum has a fixed order, so results
+// do not depend on timing.  All waits are bounded and report through the status word.
 //
 // Reduction slots keep, per warp, sub-tile and n-tile, the float4 accumulator fragments of
 // the lanes that hold live batch columns only: lanes with t < TT, TT = ceil(min(m, 8) / 2),
@@ -146,99 +155,124 @@ struct EpilogueSync {
 
 constexpr uint32_t kSpinLimit = 1u << 24;  // polls of a memory word before giving up
 
-// Run by one warp.  `slots` is the slot set of this row tile: per warp one block of
-// E = NB * 4 * SW floats laid out [sub-tile][n-tile][t][g][4].  Plain loops on purpose (this
-// runs once or twice per CTA, so its cost is mostly instruction fetches).  Returns false if a
-// bounded poll ran out.
 // EPI: what is done with a finished row tile -- kEpiStore: written to `out`; kEpiSilu:
 // silu(gate) * up written to `out`; kEpiPush: stored into every rank's exchange buffer.  A
-// template parameter so that the plain kernel carries none of the other two's code (code that
-// runs once per CTA costs mostly its instruction fetches).
+// template parameter so that the plain kernel carries none of the other two's code.
 constexpr int kEpiStore = 0, kEpiSilu = 1, kEpiPush = 2;
 
+// n / k_slabs for n * k_slabs < 2^32, by multiplication with k_magic = ceil(2^32 / k_slabs)
+__device__ __forceinline__ int div_k(const LinearParams& p, int n) {
+  return p.k_slabs == 1 ? n : (int)__umulhi((uint32_t)n, p.k_magic);
+}
+__device__ __forceinline__ int cta_begin(const LinearParams& p, int c) { return c * p.base + min(c, p.rem); }
+__device__ __forceinline__ int cta_of(const LinearParams& p, int item) {
+  const int big = p.rem * (p.base + 1);
+  return item < big ? item / (p.base + 1) : p.rem + (item - big) / p.base;
+}
+
+// Owner of a split tile: adds the sums published by the CTAs after this one, up to the one
+// holding the tile's last slab, in CTA order, into stash[0, E).  Run by one warp, lane l taking
+// elements 4 l .. 4 l + 3 of every 128; the words of up to four CTAs are in flight together,
+// and a round that finds a stale tag is repeated after a short sleep.  Returns false if that
+// ran out.
+template <int NB>
+__device__ __forceinline__ bool fetch_foreign(const LinearParams& p, float* stash, int rt, uint32_t tag, int E) {
+  constexpr int EMAX = 512 * NB;
+  const int lane = threadIdx.x & 31;
+  const int last = cta_of(p, (rt + 1) * p.k_slabs - 1);
+  bool ok = true;
+#pragma unroll 1
+  for (int e0 = lane * 4; e0 < E; e0 += 128) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int cb0 = blockIdx.x + 1; cb0 <= last; cb0 += 4) {
+      uint2 v[4][4];
+      for (uint32_t round = 0;; ++round) {
+        bool fresh = true;
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci) {
+          const uint2* src = p.partial + (size_t)(cb0 + ci) * EMAX + e0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[ci][j] = cb0 + ci <= last ? ld_relaxed_v2(src + j) : make_uint2(0u, tag);
+        }
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) fresh = fresh && v[ci][j].y == tag;
+        if (__all_sync(0xffffffffu, fresh)) break;
+        if (round > (kSpinLimit >> 4)) {
+          ok = false;
+          break;
+        }
+        __nanosleep(64);
+      }
+#pragma unroll
+      for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] += __uint_as_float(v[ci][j].x);  // CTA order
+    }
+    *reinterpret_cast<float4*>(stash + e0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  }
+  return ok;
+}
+
+// Run by the finisher warp once every compute warp has deposited.  `slots` is the slot set of
+// this row tile: per warp one block of E = NB * 4 * SW floats laid out
+// [sub-tile][n-tile][t][g][4].  `foreign`: stash holds the other CTAs' sums (owner of a split
+// tile).  `publish`: the sums go to `mine` in the workspace as tagged words and nothing else is done.
 template <int NB, int WARPS, bool FP16, int EPI>
-__device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots, int rt, int c0, int c1, uint32_t push_seq) {
-  constexpr int EMAX = 512 * NB;  // outputs of one row tile at TT = 4
+__device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots, const float* stash, uint2* mine,
+                                            bool foreign, bool publish, uint32_t tag, int rt, uint32_t push_seq) {
   const int lane = threadIdx.x & 31;
   const int tt = p.slot_t, sw = 32 * tt;
   const int E = NB * kSubTiles * sw;
-  const int seg_lo = rt * p.k_slabs, seg_hi = seg_lo + p.k_slabs;
-  const bool full = (c0 <= seg_lo) && (c1 >= seg_hi);
-  const bool owner = (c0 <= seg_lo);  // holds the tile's first slab
-  int uses = 0;
-  if (!full) uses = ld_relaxed_s32(p.counters + rt);  // in flight while the slots are summed
-  const uint32_t tag = ((uint32_t)(uses + 1) << 12) | (uint32_t)rt;
-  uint2* mine = p.partial + (size_t)blockIdx.x * EMAX;
-  bool ok = true;
 
-  // 1. add the warps' deposits in a fixed order (even and odd warps in two chains, four
-  //    elements per lane in flight); keep the sums in warp 0's block, or (not the owner of a
-  //    split tile) publish them as tagged words and be done.  E is a multiple of 128.
+  // 1. add the warps' deposits in a fixed order (even and odd warps in two chains), then the
+  //    other CTAs' sums.  Lane l takes elements 4 l .. 4 l + 3 of every 128: the four
+  //    accumulators {row g: two batch columns, row g + 8: the same} of one lane of the
+  //    depositing warps.  The sums are published, stored as outputs straight from the
+  //    registers (plain epilogue), or kept in warp 0's block for step 2.
 #pragma unroll 1
-  for (int e0 = lane; e0 < E; e0 += 128) {
-    float even[4] = {0.f, 0.f, 0.f, 0.f}, odd[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 2
-    for (int w = 0; w < WARPS; w += 2) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        even[j] += slots[w * E + e0 + 32 * j];
-        odd[j] += slots[(w + 1) * E + e0 + 32 * j];
-      }
+  for (int e0 = lane * 4; e0 < E; e0 += 128) {
+    float4 even = make_float4(0.f, 0.f, 0.f, 0.f), odd = even;
+#pragma unroll 5
+    for (int w = 0; w + 1 < WARPS; w += 2) {
+      const float4 a = *reinterpret_cast<const float4*>(slots + w * E + e0);
+      const float4 b = *reinterpret_cast<const float4*>(slots + (w + 1) * E + e0);
+      even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
+      odd.x += b.x; odd.y += b.y; odd.z += b.z; odd.w += b.w;
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float acc = even[j] + odd[j];
-      if (!full && !owner) {
-        st_relaxed_v2(mine + e0 + 32 * j, make_uint2(__float_as_uint(acc), tag));
-      } else {
-        slots[e0 + 32 * j] = acc;
-      }
+    if (WARPS & 1) {
+      const float4 a = *reinterpret_cast<const float4*>(slots + (WARPS - 1) * E + e0);
+      even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
     }
-  }
-  if (!full && !owner) return true;
-
-  // 2. owner of a split tile: add the words of the CTAs after this one, up to the one holding
-  //    the tile's last slab, in CTA order
-  if (!full) {
-    const int big = p.rem * (p.base + 1);
-    const int last_item = seg_hi - 1;
-    const int last = last_item < big ? last_item / (p.base + 1) : p.rem + (last_item - big) / p.base;
-#pragma unroll 1
-    for (int e0 = lane; e0 < E; e0 += 128) {        // four words per lane ...
-#pragma unroll 1
-      for (int cb = blockIdx.x + 1; cb <= last; cb += 4) {  // ... of up to four CTAs in flight
-        uint2 v[4][4];
+    float acc[4] = {even.x + odd.x, even.y + odd.y, even.z + odd.z, even.w + odd.w};
+    if (foreign) {
+      const float4 f = *reinterpret_cast<const float4*>(stash + e0);
+      acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
+    }
+    if (publish) {
 #pragma unroll
-        for (int ci = 0; ci < 4; ++ci)
+      for (int j = 0; j < 4; ++j) st_relaxed_v2(mine + e0 + j, make_uint2(__float_as_uint(acc[j]), tag));
+    } else if constexpr (EPI == kEpiStore) {
+      // element e = ((blk * tt + tq) * 8 + g) * 4 + i, blk = sub-tile * NB + n-tile
+      const int idx = e0 >> 2, g = idx & 7, bt = idx >> 3;
+      const int blk = bt / tt, tq = bt - blk * tt;
+      const int r = blk / NB, nb = blk - r * NB;
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            v[ci][j] = (cb + ci <= last) ? ld_relaxed_v2(p.partial + (size_t)(cb + ci) * EMAX + e0 + 32 * j)
-                                         : make_uint2(0u, tag);
-#pragma unroll
-        for (int ci = 0; ci < 4; ++ci)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t spins = 0;
-            while (v[ci][j].y != tag) {
-              if (++spins > kSpinLimit) {
-                ok = false;
-                break;
-              }
-              v[ci][j] = ld_relaxed_v2(p.partial + (size_t)(cb + ci) * EMAX + e0 + 32 * j);
-            }
-          }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {  // added in CTA order
-          float acc = slots[e0 + 32 * j];
-#pragma unroll
-          for (int ci = 0; ci < 4; ++ci) acc += __uint_as_float(v[ci][j].x);
-          slots[e0 + 32 * j] = acc;
-        }
+      for (int i = 0; i < 4; ++i) {
+        const int row = rt * kTileRows + 16 * r + g + 8 * (i >> 1);
+        const int b = 8 * nb + 2 * tq + (i & 1);
+        if (row < p.n && b < p.m) p.out[(size_t)b * p.n + row] = from_float<FP16>(acc[i]);
       }
+    } else {
+      *reinterpret_cast<float4*>(slots + e0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
     }
   }
+  if (publish || EPI == kEpiStore) return;
+  __syncwarp();
 
-  // 3. write the outputs: element (blk, tq, lane) with blk = sub-tile * NB + n-tile.  In a
+  // 2. write the outputs: element (blk, tq, lane) with blk = sub-tile * NB + n-tile.  In a
   //    tensor-parallel push they are first gathered as bf16 in the slot block of warp 1 (summed
   //    above, free now), [batch row][64 tile rows], then stored into this rank's slot of the
   //    current half of every rank's exchange buffer (plain peer stores) as 8-byte words {two
@@ -282,7 +316,7 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
     }
     if constexpr (EPI == kEpiPush) {
       __syncwarp();
-      const uint32_t tag = push_seq + 1u;
+      const uint32_t ptag = push_seq + 1u;
       const size_t base = ((size_t)((push_seq & 1u) * p.tp + p.rank) * p.stage_slot + (size_t)rt * kTileRows) / 2;
 #pragma unroll 1
       for (int ch = lane; ch < p.m * (kTileRows / 4); ch += 32) {  // four outputs and two tags per store
@@ -292,156 +326,195 @@ __device__ __forceinline__ bool tile_finish(const LinearParams& p, float* slots,
 #pragma unroll 1
         for (int j = 0; j < p.tp; ++j) {
           asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p.peer_stage[j] + off), "r"(d.x),
-                       "r"(tag), "r"(d.y), "r"(tag)
+                       "r"(ptag), "r"(d.y), "r"(ptag)
                        : "memory");
         }
       }
     }
   }
-  if (!full) {
-    __syncwarp();
-    if (lane == 0) p.counters[rt] = (uses + 1) & 0x7FFFF;  // this use of the split tile is done
-  }
-  return ok;
 }
 
 // ---- the kernel -------------------------------------------------------------------
-constexpr int kXRowPad = 16;  // x rows in a stage are 16 bytes apart from a 128-byte multiple: no bank conflicts
+template <int NB>
+constexpr int kGemvWarps = NB == 1 ? 19 : 15;  // compute warps per CTA; with the finisher a multiple of four, within the register file
+constexpr int kXRowPad = 16;  // resident x rows are 16 bytes apart from a 128-byte multiple: no bank conflicts
 
+// A lane's share of one slab: code vectors [sub-tile][v] and the scale vector of each block.
+template <int BITS>
+struct SlabRegs {
+  uint4 code[kSubTiles][Layout<BITS>::V];
+  uint4 sc[Layout<BITS>::KSB];
+};
+
+// Streaming load: weights are read once, so they are kept out of L1.
+__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// x: written by the previous kernel on the stream, read through L2.
+__device__ __forceinline__ uint4 ldg_l2(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Asks L2 for one whole slab, a 128-byte line per lane (a hint: no registers, no shared memory).
+template <int BITS>
+__device__ __forceinline__ void prefetch_slab_l2(const uint8_t* slab, int lane) {
+  constexpr int kLines = Layout<BITS>::kSlabBytes / 128;
+#pragma unroll
+  for (int l = 0; l < kLines; l += 32)
+    if (l + lane < kLines) asm volatile("prefetch.global.L2 [%0];" ::"l"(slab + (l + lane) * 128));
+}
+
+template <int BITS>
+__device__ __forceinline__ void load_slab(SlabRegs<BITS>& s, const uint8_t* slab, int lane) {
+  using L = Layout<BITS>;
+  const uint8_t* c = slab + lane * 16;
+#pragma unroll
+  for (int r = 0; r < kSubTiles; ++r)
+#pragma unroll
+    for (int v = 0; v < L::V; ++v) s.code[r][v] = ldg_stream(c + (r * L::V + v) * 512);
+  const uint8_t* sp = slab + L::kCodeBytes + (lane >> 2) * 16;
+#pragma unroll
+  for (int jb = 0; jb < L::KSB; ++jb) s.sc[jb] = ldg_stream(sp + jb * 128);
+}
+
+// Spins (bounded, backing off) until *word == want.
+__device__ __forceinline__ bool wait_shared_word(volatile int* word, int want) {
+  for (uint32_t spins = 0; *word != want; ++spins) {
+    if (spins > kSpinLimit) return false;
+    if (spins > 8) __nanosleep(32);
+  }
+  return true;
+}
+
+// WARPS compute warps and one finisher warp (the last one).
 template <int BITS, int NB, int WARPS, bool FP16, int EPI, bool XRES>
-__global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
+__global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
-  using T = Table<BITS>;
-  constexpr uint32_t kXRow = 128 * L::KSB + kXRowPad;  // bytes between x rows inside a stage
+  constexpr bool WIDE = BITS != 3;
+  using T = Table<BITS, WIDE>;
+  constexpr int W = WARPS;
+  constexpr int kThreads = (WARPS + 1) * 32;
   extern __shared__ __align__(128) uint8_t smem_raw[];
 
-  // The host planned the shared-memory layout for a known window address; refuse to run on
-  // anything else (uniform exit before any barrier).
   const uint32_t raw = smem_addr(smem_raw);
-  if (raw != p.smem_base) {
-    if (threadIdx.x == 0) atomicOr(p.counters + kStatusWord, kStatusSmemLayout);
-    return;
-  }
-#ifdef FDK_TRACE
-  const long long tr0 = clock64();
-  long long tr_wait = 0, tr_comp = 0, tr_flush = 0, tr_refill = 0, tr_finish = 0;
-#define FDK_T(var) var
-#else
-#define FDK_T(var)
-#endif
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int W = WARPS;
-  const int S = p.stages;
   const int g = lane >> 2, t = lane & 3;
-  float* slots = reinterpret_cast<float*>(smem_raw + (p.slots_addr - raw));
-  EpilogueSync* esync = reinterpret_cast<EpilogueSync*>(smem_raw + (p.mbar_addr - raw) + W * S * 8);
+  EpilogueSync* esync = reinterpret_cast<EpilogueSync*>(smem_raw);
+  float* slots = reinterpret_cast<float*>(smem_raw + p.slots_off);
+  const uint32_t table_addr = raw + p.table_off;
+  const uint32_t lane_base = table_addr + T::lane_offset(lane);
+  const uint32_t xres_addr = raw + p.xres_off;
   if (threadIdx.x == 0) {
     esync->count[0] = esync->count[1] = 0;
     esync->gen[0] = esync->gen[1] = 0;
-    if (XRES) mbar_init(p.xres_bar, 1);
   }
-  const uint32_t lane_base = p.table_addr + T::lane_offset(lane);
 
-
-  // my slab range
+  // my slab range [c0, c1); compute warp w takes slabs c0 + w, c0 + w + W, ...
   const int cta = blockIdx.x;
-  const int c0 = cta * p.base + min(cta, p.rem);
+  const int c0 = cta_begin(p, cta);
   const int c1 = c0 + p.base + (cta < p.rem ? 1 : 0);
+  int it = c0 + warp;  // the slab in the registers
+  const uint8_t* wp = p.tiled + (size_t)it * L::kSlabBytes;
+  constexpr uint32_t kStep = W * L::kSlabBytes;  // bytes between consecutive slabs of a warp
 
-  // this warp's ring: stage s lives at stage_addr(s), its barrier at bar_addr(s)
-  auto stage_addr = [&](int s) -> uint32_t {
-    const uint32_t q = warp * S + s;
-    return q < p.stage_a_count ? p.stage_a_addr + q * p.stage_bytes
-                               : p.stage_b_addr + (q - p.stage_a_count) * p.stage_bytes;
-  };
-  auto bar_addr = [&](int s) -> uint32_t { return p.mbar_addr + (warp * S + s) * 8; };
-  // valid x bytes per row for the slab at position kpos of its row tile
-  auto x_bytes = [&](int kpos) -> uint32_t {
-    const int left = p.k - kpos * L::kSlabK;
-    return 2u * (uint32_t)(left < L::kSlabK ? left : L::kSlabK);
-  };
-  // lane 0: announce the bytes of slab i and start its weight copy
-  auto issue_weights = [&](int i, int kpos, int s) {
-    const uint32_t bar = bar_addr(s);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                 "r"((uint32_t)L::kSlabBytes + (XRES ? 0u : (uint32_t)p.m * x_bytes(kpos)))
-                 : "memory");
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-            stage_addr(s)),
-        "l"(p.tiled + (size_t)i * L::kSlabBytes), "r"((uint32_t)L::kSlabBytes), "r"(bar)
-        : "memory");
-  };
-  // lanes 0..m-1: one x row each, for the same slab
-  auto issue_x = [&](int kpos, int s) {
-    if (!XRES && lane < p.m) {
-      asm volatile(
-          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-              stage_addr(s) + (uint32_t)L::kSlabBytes + lane * kXRow),
-          "l"(p.x + (size_t)lane * p.k + (size_t)kpos * L::kSlabK), "r"(x_bytes(kpos)), "r"(bar_addr(s))
-          : "memory");
-    }
-  };
-
-  int it = c0 + warp;               // next slab of this warp
-  int rt = it / p.k_slabs;          // its row tile and position inside the tile
-  int ks = it - rt * p.k_slabs;
-  // the prefetch cursor runs S slabs ahead
-  int pf_it = it, pf_ks = ks;
-  auto pf_advance = [&]() {
-    pf_it += W;
-    pf_ks += W;
-    while (pf_ks >= p.k_slabs) pf_ks -= p.k_slabs;
-  };
-
-  if (lane == 0) {
-    for (int s = 0; s < S; ++s) mbar_init(bar_addr(s), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    // start streaming before anything else: these copies read weights only
-    int i = it, kp = ks;
-    for (int s = 0; s < S && i < c1; ++s) {
-      issue_weights(i, kp, s);
-      i += W;
-      kp += W;
-      while (kp >= p.k_slabs) kp -= p.k_slabs;
-    }
+  // start streaming before anything else: these loads read weights only
+  SlabRegs<BITS> s, s2;
+  if (warp < W && it < c1) {
+    load_slab<BITS>(s, wp, lane);
+    if (it + W < c1) prefetch_slab_l2<BITS>(wp + kStep, lane);
   }
-  if (p.lut == nullptr) {
-    fill_table<BITS>(p.table_addr, [&](int i) { return inl.w[i]; });
-  } else {
-    fill_table<BITS>(p.table_addr, [&](int i) { return __ldg(reinterpret_cast<const uint32_t*>(p.lut) + i); });
+  {
+    const bool from_params = p.lut == nullptr;
+    auto word = [&](int i) {
+      return from_params ? inl.w[i] : __ldg(reinterpret_cast<const uint32_t*>(p.lut) + i);
+    };
+    if constexpr (BITS == 4 || BITS == 2 || BITS == 1) {
+      fill_table_unrolled<BITS, WIDE, kThreads>(table_addr, word, (int)threadIdx.x);
+    } else {
+      fill_table<BITS, WIDE>(table_addr, kThreads, word, (int)threadIdx.x);
+    }
   }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // everything above touched only weights; x, out and the workspace follow stream order
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  // number of this push = reduces completed before this launch (the reduce kernel counts)
-  const uint32_t push_seq = EPI == kEpiPush ? (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq)) : 0u;
-  __syncwarp();
-  if (XRES && warp == 0) {  // small x: one copy per batch row for the whole kernel
-    if (lane == 0) {
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(p.xres_bar),
-                   "r"((uint32_t)p.m * (uint32_t)p.k * 2u)
-                   : "memory");
-    }
-    __syncwarp();
-    if (lane < p.m) {
-      asm volatile(
-          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-              p.xres_addr + lane * p.xres_row),
-          "l"(p.x + (size_t)lane * p.k), "r"((uint32_t)p.k * 2u), "r"(p.xres_bar)
-          : "memory");
+  if (WIDE && (table_addr & 0xFFFFu) != 0u) {  // the host planned for another window address (uniform exit)
+    if (threadIdx.x == 0) atomicOr(p.counters + kStatusWord, kStatusSmemLayout);
+    return;
+  }
+  const int rt_first = div_k(p, c0);
+  const int rt_last = div_k(p, c1 - 1);
+  // finisher: the use counts of the two tiles of this CTA that can be split (first and last)
+  // and the number of this push, fetched now so that their latency is out of the way
+  int uses_first = 0, uses_last = 0;
+  uint32_t push_seq = 0;
+  if (warp == W) {
+    uses_first = ld_relaxed_s32(p.counters + rt_first);
+    uses_last = ld_relaxed_s32(p.counters + rt_last);
+    // number of this push = reduces completed before this launch (the reduce kernel counts)
+    if (EPI == kEpiPush) push_seq = (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq));
+  }
+  if constexpr (XRES) {  // x fits: one copy per CTA
+    const int vecs = p.k >> 3;
+#pragma unroll 1
+    for (int row = 0; row < p.m; ++row) {
+      const uint16_t* src = p.x + (size_t)row * p.k;
+      const uint32_t dst = xres_addr + row * p.xres_row;
+#pragma unroll 2
+      for (int c = threadIdx.x; c < vecs; c += kThreads) {
+        const uint4 xv = ldg_l2(src + c * 8);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + c * 16), "r"(xv.x), "r"(xv.y), "r"(xv.z), "r"(xv.w)
+                     : "memory");
+      }
     }
   }
-  for (int s = 0; s < S && pf_it < c1; ++s) {
-    issue_x(pf_ks, s);
-    pf_advance();
-  }
-  FDK_T(const long long tr1 = clock64();)
-  __syncthreads();
-  FDK_T(const long long tr2 = clock64();)
+  __syncthreads();  // table, x and the epilogue's sync words are in place
 
+  const int tt = p.slot_t, sw = 32 * tt;
+  const uint32_t slot_set_floats = W * kSubTiles * NB * sw;
+  bool timed_out = false;
+
+  if (warp == W) {
+    // ---- finisher ----
+    const int E = NB * kSubTiles * sw;
+    float* stash = reinterpret_cast<float*>(smem_raw + p.stash_off);
+    for (int rt = rt_first; rt <= rt_last; ++rt) {
+      const int seg = rt - rt_first;
+      const int set = p.slot_sets == 2 ? (seg & 1) : 0;
+      float* my_slots = slots + set * slot_set_floats;
+      const int seg_lo = rt * p.k_slabs, seg_hi = seg_lo + p.k_slabs;
+      const bool full = (c0 <= seg_lo) && (c1 >= seg_hi);
+      const bool owner = (c0 <= seg_lo);  // holds the tile's first slab
+      const int uses = rt == rt_first ? uses_first : uses_last;  // only those two can be split
+      const uint32_t tag = ((uint32_t)(uses + 1) << 12) | (uint32_t)rt;
+      if (!full && owner) {
+        if (!fetch_foreign<NB>(p, stash, rt, tag, E)) timed_out = true;
+        __syncwarp();
+      }
+      if (!wait_shared_word(&esync->count[set], W)) timed_out = true;
+      __threadfence_block();
+      tile_finish<NB, WARPS, FP16, EPI>(p, my_slots, stash, p.partial + (size_t)cta * (512 * NB), !full && owner,
+                                        !full && !owner, tag, rt, push_seq);
+      __syncwarp();
+      if (lane == 0) {
+        if (!full && owner) p.counters[rt] = (uses + 1) & 0x7FFFF;  // this use of the split tile is done
+        esync->count[set] = 0;
+        __threadfence_block();
+        atomicAdd(&esync->gen[set], 1);
+      }
+      __syncwarp();
+    }
+    if (timed_out && lane == 0) atomicOr(p.counters + kStatusWord, kStatusTimeout);
+    return;
+  }
+
+  // ---- compute warps ----
   float tot[kSubTiles][NB][4];
 #pragma unroll
   for (int r = 0; r < kSubTiles; ++r)
@@ -450,93 +523,71 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
 #pragma unroll
       for (int i = 0; i < 4; ++i) tot[r][nb][i] = 0.f;
 
-  const int rt_first = c0 / p.k_slabs;
-  const int rt_last = (c1 - 1) / p.k_slabs;
+  int rt = div_k(p, it);  // row tile of slab `it` and its position inside the tile
+  int ks = it - rt * p.k_slabs;
   int cur_rt = rt_first;
-  bool timed_out = false;
-  const int tt = p.slot_t, sw = 32 * tt;
 
-  const uint32_t slot_set_floats = W * kSubTiles * NB * sw;
+  // Deposits the totals of row tiles cur_rt .. target - 1 (zeros for tiles in which this warp
+  // had no slab) and clears them.
   auto flush_until = [&](int target) {
     while (cur_rt < target) {
       const int seg = cur_rt - rt_first;
       const int set = p.slot_sets == 2 ? (seg & 1) : 0, turn = p.slot_sets == 2 ? (seg >> 1) : seg;
       float* my_slots = slots + set * slot_set_floats;
-      // the slot set is free once the reduction of two row tiles ago has read it
-      {
-        volatile int* gen = &esync->gen[set];
-        uint32_t spins = 0;
-        while (*gen != turn) {
-          if (++spins > kSpinLimit) {
-            timed_out = true;
-            break;
-          }
-        }
-      }
+      // the slot set is free once the finisher has summed the tile that used it before
+      if (!wait_shared_word(&esync->gen[set], turn)) timed_out = true;
 #pragma unroll
       for (int r = 0; r < kSubTiles; ++r)
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
           if (t < tt) {
-            float4 v = make_float4(tot[r][nb][0], tot[r][nb][1], tot[r][nb][2], tot[r][nb][3]);
-            *reinterpret_cast<float4*>(my_slots + ((warp * kSubTiles + r) * NB + nb) * sw + t * 32 + g * 4) = v;
+            float4 dv = make_float4(tot[r][nb][0], tot[r][nb][1], tot[r][nb][2], tot[r][nb][3]);
+            *reinterpret_cast<float4*>(my_slots + ((warp * kSubTiles + r) * NB + nb) * sw + t * 32 + g * 4) = dv;
           }
           tot[r][nb][0] = tot[r][nb][1] = tot[r][nb][2] = tot[r][nb][3] = 0.f;
         }
       __threadfence_block();
       __syncwarp();
-      int old = 0;
-      if (lane == 0) old = atomicAdd(&esync->count[set], 1);
-      old = __shfl_sync(0xffffffffu, old, 0);
-      if (old == W - 1) {  // every warp of the CTA has deposited: this warp finishes the tile
-        __threadfence_block();
-        FDK_T(long long tf = clock64();)
-        if (!tile_finish<NB, WARPS, FP16, EPI>(p, my_slots, cur_rt, c0, c1, push_seq)) timed_out = true;
-        FDK_T(tr_finish += clock64() - tf;)
-        __syncwarp();
-        if (lane == 0) {
-          esync->count[set] = 0;
-          __threadfence_block();
-          atomicAdd(&esync->gen[set], 1);
-        }
-      }
+      if (lane == 0) atomicAdd(&esync->count[set], 1);
       ++cur_rt;
     }
   };
 
-  // One slab: stage address `sa`, slab position `kpos` inside its row tile.
-  auto compute = [&](uint32_t sa, int kpos) {
-    constexpr bool kPreload = (L::V == 1 && L::KSB > 1);
-    uint4 pre[kPreload ? kSubTiles : 1];
-    if constexpr (kPreload) {
+  // per-lane address of this lane's x fragment of column 0, per batch-column group
+  uint32_t x_lane[NB];
+  const uint16_t* x_ptr[NB];
 #pragma unroll
-      for (int r = 0; r < kSubTiles; ++r) pre[r] = ring128(sa + (r * 32 + lane) * 16);
-    }
+  for (int nb = 0; nb < NB; ++nb) {
+    const int b = min(g + 8 * nb, p.m - 1);  // lanes of unused batch columns read a live row
+    x_lane[nb] = xres_addr + b * p.xres_row + t * 32;
+    x_ptr[nb] = p.x + (size_t)b * p.k + t * 16;
+  }
+
+  // Works on the slab held in `s`, at position `kpos` inside its row tile.
+  auto compute = [&](const SlabRegs<BITS>& s, int kpos) {
     auto block = [&](auto jbc) {
       constexpr int JB = decltype(jbc)::value;
-      if ((kpos * L::KSB + JB) * kBlock >= p.k) return;  // padded block: codes and scales are zero
+      const int col = (kpos * L::KSB + JB) * kBlock;
+      if (L::KSB > 1 && col >= p.k) return;  // a padded block holds zero codes and scales
       uint32_t xb[NB][8];
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
-        const int b = min(g + 8 * nb, p.m - 1);  // lanes of unused batch columns read a live row
-        const uint32_t xa = XRES ? p.xres_addr + b * p.xres_row + (kpos * L::KSB + JB) * 128 + t * 32
-                                        : sa + L::kSlabBytes + b * kXRow + JB * 128 + t * 32;
-        const uint4 lo = ring128(xa), hi = ring128(xa + 16);
+        uint4 lo, hi;
+        if constexpr (XRES) {
+          lo = ring128(x_lane[nb] + col * 2);
+          hi = ring128(x_lane[nb] + col * 2 + 16);
+        } else {
+          lo = ldg_l2(x_ptr[nb] + col);
+          hi = ldg_l2(x_ptr[nb] + col + 8);
+        }
         xb[nb][0] = lo.x; xb[nb][1] = lo.y; xb[nb][2] = lo.z; xb[nb][3] = lo.w;
         xb[nb][4] = hi.x; xb[nb][5] = hi.y; xb[nb][6] = hi.z; xb[nb][7] = hi.w;
       }
-      const uint4 sc = ring128(sa + L::kCodeBytes + JB * 128 + g * 16);
+      const uint4 sc = s.sc[JB];
       auto sub_tile = [&](auto rc) {
         constexpr int R = decltype(rc)::value;
-        uint4 code[L::V];
-        if constexpr (kPreload) {
-          code[0] = pre[R];
-        } else {
-#pragma unroll
-          for (int v = 0; v < L::V; ++v) code[v] = ring128(sa + ((R * L::V + v) * 32 + lane) * 16);
-        }
         uint32_t a[4][4];
-        build_fragments<BITS, JB>(code, lane_base, a);
+        build_fragments<BITS, JB, WIDE>(s.code[R], lane_base, a);
         const uint32_t scw = word_of<R>(sc);
         const float s_lo = pair_lo<FP16>(scw), s_hi = pair_hi<FP16>(scw);
 #pragma unroll
@@ -565,116 +616,111 @@ __global__ void __launch_bounds__(WARPS * 32, (NB == 1 || WARPS <= 8) ? 2 : 1)
     }
   };
 
-  if (XRES && it < c1) {
-    if (!mbar_wait(p.xres_bar, 0)) timed_out = true;
-  }
-  int s = 0;
-  uint32_t parity = 0;
-  while (it < c1) {
-    FDK_T(long long ta = clock64();)
+  // One step: start loading the warp's next slab into `nxt`, ask L2 for the one after it, work
+  // on the slab in `cur`, move on.  Returns false when the warp has no slab left.
+  auto step = [&](const SlabRegs<BITS>& cur, SlabRegs<BITS>& nxt) {
+    if (it >= c1) return false;
     if (rt != cur_rt) flush_until(rt);
-    FDK_T(long long tb = clock64(); tr_flush += tb - ta;)
-    if (!mbar_wait(bar_addr(s), parity)) timed_out = true;  // carry on with whatever is there
-    FDK_T(long long tc = clock64(); tr_wait += tc - tb;)
-    compute(stage_addr(s), ks);
-    __syncwarp();  // every lane has consumed its share of this stage
-    FDK_T(long long td = clock64(); tr_comp += td - tc;)
-    if (pf_it < c1) {
-      if (lane == 0) issue_weights(pf_it, pf_ks, s);
-      __syncwarp();
-      issue_x(pf_ks, s);
-      pf_advance();
-    }
-    FDK_T(tr_refill += clock64() - td;)
+    if (it + W < c1) load_slab<BITS>(nxt, wp + kStep, lane);
+    if (it + 2 * W < c1) prefetch_slab_l2<BITS>(wp + 2 * (size_t)kStep, lane);
+    compute(cur, ks);
+    wp += kStep;
     it += W;
     ks += W;
     while (ks >= p.k_slabs) {
       ks -= p.k_slabs;
       ++rt;
     }
-    if (++s == S) {
-      s = 0;
-      parity ^= 1;
-    }
+    return true;
+  };
+  // two register sets, used alternately
+  while (step(s, s2) && step(s2, s)) {
   }
-  FDK_T(const long long tr3 = clock64();)
   flush_until(rt_last + 1);
   if (timed_out && lane == 0) atomicOr(p.counters + kStatusWord, kStatusTimeout);
-#ifdef FDK_TRACE
-  if (p.trace != nullptr && lane == 0) {
-    unsigned long long* o = p.trace + ((size_t)blockIdx.x * W + warp) * 8;
-    o[0] = tr1 - tr0; o[1] = tr_refill; o[2] = tr3 - tr2; o[3] = clock64() - tr3;
-    o[4] = tr_wait; o[5] = tr_comp; o[6] = tr_flush; o[7] = tr_finish + 1;
-  }
-#endif
-#undef FDK_T
 }
 
 // ---- host side ----------------------------------------------------------------------
 
-
 inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
-// Plans the shared-memory layout for `warps` warps with `stages` ring stages each; returns
-// the dynamic size needed.
+// Plans the shared-memory layout of one CTA as offsets from the start of its dynamic shared
+// memory, which kernels see at address `base` of the shared window:
+//   [sync words] ... [table, at a multiple of 64 KB of the window when it is the wide one] ...
+// with the reduction slots and (when it fits) x placed below the table if there is room, above
+// it otherwise.  Returns the dynamic size needed; `resident` tells whether x is staged.
 template <int BITS, int NB>
-size_t plan_smem(uint32_t base, int warps, int stages, LinearParams& p) {
-  using L = Layout<BITS>;
-  using T = Table<BITS>;
-  const uint32_t n_stages = warps * stages;
+size_t plan_smem(uint32_t base, int warps, size_t limit, LinearParams& p, bool* resident) {
+  constexpr bool WIDE = BITS != 3;
+  using T = Table<BITS, WIDE>;
   const uint32_t tt = ((p.m < 8 ? p.m : 8) + 1) / 2;
   // two sets let a warp deposit its next row tile while the last one is being summed; large
-  // deposits (batches of five rows and more) get one set and more warps instead
+  // deposits (batches of five rows and more) get one set
   const uint32_t sets = tt >= 3 ? 1 : 2;
   p.slot_sets = sets;
-  const uint32_t slot_bytes = sets * warps * kSubTiles * NB * 32 * tt * sizeof(float);
-  const uint32_t mbar_bytes = align_up(n_stages * 8 + 8 + sizeof(EpilogueSync), 128);  // barriers + epilogue sync words
-  // x small enough is staged whole, once per CTA; otherwise its rows travel with each slab
-  const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
-  const bool resident = (size_t)p.m * xres_row <= 36 * 1024;
-  const uint32_t xres_bytes = resident ? align_up(p.m * xres_row, 128) : 0;
-  const uint32_t stage_bytes =
-      align_up(L::kSlabBytes + (resident ? 0 : p.m * (128 * L::KSB + kXRowPad)), 128);
-  p.stage_bytes = stage_bytes;
-  p.stages = stages;
   p.slot_t = tt;
-  uint32_t cursor = align_up(base, 128);
-  p.smem_base = base;
-  p.mbar_addr = cursor;
-  p.xres_bar = cursor + n_stages * 8 + sizeof(EpilogueSync);
-  cursor += mbar_bytes;
+  const uint32_t slot_bytes = align_up(sets * warps * kSubTiles * NB * 32 * tt * sizeof(float), 128);
+  const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
+  const uint32_t xres_bytes = align_up((uint32_t)p.m * xres_row, 128);
   p.xres_row = xres_row;
-  p.xres_addr = resident ? cursor : 0;
-  cursor += xres_bytes;
-  p.slots_addr = cursor;
-  cursor = align_up(cursor + slot_bytes, 128);
-  p.table_addr = cursor;
-  cursor += T::kBytes;
-  p.stage_a_addr = cursor;
-  p.stage_a_count = n_stages;
-  p.stage_b_addr = cursor;
-  cursor += n_stages * stage_bytes;
-  return cursor - base;
+  uint32_t low = 128;                                                   // cursor below the table
+  const uint32_t table_off = WIDE ? align_up(base + low, 65536) - base : low;
+  uint32_t high = table_off + T::kBytes;                               // cursor above it
+  p.table_off = table_off;
+  auto place = [&](uint32_t bytes) {
+    if (low + bytes <= table_off) {
+      const uint32_t at = low;
+      low += bytes;
+      return at;
+    }
+    const uint32_t at = high;
+    high += bytes;
+    return at;
+  };
+  p.slots_off = place(slot_bytes);
+  p.stash_off = place(NB * kSubTiles * 32 * tt * sizeof(float));
+  const uint32_t high_before = high, low_before = low;
+  p.xres_off = place(xres_bytes);
+  *resident = high <= limit;
+  if (!*resident) {
+    high = high_before;
+    low = low_before;
+    p.xres_off = 0;
+  }
+  return high;
 }
 
 template <int BITS, int NB, int WARPS, bool FP16>
-int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int grid, unsigned flags,
-                   cudaStream_t stream) {
+int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsigned flags, cudaStream_t stream) {
+  uint32_t base = 0;
+  if (int st = dynamic_smem_base(&base)) return st;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  bool xres = false;
+  const size_t smem = plan_smem<BITS, NB>(base, WARPS, (size_t)di.max_smem_optin, p, &xres);
+  FDK_CHECK_ARG(smem <= (size_t)di.max_smem_optin, FDK_ERR_CUDA, "shared-memory plan of %zu bytes exceeds %d", smem,
+                di.max_smem_optin);
+  // one CTA per SM, fewer when there are fewer slabs than that
+  int grid = sm_count;
+  if (grid > p.total) grid = p.total;
+  p.base = p.total / grid;
+  p.rem = p.total % grid;
+
   const int epi = p.tp > 0 ? kEpiPush : (p.silu ? kEpiSilu : kEpiStore);
-  const bool xres = p.xres_addr != 0;
   auto kernel = epi == kEpiPush   ? (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush, false>)
                 : epi == kEpiSilu ? (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu, false>)
                                   : (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore, false>);
-  static size_t configured[6][64] = {};
+  static std::atomic<size_t> configured[6][64] = {};
   int dev = 0;
   FDK_CUDA(cudaGetDevice(&dev));
-  if (configured[2 * epi + xres][dev & 63] < smem) {
+  std::atomic<size_t>& have = configured[2 * epi + (xres ? 1 : 0)][dev & 63];
+  if (have.load(std::memory_order_acquire) < smem) {
     FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[2 * epi + xres][dev & 63] = smem;
+    have.store(smem, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(WARPS * 32);
+  cfg.blockDim = dim3((WARPS + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -686,11 +732,6 @@ int launch_variant(LinearParams p, const InlineLut<BITS>& inl, size_t smem, int 
   return FDK_OK;
 }
 
-// CTAs are sized so that two fit on an SM (12 or 8 warps, at most half the shared memory):
-// with one CTA per SM the other half is free for the NEXT kernel on the stream, which under
-// programmatic dependent launch starts its table fill and weight prefetch while this one is
-// still running; a large matrix takes both halves itself (two CTAs per SM).  A plan that does
-// not fit half an SM gets the whole SM.
 template <int BITS, int NB, bool FP16>
 int launch(LinearParams p, const void* lut_host, int sm_count, unsigned flags, cudaStream_t stream) {
   InlineLut<BITS> inl;
@@ -700,69 +741,7 @@ int launch(LinearParams p, const void* lut_host, int sm_count, unsigned flags, c
   } else {
     memset(inl.w, 0, sizeof(inl.w));
   }
-  uint32_t base = 0;
-  if (int st = dynamic_smem_base(&base)) return st;
-  DeviceInfo di;
-  if (int st = device_info(&di)) return st;
-  constexpr int kWide = 12;
-  constexpr int kMid = 8;
-  constexpr int kNarrow = 4;
-  const size_t half_sm = ((size_t)di.max_smem_optin + 1024) / 2 - 1024;  // two CTAs, 1 KB reserved each
-  const int widths[3] = {kWide, kMid, kNarrow};
-  int best_w = 0, best_s = 0;
-  size_t best_smem = 0;
-  bool two_per_sm = true;
-  bool env_free = true;  // no plan forced from the environment (development builds)
-#ifdef FDK_TRACE
-  static const char* env_s = getenv("FDK_STAGES");
-  static const char* env_w = getenv("FDK_WARPS");
-  if (env_s != nullptr) {
-    const int want_w = env_w ? atoi(env_w) : kWide;
-    LinearParams q = p;
-    best_smem = plan_smem<BITS, NB>(base, want_w, atoi(env_s), q);
-    best_w = want_w;
-    best_s = atoi(env_s);
-    two_per_sm = best_smem <= half_sm;
-    env_free = false;
-  }
-#endif
-  // Candidates: each width, in half an SM or all of it, with as many stages as fit.  The one
-  // that keeps the most warps on an SM wins (two CTAs count double where the grid can be
-  // doubled: NB == 1 and enough slabs); ties go to the half-SM plan, which leaves room for the
-  // next kernel's prologue.  Plans with a single stage are taken only if nothing else fits.
-  int best_score = -1;
-  for (int wi = 0; wi < 3 && env_free; ++wi) {
-    for (int pass = 0; pass < 2; ++pass) {
-      const size_t limit = pass == 0 ? half_sm : (size_t)di.max_smem_optin;
-      for (int s = kMaxStages; s >= 1; --s) {
-        LinearParams q = p;
-        const size_t smem = plan_smem<BITS, NB>(base, widths[wi], s, q);
-        if (smem > limit) continue;
-        const bool doubled = pass == 0 && NB == 1 && p.total >= 2 * widths[wi] * sm_count;
-        const int score = (s >= 2 ? 1000 : 0) + widths[wi] * (doubled ? 2 : 1) * 10 + (pass == 0 ? 1 : 0);
-        if (score > best_score) {
-          best_score = score;
-          best_w = widths[wi];
-          best_s = s;
-          best_smem = smem;
-          two_per_sm = pass == 0;
-        }
-        break;  // fewer stages of the same plan are never better
-      }
-    }
-  }
-  FDK_CHECK_ARG(best_w != 0, FDK_ERR_CUDA, "no shared-memory plan fits %d bytes", di.max_smem_optin);
-  plan_smem<BITS, NB>(base, best_w, best_s, p);
-  // grid: one CTA per SM, or two when each would still have plenty of slabs (NB == 1 only: the
-  // workspace holds one 4 KB partial per CTA for up to 320 CTAs)
-  int grid = sm_count;
-  if (two_per_sm && NB == 1 && p.total >= 2 * best_w * sm_count) grid = 2 * sm_count;
-  if (grid > p.total) grid = p.total;
-  p.base = p.total / grid;
-  p.rem = p.total % grid;
-  if (best_w == kWide) return launch_variant<BITS, NB, kWide, FP16>(p, inl, best_smem, grid, flags, stream);
-  if (best_w == kMid) return launch_variant<BITS, NB, kMid, FP16>(p, inl, best_smem, grid, flags, stream);
-  return launch_variant<BITS, NB, kNarrow, FP16>(p, inl, best_smem, grid, flags, stream);
+  return launch_width<BITS, NB, kGemvWarps<NB>, FP16>(p, inl, sm_count, flags, stream);
 }
 
 }  // namespace
@@ -778,6 +757,5 @@ int launch_bits(const LinearParams& p, const void* lut_host, int grid, int dtype
   return wide ? launch<BITS, 2, false>(p, lut_host, grid, flags, stream)
               : launch<BITS, 1, false>(p, lut_host, grid, flags, stream);
 }
-
 
 }  // namespace fdk

@@ -114,13 +114,19 @@ __device__ __forceinline__ uint32_t word_at(const uint4& v, int i) {
 // offset (lane % kReplicas) * kEntryBytes.  Whatever code bytes the lanes hold, the lanes of a
 // wavefront read 128 different bytes' worth of banks.  A lookup address is one PRMT (extract
 // the code byte) and one multiply-add.
-template <int BITS>
+//
+// WIDE: rows 256 bytes apart (the second half of each row unused) in a table that starts at a
+// multiple of 64 KB in the shared window.  The address of an entry is then the table's address
+// with the code byte put into bits 8..15: one PRMT, no arithmetic (64 KB instead of 32 KB;
+// not for 3 bits, whose 6-bit fields are not bytes).
+template <int BITS, bool WIDE = false>
 struct Table {
+  static_assert(!(WIDE && BITS == 3), "3-bit codes use the compact table");
   static constexpr int kEntries = (BITS == 3) ? 64 : 256;
   static constexpr int kEntryBytes = (BITS == 2) ? 8 : (BITS == 1 ? 16 : 4);
   static constexpr int kReplicas = 128 / kEntryBytes;
-  static constexpr int kStride = 128;
-  static constexpr int kBytes = kEntries * kStride;  // 32 KB, or 8 KB for 3 bits
+  static constexpr int kStride = WIDE ? 256 : 128;
+  static constexpr int kBytes = kEntries * kStride;  // 32 KB (64 KB wide), or 8 KB for 3 bits
   __device__ static __forceinline__ uint32_t lane_offset(int lane) { return (lane % kReplicas) * kEntryBytes; }
 };
 
@@ -132,48 +138,76 @@ struct InlineLut {
   uint32_t w[kWords];
 };
 
-// Fills the replicated table.  A plain loop on purpose: code that runs once per
-// launch costs mostly instruction fetches, so it is kept short rather than unrolled.
-// word(i) returns 32-bit word i of the source table.
-template <int BITS, class WordFn>
+// Fills the replicated table: one 128-byte row per warp and iteration, lane l writing word l
+// of the row (replica l * 4 / kEntryBytes of the entry, its word l % (kEntryBytes / 4)).
+// `threads` (a multiple of 32) threads numbered `tid` take part; word(i) returns 32-bit word
+// i of the source table.
+template <int BITS, bool WIDE = false, class WordFn>
 __device__ __forceinline__ void fill_table(uint32_t table_base, int threads, WordFn word, int tid) {
-  using T = Table<BITS>;
+  using T = Table<BITS, WIDE>;
+  const int lane = tid & 31, warps = threads >> 5;
 #pragma unroll 1
-  for (int idx = tid; idx < T::kEntries * T::kReplicas; idx += threads) {
-    const int e = idx / T::kReplicas, l = idx % T::kReplicas;
-    const uint32_t addr = table_base + e * T::kStride + l * T::kEntryBytes;
+  for (int e = tid >> 5; e < T::kEntries; e += warps) {
+    uint32_t v;
     if constexpr (BITS == 4) {
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(word(e)) : "memory");
+      v = word(e);
     } else if constexpr (BITS == 2) {
-      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(word(2 * e)), "r"(word(2 * e + 1)) : "memory");
+      v = word(2 * e + (lane & 1));
     } else if constexpr (BITS == 1) {
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(word(4 * e)), "r"(word(4 * e + 1)),
-                   "r"(word(4 * e + 2)), "r"(word(4 * e + 3))
-                   : "memory");
+      v = word(4 * e + (lane & 3));
     } else if constexpr (BITS == 8) {
       const uint32_t pair = word(e >> 1);
       const uint32_t h = (e & 1) ? (pair >> 16) : (pair & 0xFFFFu);
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(h | (h << 16)) : "memory");
+      v = h | (h << 16);
     } else {  // 3 bits: pair table from the 8-entry codebook, first code in the high 3 index bits
       auto code = [&](int c) {
         const uint32_t pair = word(c >> 1);
         return (c & 1) ? (pair >> 16) : (pair & 0xFFFFu);
       };
-      asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(code(e >> 3) | (code(e & 7) << 16)) : "memory");
+      v = code(e >> 3) | (code(e & 7) << 16);
     }
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(table_base + e * T::kStride + lane * 4), "r"(v) : "memory");
+  }
+}
+
+// The same with a thread count known at compile time: all the source words of a thread are
+// fetched before the first is stored, so a thread pays the latency of the source once.
+template <int BITS, bool WIDE, int THREADS, class WordFn>
+__device__ __forceinline__ void fill_table_unrolled(uint32_t table_base, WordFn word, int tid) {
+  using T = Table<BITS, WIDE>;
+  static_assert(BITS == 4 || BITS == 2 || BITS == 1, "byte tables of 4-, 2- and 1-bit codes");
+  constexpr int kWarps = THREADS / 32;
+  constexpr int kRounds = (T::kEntries + kWarps - 1) / kWarps;
+  constexpr int kWordsPerEntry = T::kEntryBytes / 4;
+  const int lane = tid & 31, warp = tid >> 5;
+  uint32_t v[kRounds];
+#pragma unroll
+  for (int i = 0; i < kRounds; ++i) {
+    const int e = warp + i * kWarps;
+    v[i] = e < T::kEntries ? word(kWordsPerEntry * e + (lane & (kWordsPerEntry - 1))) : 0u;
+  }
+#pragma unroll
+  for (int i = 0; i < kRounds; ++i) {
+    const int e = warp + i * kWarps;
+    if (e < T::kEntries)
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(table_base + e * T::kStride + lane * 4), "r"(v[i]) : "memory");
   }
 }
 
 // Address of the table entry selected by byte J of `w` (lane_base = table base + lane offset).
-template <int BITS, int J>
+template <int BITS, int J, bool WIDE = false>
 __device__ __forceinline__ uint32_t entry_addr(uint32_t w, uint32_t lane_base) {
-  const uint32_t b = prmt<0x4440u | J>(w, 0u);  // the byte alone
-  return lane_base + b * (uint32_t)Table<BITS>::kStride;
+  if constexpr (WIDE) {  // byte J of w into byte 1 of the lane's table address
+    return prmt<0x3200u | ((4u + J) << 4)>(lane_base, w);
+  } else {
+    const uint32_t b = prmt<0x4440u | J>(w, 0u);  // the byte alone
+    return lane_base + b * (uint32_t)Table<BITS>::kStride;
+  }
 }
 
-template <int BITS, class WordFn>
+template <int BITS, bool WIDE = false, class WordFn>
 __device__ __forceinline__ void fill_table(uint32_t table_base, WordFn word) {
-  fill_table<BITS>(table_base, (int)blockDim.x, word, (int)threadIdx.x);
+  fill_table<BITS, WIDE>(table_base, (int)blockDim.x, word, (int)threadIdx.x);
 }
 
 __device__ __forceinline__ uint2 ld_relaxed_v2(const uint2* p) {

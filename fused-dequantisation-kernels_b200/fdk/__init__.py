@@ -10,7 +10,7 @@ from typing import Any
 
 __all__ = ["bench", "kernels", "models", "llama", "native"]
 
-_LAZY = {"bench", "kernels", "models", "llama", "native", "tensor_parallel"}
+_LAZY = {"bench", "kernels", "models", "llama", "native"}
 
 
 def __getattr__(name: str) -> Any:

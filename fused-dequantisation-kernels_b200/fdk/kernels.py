@@ -9,10 +9,12 @@ reference's src/fdk/kernels.py, backed by libfdk_b200.so instead of Triton.
 
 The reference's operators read the packed tensors directly.  The native kernels read a
 tiled copy of them; for callers that pass packed tensors it is built on first use and
-cached by storage address and version (modules hold their tiled buffer themselves).
+cached per tensor object and version (modules hold their tiled buffer themselves).
 """
 
 from __future__ import annotations
+
+import weakref
 
 import torch
 from torch import Tensor
@@ -45,8 +47,11 @@ def mm_lut_ref(a: Tensor, bq: Tensor, lut8: Tensor, bs: Tensor, out: Tensor | No
 
 
 ### tiled-buffer cache for the operator-level API
+# Keyed on the weight tensor OBJECT (id, checked against a weak reference, which also evicts the
+# entry when the tensor is collected) and on the versions of both tensors: a new tensor that the
+# allocator happens to place at the address of a freed one is never mistaken for it.
 
-_tiled_cache: dict[tuple, tuple[tuple[int, int], Tensor]] = {}
+_tiled_cache: dict[int, tuple] = {}
 
 
 def clear_tiled_cache() -> None:
@@ -54,13 +59,13 @@ def clear_tiled_cache() -> None:
 
 
 def tiled_for(b: Tensor, bs: Tensor, n: int, k: int, bits: int) -> Tensor:
-    key = (b.data_ptr(), bs.data_ptr(), n, k, bits, b.device.index)
-    versions = (b._version, bs._version)
+    key = id(b)
+    stamp = (b._version, id(bs), bs._version, n, k, bits)
     hit = _tiled_cache.get(key)
-    if hit is not None and hit[0] == versions:
-        return hit[1]
+    if hit is not None and hit[0]() is b and hit[1]() is bs and hit[2] == stamp:
+        return hit[3]
     tiled = native.repack(b, bs, n, k, bits, k // bs.shape[1])
-    _tiled_cache[key] = (versions, tiled)
+    _tiled_cache[key] = (weakref.ref(b, lambda _, k_=key: _tiled_cache.pop(k_, None)), weakref.ref(bs), stamp, tiled)
     return tiled
 
 

@@ -209,6 +209,7 @@ class LlamaDecoder(nn.Module):
         self.act = torch.empty((batch, f), device=dev, dtype=dt)
         self.attn = torch.empty((batch, self.q_heads * 128), device=dev, dtype=dt)
         self.position = torch.zeros((), device=dev, dtype=torch.int64)
+        self.host_position = 0  # eager calls made so far (graph replays are bounded on the device instead)
         # context slices per (batch row, KV head): about 128 keys each (a CTA's eight warps then
         # load nearly all their keys in one go), as long as that stays within one CTA per SM:
         # more slices than that only add merge work (16 rows: 16 us unsliced, 32 us in 4 slices)
@@ -251,6 +252,7 @@ class LlamaDecoder(nn.Module):
             kc[:, :, :context].copy_(torch.randn(kc[:, :, :context].shape, generator=gen, device=kc.device, dtype=torch.float32))
             vc[:, :, :context].copy_(torch.randn(vc[:, :, :context].shape, generator=gen, device=vc.device, dtype=torch.float32))
         self.position.fill_(context)
+        self.host_position = context
 
     # ---- one decode step --------------------------------------------------------------
 
@@ -258,6 +260,9 @@ class LlamaDecoder(nn.Module):
         """tokens [batch] int64 at position `self.position` -> logits [batch, vocab]; advances the
         position.  No host synchronisation, fixed shapes: capturable in a CUDA graph."""
         dims, eps = self.dims, self.dims.rms_norm_eps
+        if self.host_position >= self.max_len:
+            raise RuntimeError(f"decode step at position {self.host_position}: the KV cache was allocated for {self.max_len} positions")
+        self.host_position += 1
         torch.index_select(self.embed.weight, 0, tokens, out=self.hidden)
         if self.exchange is not None:
             return self._forward_fused()

@@ -118,9 +118,9 @@ int fdk_workspace_size(size_t* bytes_host);
 int fdk_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Reads the workspace's device-side status word (synchronous copy): 0 when every
- * fdk_linear_lut that used the workspace ran normally; bit 0 = a bounded wait on a copy
- * barrier ran out, bit 1 = the shared-memory layout planned by the host did not match the
- * device.  The kernels never trap or spin without limit; this is where they report.
+ * fdk_linear_lut that used the workspace ran normally; bit 0 = a bounded wait (for another
+ * CTA's partial sums, or on a copy barrier of the tensor-core kernel) ran out, bit 1 = the
+ * shared-memory layout planned by the host did not match the device.  The kernels never trap or spin without limit; this is where they report.
  * No counterpart in the reference (its kernels have no device-side error reporting,
  * cf. the soft handling in src/fdk/bench.py:457-458). */
 int fdk_workspace_status(const void* workspace, int* status_host);
@@ -136,7 +136,8 @@ int fdk_workspace_status(const void* workspace, int* status_host);
  *             kernel by value with the launch parameters, which saves the kernel a
  *             memory round trip before it can start (the table is 16 B .. 4 KB)
  *   out       [m, n] row-major
- *   m         >= 1; batch rows are processed 16 at a time, any m is accepted.
+ *   m         >= 1, any m: up to 8 rows run the GEMV kernel, more the tensor-core kernel
+ *             (the GEMV kernel takes up to 16 rows where one of its epilogues is asked for).
  * Deterministic: the same inputs give the same bits on every call. */
 int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
                    int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
