@@ -197,7 +197,7 @@ __global__ void rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restr
 __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long long* __restrict__ pos_ptr,
                                    uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_cache,
                                    uint16_t* __restrict__ v_cache, int q_heads, int kv_heads, int max_len,
-                                   float theta) {
+                                   float theta, int paired) {
   pdl_prologue();
   const int row = blockIdx.y, head = blockIdx.x, i = threadIdx.x;  // i in 0..63: the pair (i, i + 64)
   const long long pos = *pos_ptr;
@@ -216,7 +216,10 @@ __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long 
   const float angle = (float)pos * inv_freq;
   const float c = to_float<false>(from_float<false>(cosf(angle)));
   const float s = to_float<false>(from_float<false>(sinf(angle)));
-  const float x0 = to_float<false>(src[i]), x1 = to_float<false>(src[i + 64]);
+  // paired: the head's values come in the order [0..31, 64..95, 32..63, 96..127] (the row order the
+  // projection kernel's rotary output wants), so dimension i sits at i or i + 32, its partner 32 further on
+  const int at = paired ? (i < 32 ? i : i + 32) : i;
+  const float x0 = to_float<false>(src[at]), x1 = to_float<false>(src[at + (paired ? 32 : 64)]);
   // out = x * cos + rotate_half(x) * sin, each product and the sum rounded to bf16
   auto r = [](float v) { return to_float<false>(from_float<false>(v)); };
   const uint16_t o0 = from_float<false>(r(x0 * c) + r(-x1 * s));
@@ -230,6 +233,37 @@ __global__ void rope_append_kernel(const uint16_t* __restrict__ qkv, const long 
   }
   dst[i] = o0;
   dst[i + 64] = o1;
+}
+
+// table[i] = {bf16 cos, bf16 sin} of angle pos * theta^(-2 i / 128), i = 0 .. 63: what every
+// rotary embedding of one decode step needs, computed once per step (the values of
+// rope_append_kernel above).
+__global__ void rope_table_kernel(const long long* __restrict__ pos_ptr, uint32_t* __restrict__ table, float theta) {
+  pdl_prologue();
+  const int i = threadIdx.x;
+  const float inv_freq = powf(theta, -(float)(2 * i) / 128.f);
+  const float angle = (float)(*pos_ptr) * inv_freq;
+  table[i] = (uint32_t)from_float<false>(cosf(angle)) | ((uint32_t)from_float<false>(sinf(angle)) << 16);
+}
+
+// sumsq[row][t] = sum of squares of h[row][64 t .. 64 t + 63]; one warp per (row, tile), lane l
+// taking elements l and l + 32, added in the order of the projection kernel's residual output.
+__global__ void sumsq_tiles_kernel(const uint16_t* __restrict__ h, float* __restrict__ sumsq, int width, int tiles) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), row = blockIdx.y;
+  if (t >= tiles) return;
+  float sq = 0.f;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int col = t * 64 + lane + 32 * half;
+    if (col < width) {
+      const float v = to_float<false>(h[(size_t)row * width + col]);
+      sq = fmaf(v, v, sq);
+    }
+  }
+  sq = warp_sum(sq);
+  if (lane == 0) sumsq[(size_t)row * tiles + t] = sq;
 }
 
 // out[row, j] = silu(gate) * up; the columns of gate_up alternate `group` gate values and the
@@ -366,16 +400,42 @@ extern "C" int fdk_tp_exchange_status(const fdk_tp_exchange* ex, int* status_hos
   return FDK_OK;
 }
 
-extern "C" int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache,
-                               int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
-                               void* stream) {
+static int rope_append_impl(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache, int rows,
+                            int q_heads, int kv_heads, int head_dim, int max_len, float theta, int paired,
+                            void* stream) {
   FDK_CHECK_ARG(qkv && pos && q_out && k_cache && v_cache, FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(head_dim == 128, FDK_ERR_SHAPE, "head_dim=%d: only 128 is supported", head_dim);
   FDK_CHECK_ARG(rows > 0 && q_heads > 0 && kv_heads > 0 && max_len > 0, FDK_ERR_BAD_ARG, "non-positive size");
   dim3 grid(q_heads + 2 * kv_heads, rows);
   return launch_pdl(rope_append_kernel, grid, dim3(64), 0, (cudaStream_t)stream, (const uint16_t*)qkv,
                     (const long long*)pos, (uint16_t*)q_out, (uint16_t*)k_cache, (uint16_t*)v_cache, q_heads,
-                    kv_heads, max_len, theta);
+                    kv_heads, max_len, theta, paired);
+}
+
+extern "C" int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache,
+                               int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
+                               void* stream) {
+  return rope_append_impl(qkv, pos, q_out, k_cache, v_cache, rows, q_heads, kv_heads, head_dim, max_len, theta, 0, stream);
+}
+
+extern "C" int fdk_rope_append_paired(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache,
+                                      int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
+                                      void* stream) {
+  return rope_append_impl(qkv, pos, q_out, k_cache, v_cache, rows, q_heads, kv_heads, head_dim, max_len, theta, 1, stream);
+}
+
+extern "C" int fdk_rope_table(const void* pos, void* table, float theta, void* stream) {
+  FDK_CHECK_ARG(pos && table, FDK_ERR_BAD_ARG, "null pointer");
+  return launch_pdl(rope_table_kernel, dim3(1), dim3(64), 0, (cudaStream_t)stream, (const long long*)pos,
+                    (uint32_t*)table, theta);
+}
+
+extern "C" int fdk_sumsq_tiles(const void* h, float* sumsq, int rows, int width, void* stream) {
+  FDK_CHECK_ARG(h && sumsq, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(rows > 0 && width > 0, FDK_ERR_BAD_ARG, "non-positive size");
+  const int tiles = (width + 63) / 64;
+  return launch_pdl(sumsq_tiles_kernel, dim3((tiles + 7) / 8, rows), dim3(256), 0, (cudaStream_t)stream,
+                    (const uint16_t*)h, sumsq, width, tiles);
 }
 
 extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, int group, void* stream) {

@@ -1,6 +1,7 @@
 // C entry points of the fused GEMV / skinny GEMM (the kernel itself: linear_lut_kernel.cuh,
 // instantiated per code width in linear_lut_bits*.cu).
 #include <cstring>
+#include <mutex>
 
 #include "linear_lut_params.cuh"
 #include "tp_exchange.cuh"
@@ -22,9 +23,11 @@ __global__ void probe_smem_base_kernel() {
 int dynamic_smem_base(uint32_t* out) {
   static uint32_t cache[64];
   static bool have[64] = {};
+  static std::mutex mu;
   int dev = 0;
   FDK_CUDA(cudaGetDevice(&dev));
   dev &= 63;
+  std::lock_guard<std::mutex> lock(mu);
   if (!have[dev]) {
     probe_smem_base_kernel<<<1, 1, 1024>>>();
     FDK_CUDA(cudaGetLastError());
@@ -64,11 +67,14 @@ extern "C" int fdk_workspace_status(const void* workspace, int* status_host) {
 
 static int linear_lut_impl(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
                            int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
-                           unsigned flags, const fdk_tp_exchange* ex, void* stream) {
+                           unsigned flags, const fdk_tp_exchange* ex, const fdk_linear_fusion* fu, void* stream) {
   FDK_CHECK_ARG(m > 0 && n > 0 && k > 0, FDK_ERR_BAD_ARG, "m=%d, n=%d, k=%d must be positive", m, n, k);
   FDK_CHECK_ARG(bits_supported(bits), FDK_ERR_SHAPE, "bits=%d not in {1,2,3,4,8}", bits);
   FDK_CHECK_ARG(k % kBlock == 0, FDK_ERR_SHAPE, "k=%d must be a multiple of 64", k);
-  FDK_CHECK_ARG(x && tiled && (lut || lut_host) && (out || ex), FDK_ERR_BAD_ARG, "null pointer");
+  const bool norm = fu != nullptr && fu->norm_h != nullptr;
+  const bool resid = fu != nullptr && fu->resid_h != nullptr;
+  const bool rope = fu != nullptr && fu->rope_pos != nullptr;
+  FDK_CHECK_ARG((x || norm) && tiled && (lut || lut_host) && (out || ex || resid || rope), FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(dtype == FDK_DTYPE_BF16 || dtype == FDK_DTYPE_F16, FDK_ERR_BAD_ARG, "dtype=%d", dtype);
   FDK_CHECK_ARG((flags & ~(FDK_FLAG_PDL | FDK_FLAG_SILU_PAIRS)) == 0, FDK_ERR_BAD_ARG, "unknown flags 0x%x", flags);
   FDK_CHECK_ARG(!(flags & FDK_FLAG_SILU_PAIRS) || (ex == nullptr && m <= 16 && n % kTileRows == 0), FDK_ERR_SHAPE,
@@ -115,7 +121,41 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
     }
     p.seq = (const uint32_t*)((const uint8_t*)ex->buffers[ex->rank] + kTpSeqOffset);
   }
-  if (ex == nullptr && !(flags & FDK_FLAG_SILU_PAIRS) && m > 8) {
+  if (fu != nullptr) {
+    FDK_CHECK_ARG(ex == nullptr && m <= 16 && dtype == FDK_DTYPE_BF16, FDK_ERR_SHAPE,
+                  "the decode fusions take bf16 batches of up to 16 rows (m=%d)", m);
+    FDK_CHECK_ARG(!(resid && rope) && !((resid || rope) && (flags & FDK_FLAG_SILU_PAIRS)), FDK_ERR_BAD_ARG,
+                  "one output fusion at a time");
+    if (norm) {
+      FDK_CHECK_ARG(fu->norm_weight && fu->norm_sumsq && fu->norm_tiles > 0, FDK_ERR_BAD_ARG, "incomplete norm fusion");
+      FDK_CHECK_ARG((((uintptr_t)fu->norm_h | (uintptr_t)fu->norm_weight) & 15) == 0, FDK_ERR_ALIGN,
+                    "norm_h and norm_weight must be 16-byte aligned");
+      p.norm_h = (const uint16_t*)fu->norm_h;
+      p.norm_w = (const uint16_t*)fu->norm_weight;
+      p.norm_ss = fu->norm_sumsq;
+      p.norm_tiles = fu->norm_tiles;
+      p.norm_eps = fu->norm_eps;
+    }
+    if (resid) {
+      FDK_CHECK_ARG(fu->resid_sumsq != nullptr, FDK_ERR_BAD_ARG, "resid_sumsq is null");
+      p.resid_h = (uint16_t*)fu->resid_h;
+      p.resid_ss = fu->resid_sumsq;
+    }
+    if (rope) {
+      FDK_CHECK_ARG(fu->rope_table && fu->q_out && fu->k_cache && fu->v_cache, FDK_ERR_BAD_ARG, "incomplete rotary fusion");
+      FDK_CHECK_ARG(fu->q_heads > 0 && fu->kv_heads > 0 && fu->max_len > 0 && n == (fu->q_heads + 2 * fu->kv_heads) * 128,
+                    FDK_ERR_SHAPE, "n=%d must be (q_heads + 2 kv_heads) * 128 (%d, %d)", n, fu->q_heads, fu->kv_heads);
+      p.rope_pos = (const long long*)fu->rope_pos;
+      p.rope_table = (const uint32_t*)fu->rope_table;
+      p.q_out = (uint16_t*)fu->q_out;
+      p.k_cache = (uint16_t*)fu->k_cache;
+      p.v_cache = (uint16_t*)fu->v_cache;
+      p.q_heads = fu->q_heads;
+      p.kv_heads = fu->kv_heads;
+      p.max_len = fu->max_len;
+    }
+  }
+  if (fu == nullptr && ex == nullptr && !(flags & FDK_FLAG_SILU_PAIRS) && m > 8) {
     return gemm_lut_tc(x, tiled, lut, lut_host, out, m, n, k, bits, dtype == FDK_DTYPE_F16, workspace, workspace_bytes,
                        di.sm_count,
                        (cudaStream_t)stream);
@@ -142,7 +182,15 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
                               size_t workspace_bytes, unsigned flags, void* stream) {
   FDK_CHECK_ARG(out != nullptr, FDK_ERR_BAD_ARG, "null pointer");
   return linear_lut_impl(x, tiled, lut, lut_host, out, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
-                         nullptr, stream);
+                         nullptr, nullptr, stream);
+}
+
+extern "C" int fdk_linear_lut_fused(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
+                                    int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
+                                    unsigned flags, const fdk_linear_fusion* fusion, void* stream) {
+  FDK_CHECK_ARG(fusion != nullptr, FDK_ERR_BAD_ARG, "fusion is null");
+  return linear_lut_impl(x, tiled, lut, lut_host, out, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
+                         nullptr, fusion, stream);
 }
 
 extern "C" int fdk_linear_lut_push(const void* x, const void* tiled, const void* lut, const void* lut_host, int m,
@@ -150,7 +198,7 @@ extern "C" int fdk_linear_lut_push(const void* x, const void* tiled, const void*
                                    unsigned flags, const fdk_tp_exchange* ex, void* stream) {
   FDK_CHECK_ARG(ex != nullptr, FDK_ERR_BAD_ARG, "exchange is null");
   return linear_lut_impl(x, tiled, lut, lut_host, nullptr, m, n, k, bits, dtype, workspace, workspace_bytes, flags,
-                         ex, stream);
+                         ex, nullptr, stream);
 }
 
 // ---- entry point that allocates nothing ---------------------------------------------------
@@ -164,20 +212,30 @@ constexpr int kStaticMaxSms = 160;
 constexpr size_t kStaticScratchBytes = kCounterBytes + (size_t)kStaticMaxSms * 1024 * sizeof(uint2);  // 1,327,104
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-extern "C" int fdk_linear_lut_static(const void* x, const void* tiled, const void* lut, const void* lut_host,
-                                     void* out, int m, int n, int k, int bits, int dtype, unsigned flags,
-                                     void* stream) {
-  // In host code `g_static_scratch` is only a handle for the symbol; the kernel needs the
-  // array's address on the CURRENT device, looked up once per device.
+// The array's address on the current device (looked up once per device; nothing is allocated).
+static int static_scratch(void** out) {
   static void* scratch_of_device[64] = {};
+  static std::mutex mu;
   int dev = 0;
   FDK_CUDA(cudaGetDevice(&dev));
   FDK_CHECK_ARG(dev >= 0 && dev < 64, FDK_ERR_BAD_ARG, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
   if (scratch_of_device[dev] == nullptr) {
+    // In host code `g_static_scratch` is only a handle for the symbol; the kernel needs the
+    // array's address on the CURRENT device.
     void* ptr = nullptr;
     FDK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
     scratch_of_device[dev] = ptr;  // zero-filled when the module was loaded: nothing to clear
   }
+  *out = scratch_of_device[dev];
+  return FDK_OK;
+}
+
+extern "C" int fdk_linear_lut_static(const void* x, const void* tiled, const void* lut, const void* lut_host,
+                                     void* out, int m, int n, int k, int bits, int dtype, unsigned flags,
+                                     void* stream) {
+  void* scratch = nullptr;
+  if (int st = static_scratch(&scratch)) return st;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
   const size_t need = kCounterBytes + (size_t)di.sm_count * 1024 * sizeof(uint2);
@@ -185,6 +243,13 @@ extern "C" int fdk_linear_lut_static(const void* x, const void* tiled, const voi
                 "this GPU has %d multiprocessors and needs %zu bytes of scratch; the built-in scratch holds %zu "
                 "(up to %d multiprocessors): use fdk_linear_lut with a caller-allocated workspace",
                 di.sm_count, need, kStaticScratchBytes, kStaticMaxSms);
-  return fdk_linear_lut(x, tiled, lut, lut_host, out, m, n, k, bits, dtype, scratch_of_device[dev],
-                        kStaticScratchBytes, flags, stream);
+  return fdk_linear_lut(x, tiled, lut, lut_host, out, m, n, k, bits, dtype, scratch, kStaticScratchBytes, flags, stream);
+}
+
+extern "C" int fdk_static_status(int* status_host) {
+  FDK_CHECK_ARG(status_host != nullptr, FDK_ERR_BAD_ARG, "null pointer");
+  void* scratch = nullptr;
+  if (int st = static_scratch(&scratch)) return st;
+  FDK_CUDA(cudaMemcpy(status_host, (const int*)scratch + kStatusWord, sizeof(int), cudaMemcpyDeviceToHost));
+  return FDK_OK;
 }

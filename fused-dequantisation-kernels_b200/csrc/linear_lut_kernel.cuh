@@ -158,7 +158,14 @@ constexpr uint32_t kSpinLimit = 1u << 24;  // polls of a memory word before givi
 // EPI: what is done with a finished row tile -- kEpiStore: written to `out`; kEpiSilu:
 // silu(gate) * up written to `out`; kEpiPush: stored into every rank's exchange buffer.  A
 // template parameter so that the plain kernel carries none of the other two's code.
-constexpr int kEpiStore = 0, kEpiSilu = 1, kEpiPush = 2;
+// kEpiResid: added to the residual stream in place, with the sums of squares the next RMSNorm
+// needs; kEpiRope: rotary embedding of the q and k heads and the KV-cache append.
+constexpr int kEpiStore = 0, kEpiSilu = 1, kEpiPush = 2, kEpiResid = 3, kEpiRope = 4;
+
+// Shared-memory words ahead of everything else (offsets in bytes from the start of the dynamic
+// shared memory): the epilogue's sync words, the RMSNorm factors of the batch rows, the
+// position and the cos/sin table of the rotary epilogue.
+constexpr uint32_t kSmemInv = 32, kSmemPos = 96, kSmemRope = 128, kSmemHead = 512;
 
 // n / k_slabs for n * k_slabs < 2^32, by multiplication with k_magic = ceil(2^32 / k_slabs)
 __device__ __forceinline__ int div_k(const LinearParams& p, int n) {
@@ -222,7 +229,8 @@ __device__ __forceinline__ bool fetch_foreign(const LinearParams& p, float* stas
 // tile).  `publish`: the sums go to `mine` in the workspace as tagged words and nothing else is done.
 template <int NB, int WARPS, bool FP16, int EPI>
 __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots, const float* stash, uint2* mine,
-                                            bool foreign, bool publish, uint32_t tag, int rt, uint32_t push_seq) {
+                                            bool foreign, bool publish, uint32_t tag, int rt, uint32_t push_seq,
+                                            const uint32_t (&hpre)[8 * NB], const uint8_t* smem_head) {
   const int lane = threadIdx.x & 31;
   const int tt = p.slot_t, sw = 32 * tt;
   const int E = NB * kSubTiles * sw;
@@ -314,6 +322,79 @@ __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots,
         }
       }
     }
+    if constexpr (EPI == kEpiResid) {
+      // lane l takes rows l and l + 32 of the tile, for every batch row: y rounded as if stored,
+      // added to the residual stream (the values of h were fetched before the deposits came in),
+      // squares summed over the tile in a fixed order
+      const int row_tiles = (p.n + kTileRows - 1) / kTileRows;
+#pragma unroll
+      for (int b = 0; b < 8 * NB; ++b) {
+        if (b < p.m) {
+          const int nb = b >> 3, tq = (b & 7) >> 1;
+          float sq = 0.f;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int lrow = lane + 32 * half;
+            const int r = lrow >> 4, gg = lrow & 7, hi = (lrow >> 3) & 1;
+            const int e = (((r * NB + nb) * tt + tq) * 8 + gg) * 4 + 2 * hi + (b & 1);
+            const int row = rt * kTileRows + lrow;
+            if (row < p.n) {
+              const float y = to_float<FP16>(from_float<FP16>(slots[e]));
+              const float hold = to_float<FP16>((uint16_t)(half ? hpre[b] >> 16 : hpre[b] & 0xFFFFu));
+              const uint16_t hnew = from_float<FP16>(hold + y);
+              p.resid_h[(size_t)b * p.n + row] = hnew;
+              const float hf = to_float<FP16>(hnew);
+              sq = fmaf(hf, hf, sq);
+            }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+          if (lane == 0) p.resid_ss[(size_t)b * row_tiles + rt] = sq;
+        }
+      }
+    }
+    if constexpr (EPI == kEpiRope) {
+      // tile rt is half t of head rt / 2; for q and k heads its sub-tiles 0,1 hold dimensions
+      // 32 t .. 32 t + 31 and sub-tiles 2,3 their partners 64 further on
+      auto rnd = [](float v) { return to_float<FP16>(from_float<FP16>(v)); };
+      const int head = rt >> 1, th = rt & 1;
+      const long long pos = *reinterpret_cast<const long long*>(smem_head + kSmemPos);
+      const bool in_cache = pos >= 0 && pos < p.max_len;
+      const uint32_t* table = reinterpret_cast<const uint32_t*>(smem_head + kSmemRope);
+#pragma unroll 1
+      for (int blk = 0; blk < 2 * NB; ++blk) {
+        const int r = blk / NB, nb = blk - r * NB;
+        const int lrow = 16 * r + g + 8 * (c >> 1);  // 0 .. 31
+#pragma unroll 1
+        for (int tq = 0; tq < tt; ++tq) {
+          const int b = 8 * nb + 2 * tq + (c & 1);
+          if (b < p.m) {
+            const float x0 = rnd(slots[blk * sw + tq * 32 + lane]);
+            const float x1 = rnd(slots[(blk + 2 * NB) * sw + tq * 32 + lane]);
+            if (head < p.q_heads + p.kv_heads) {
+              const uint32_t cs = table[32 * th + lrow];
+              const float co = pair_lo<FP16>(cs), si = pair_hi<FP16>(cs);
+              const uint16_t o0 = from_float<FP16>(rnd(x0 * co) + rnd(-x1 * si));
+              const uint16_t o1 = from_float<FP16>(rnd(x1 * co) + rnd(x0 * si));
+              uint16_t* dst = nullptr;
+              if (head < p.q_heads) {
+                dst = p.q_out + ((size_t)b * p.q_heads + head) * 128;
+              } else if (in_cache) {
+                dst = p.k_cache + (((size_t)b * p.kv_heads + (head - p.q_heads)) * p.max_len + pos) * 128;
+              }
+              if (dst != nullptr) {
+                dst[32 * th + lrow] = o0;
+                dst[32 * th + lrow + 64] = o1;
+              }
+            } else if (in_cache) {  // v: rows in their own order
+              uint16_t* dst = p.v_cache + (((size_t)b * p.kv_heads + (head - p.q_heads - p.kv_heads)) * p.max_len + pos) * 128;
+              dst[64 * th + lrow] = from_float<FP16>(x0);
+              dst[64 * th + lrow + 32] = from_float<FP16>(x1);
+            }
+          }
+        }
+      }
+    }
     if constexpr (EPI == kEpiPush) {
       __syncwarp();
       const uint32_t ptag = push_seq + 1u;
@@ -393,7 +474,8 @@ __device__ __forceinline__ bool wait_shared_word(volatile int* word, int want) {
 }
 
 // WARPS compute warps and one finisher warp (the last one).
-template <int BITS, int NB, int WARPS, bool FP16, int EPI, bool XRES>
+// NORM: x is the RMSNorm of p.norm_h, applied while x is staged (needs XRES).
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, bool XRES, bool NORM = false>
 __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
@@ -459,8 +541,63 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     uses_last = ld_relaxed_s32(p.counters + rt_last);
     // number of this push = reduces completed before this launch (the reduce kernel counts)
     if (EPI == kEpiPush) push_seq = (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq));
+    if constexpr (EPI == kEpiRope) {  // the position and its cos/sin table, kept in shared memory
+      uint32_t* table = reinterpret_cast<uint32_t*>(smem_raw + kSmemRope);
+      table[lane] = __ldcg(p.rope_table + lane);
+      table[lane + 32] = __ldcg(p.rope_table + lane + 32);
+      if (lane == 0) *reinterpret_cast<long long*>(smem_raw + kSmemPos) = *reinterpret_cast<const volatile long long*>(p.rope_pos);
+    }
   }
-  if constexpr (XRES) {  // x fits: one copy per CTA
+  if constexpr (XRES && NORM) {
+    // x = norm_w * round(h * rsqrt(mean(h^2) + eps)), the roundings of the separate RMSNorm
+    // kernel; mean(h^2) from the sums of squares the previous projection left per 64 elements.
+    // A thread's first two vectors of h and of the norm weight are requested before the
+    // factors are computed, so that all of it costs one round trip to L2.
+    static_assert(!NORM || XRES, "the norm is applied while x is staged in shared memory");
+    const int vecs = p.k >> 3, total = p.m * vecs;
+    float* inv_smem = reinterpret_cast<float*>(smem_raw + kSmemInv);
+    uint4 hv[2], wv[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = threadIdx.x + u * kThreads;
+      if (i < total) {
+        hv[u] = ldg_l2(p.norm_h + (size_t)i * 8);
+        wv[u] = ldg_l2(p.norm_w + (size_t)(i % vecs) * 8);
+      }
+    }
+    if (warp < p.m) {  // one warp per batch row: partial sums added in a fixed order
+      float ssum = 0.f;
+      for (int j = lane; j < p.norm_tiles; j += 32) ssum += __ldcg(p.norm_ss + (size_t)warp * p.norm_tiles + j);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+      if (lane == 0) inv_smem[warp] = rsqrtf(ssum / (float)p.k + p.norm_eps);
+    }
+    __syncthreads();
+    auto stage = [&](int i, const uint4& h4, const uint4& w4) {
+      const int row = i / vecs, c = i - row * vecs;
+      const float inv = inv_smem[row];
+      const uint32_t* hw = reinterpret_cast<const uint32_t*>(&h4);
+      const uint32_t* ww = reinterpret_cast<const uint32_t*>(&w4);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = to_float<FP16>(from_float<FP16>(pair_lo<FP16>(hw[j]) * inv)) * pair_lo<FP16>(ww[j]);
+        const float b = to_float<FP16>(from_float<FP16>(pair_hi<FP16>(hw[j]) * inv)) * pair_hi<FP16>(ww[j]);
+        o[j] = (uint32_t)from_float<FP16>(a) | ((uint32_t)from_float<FP16>(b) << 16);
+      }
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xres_addr + row * p.xres_row + c * 16), "r"(o[0]),
+                   "r"(o[1]), "r"(o[2]), "r"(o[3])
+                   : "memory");
+    };
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = threadIdx.x + u * kThreads;
+      if (i < total) stage(i, hv[u], wv[u]);
+    }
+#pragma unroll 1
+    for (int i = threadIdx.x + 2 * kThreads; i < total; i += kThreads)
+      stage(i, ldg_l2(p.norm_h + (size_t)i * 8), ldg_l2(p.norm_w + (size_t)(i % vecs) * 8));
+  } else if constexpr (XRES) {  // x fits: one copy per CTA
     const int vecs = p.k >> 3;
 #pragma unroll 1
     for (int row = 0; row < p.m; ++row) {
@@ -497,10 +634,24 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
         if (!fetch_foreign<NB>(p, stash, rt, tag, E)) timed_out = true;
         __syncwarp();
       }
+      uint32_t hpre[8 * NB] = {};
+      if constexpr (EPI == kEpiResid) {  // the tile's part of the residual stream, fetched while the deposits come in
+        if (full || owner) {
+#pragma unroll
+          for (int b = 0; b < 8 * NB; ++b) {
+            if (b < p.m) {
+              const int row = rt * kTileRows + lane;
+              const uint16_t lo = row < p.n ? __ldcg(p.resid_h + (size_t)b * p.n + row) : (uint16_t)0;
+              const uint16_t hi = row + 32 < p.n ? __ldcg(p.resid_h + (size_t)b * p.n + row + 32) : (uint16_t)0;
+              hpre[b] = (uint32_t)lo | ((uint32_t)hi << 16);
+            }
+          }
+        }
+      }
       if (!wait_shared_word(&esync->count[set], W)) timed_out = true;
       __threadfence_block();
       tile_finish<NB, WARPS, FP16, EPI>(p, my_slots, stash, p.partial + (size_t)cta * (512 * NB), !full && owner,
-                                        !full && !owner, tag, rt, push_seq);
+                                        !full && !owner, tag, rt, push_seq, hpre, smem_raw);
       __syncwarp();
       if (lane == 0) {
         if (!full && owner) p.counters[rt] = (uses + 1) & 0x7FFFF;  // this use of the split tile is done
@@ -663,7 +814,7 @@ size_t plan_smem(uint32_t base, int warps, size_t limit, LinearParams& p, bool* 
   const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
   const uint32_t xres_bytes = align_up((uint32_t)p.m * xres_row, 128);
   p.xres_row = xres_row;
-  uint32_t low = 128;                                                   // cursor below the table
+  uint32_t low = kSmemHead;                                             // cursor below the table
   const uint32_t table_off = WIDE ? align_up(base + low, 65536) - base : low;
   uint32_t high = table_off + T::kBytes;                               // cursor above it
   p.table_off = table_off;
@@ -690,6 +841,39 @@ size_t plan_smem(uint32_t base, int warps, size_t limit, LinearParams& p, bool* 
   return high;
 }
 
+// Sets the kernel's shared-memory limit once per device and launches it.
+template <class Kernel, int BITS>
+int launch_kernel(Kernel kernel, std::atomic<size_t> (&configured)[64], const LinearParams& p, const InlineLut<BITS>& inl,
+                  int grid, int threads, size_t smem, unsigned flags, cudaStream_t stream) {
+  int dev = 0;
+  FDK_CUDA(cudaGetDevice(&dev));
+  std::atomic<size_t>& have = configured[dev & 63];
+  if (have.load(std::memory_order_acquire) < smem) {
+    FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    have.store(smem, std::memory_order_release);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & FDK_FLAG_PDL) ? 1 : 0;
+  FDK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, inl));
+  return FDK_OK;
+}
+
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, bool XRES, bool NORM>
+int launch_instance(const LinearParams& p, const InlineLut<BITS>& inl, int grid, size_t smem, unsigned flags,
+                    cudaStream_t stream) {
+  static std::atomic<size_t> configured[64] = {};
+  return launch_kernel(linear_lut_kernel<BITS, NB, WARPS, FP16, EPI, XRES, NORM>, configured, p, inl, grid,
+                       (WARPS + 1) * 32, smem, flags, stream);
+}
+
 template <int BITS, int NB, int WARPS, bool FP16>
 int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsigned flags, cudaStream_t stream) {
   uint32_t base = 0;
@@ -706,30 +890,40 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
   p.base = p.total / grid;
   p.rem = p.total % grid;
 
-  const int epi = p.tp > 0 ? kEpiPush : (p.silu ? kEpiSilu : kEpiStore);
-  auto kernel = epi == kEpiPush   ? (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiPush, false>)
-                : epi == kEpiSilu ? (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiSilu, false>)
-                                  : (xres ? linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore, true> : linear_lut_kernel<BITS, NB, WARPS, FP16, kEpiStore, false>);
-  static std::atomic<size_t> configured[6][64] = {};
-  int dev = 0;
-  FDK_CUDA(cudaGetDevice(&dev));
-  std::atomic<size_t>& have = configured[2 * epi + (xres ? 1 : 0)][dev & 63];
-  if (have.load(std::memory_order_acquire) < smem) {
-    FDK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    have.store(smem, std::memory_order_release);
+  const int epi = p.tp > 0 ? kEpiPush : p.silu ? kEpiSilu : p.resid_h != nullptr ? kEpiResid : p.rope_pos != nullptr ? kEpiRope : kEpiStore;
+  const bool norm = p.norm_h != nullptr;
+#define FDK_LAUNCH(EPI_, XRES_, NORM_) \
+  return launch_instance<BITS, NB, WARPS, FP16, EPI_, XRES_, NORM_>(p, inl, grid, smem, flags, stream)
+  if constexpr (!FP16) {  // the decode fusions exist for bf16 only
+    if (norm) {
+      FDK_CHECK_ARG(xres, FDK_ERR_SHAPE, "the fused RMSNorm needs x [%d, %d] to fit in shared memory", p.m, p.k);
+      if (epi == kEpiStore) FDK_LAUNCH(kEpiStore, true, true);
+      if (epi == kEpiSilu) FDK_LAUNCH(kEpiSilu, true, true);
+      if (epi == kEpiRope) FDK_LAUNCH(kEpiRope, true, true);
+      FDK_CHECK_ARG(false, FDK_ERR_BAD_ARG, "the fused RMSNorm goes with the plain, SiLU or rotary output only");
+    }
+    if (epi == kEpiResid) {
+      if (xres) FDK_LAUNCH(kEpiResid, true, false);
+      FDK_LAUNCH(kEpiResid, false, false);
+    }
+    if (epi == kEpiRope) {
+      if (xres) FDK_LAUNCH(kEpiRope, true, false);
+      FDK_LAUNCH(kEpiRope, false, false);
+    }
+  } else {
+    FDK_CHECK_ARG(!norm && epi != kEpiResid && epi != kEpiRope, FDK_ERR_BAD_ARG, "the decode fusions take bf16 only");
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3((WARPS + 1) * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = (flags & FDK_FLAG_PDL) ? 1 : 0;
-  FDK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, inl));
-  return FDK_OK;
+  if (epi == kEpiPush) {
+    if (xres) FDK_LAUNCH(kEpiPush, true, false);
+    FDK_LAUNCH(kEpiPush, false, false);
+  }
+  if (epi == kEpiSilu) {
+    if (xres) FDK_LAUNCH(kEpiSilu, true, false);
+    FDK_LAUNCH(kEpiSilu, false, false);
+  }
+  if (xres) FDK_LAUNCH(kEpiStore, true, false);
+  FDK_LAUNCH(kEpiStore, false, false);
+#undef FDK_LAUNCH
 }
 
 template <int BITS, int NB, bool FP16>

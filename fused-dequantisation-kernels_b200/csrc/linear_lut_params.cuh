@@ -29,6 +29,27 @@ struct LinearParams {
   uint32_t xres_off;      // all of x staged once per CTA at this offset (kernels instantiated with XRES)
   uint32_t xres_row;      // bytes between its rows
   uint32_t stash_off;     // E floats: the other CTAs' sums of a split row tile, fetched ahead by the finisher
+  // input side of the decode fusion (norm_h != null): x = norm_w * bf16(h * rsqrt(mean(h^2) + eps)),
+  // computed while x is staged; mean(h^2) of row b = sum of norm_ss[b][0 .. norm_tiles) / k
+  const uint16_t* norm_h;   // [m, k]
+  const uint16_t* norm_w;   // [k]
+  const float* norm_ss;     // [m, norm_tiles]
+  int norm_tiles;
+  float norm_eps;
+  // output side of the decode fusion, one of:
+  // residual (resid_h != null): h[m, n] += bf16(y) in place, resid_ss[b][row tile] = sum of the squares of
+  // the new h over the tile's 64 rows
+  uint16_t* resid_h;
+  float* resid_ss;          // [m, ceil(n / 64)]
+  // rotary (rope_pos != null): the rows are the fused q|k|v projection with every q and k head's rows
+  // ordered [0..31, 64..95, 32..63, 96..127]; q is rotated into q_out, k rotated and v copied into the
+  // caches at *rope_pos (nothing is written for a position outside [0, max_len))
+  const long long* rope_pos;
+  const uint32_t* rope_table;  // [64] {bf16 cos, bf16 sin} of the position's 64 angles
+  uint16_t* q_out;
+  uint16_t* k_cache;
+  uint16_t* v_cache;
+  int q_heads, kv_heads, max_len;
   // tensor-parallel push (tp > 0): outputs go to every rank's exchange buffer instead of `out`
   int silu;  // rows come as 32 gate + 32 up per tile; write silu(gate) * up, [m, n / 2]
   int tp, rank;

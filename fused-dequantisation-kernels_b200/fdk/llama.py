@@ -33,6 +33,9 @@ from .models import LlamaDims, QuantisationConfig, QuantisedLinear
 
 
 PAIR_GROUP = 32  # gate / up rows alternate in groups of this many (see _shard_layer_weights)
+# row order of a q or k head in the fused q|k|v weight: the two dimensions that the rotary
+# embedding combines (i, i + 64) in one 64-row tile of the projection kernel
+ROPE_ROW_ORDER = list(range(0, 32)) + list(range(64, 96)) + list(range(32, 64)) + list(range(96, 128))
 
 
 @dataclass
@@ -122,7 +125,12 @@ class LlamaDecoder(nn.Module):
         d = dims.head_dim
         qs = shard_rows(dims.num_attention_heads, tp)
         ks = shard_rows(dims.num_key_value_heads, tp)
-        qkv = torch.cat([q[qs.start * d: qs.stop * d], k[ks.start * d: ks.stop * d], v[ks.start * d: ks.stop * d]])
+        order = torch.tensor(ROPE_ROW_ORDER, device=q.device)
+
+        def paired(w):  # [heads * 128, hidden] -> the same with every head's rows in ROPE_ROW_ORDER
+            return w.unflatten(0, (-1, d))[:, order].flatten(0, 1)
+
+        qkv = torch.cat([paired(q[qs.start * d: qs.stop * d]), paired(k[ks.start * d: ks.stop * d]), v[ks.start * d: ks.stop * d]])
         fs = shard_rows(dims.intermediate_size, tp)
         # rows in groups of 64: 32 gate rows, then the 32 matching up rows, so that one 64-row
         # tile of the projection kernel holds both factors of 32 outputs of SiLU(gate) * up
@@ -215,6 +223,17 @@ class LlamaDecoder(nn.Module):
         # more slices than that only add merge work (16 rows: 16 us unsliced, 32 us in 4 slices)
         self.splits = max(1, min(max_len // 128, 148 // (batch * self.kv_heads), 16))
         self.attn_scratch, self.attn_counters = native.attention_scratch(batch, self.q_heads, self.kv_heads, self.splits, dev)
+        # the projections do the norms, the residual adds and the rotary embedding themselves where
+        # they can: native quantised layers, one rank, batches up to 16 rows, x small enough to be staged
+        native_layers = all(
+            isinstance(m, QuantisedLinear) and m.kernel != "torch.compile"
+            for l in self.layers for m in (l.qkv, l.o, l.gate_up, l.down)
+        )
+        self.fusions = None
+        if native_layers and self.tp.size == 1 and batch <= 16 and batch * (2 * h + 16) <= 64 * 1024 and h % 64 == 0:
+            self.sumsq = torch.zeros((batch, h // 64), device=dev, dtype=torch.float32)
+            self.rope_tab = torch.zeros(64, device=dev, dtype=torch.int32)
+            self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
         # fused push + reduce instead of NCCL: quantised row-parallel projections, batch <= 16
         self.close()
         can_push = all(
@@ -222,6 +241,24 @@ class LlamaDecoder(nn.Module):
         )
         if self.tp.size > 1 and self.tp.fused and batch <= 16 and can_push and h % 64 == 0:
             self.exchange = self.tp.open_exchange(16 * h, dev)
+
+    def _layer_fusions(self, i: int):
+        """The four fusion descriptors of layer i (pointers into this decoder's buffers)."""
+        layer, eps = self.layers[i], self.dims.rms_norm_eps
+
+        def norm(weight: Tensor) -> dict:
+            return dict(norm_h=self.hidden.data_ptr(), norm_weight=weight.data_ptr(), norm_sumsq=self.sumsq.data_ptr(),
+                        norm_tiles=self.sumsq.shape[1], norm_eps=eps)
+
+        resid = dict(resid_h=self.hidden.data_ptr(), resid_sumsq=self.sumsq.data_ptr())
+        rope = dict(rope_pos=self.position.data_ptr(), rope_table=self.rope_tab.data_ptr(), q_out=self.q.data_ptr(),
+                    k_cache=self.k_cache[i].data_ptr(), v_cache=self.v_cache[i].data_ptr(), q_heads=self.q_heads,
+                    kv_heads=self.kv_heads, max_len=self.max_len)
+        return (
+            native.LinearFusion(**norm(layer.input_norm), **rope),  # q|k|v
+            native.LinearFusion(**resid),                           # o and down
+            native.LinearFusion(**norm(layer.post_norm)),           # gate|up
+        )
 
     def _gated(self, layer: DecoderLayer) -> None:
         """self.act = SiLU(gate) * up of self.normed."""
@@ -266,11 +303,14 @@ class LlamaDecoder(nn.Module):
         torch.index_select(self.embed.weight, 0, tokens, out=self.hidden)
         if self.exchange is not None:
             return self._forward_fused()
+        if self.fusions is not None:
+            return self._forward_glue_fused()
         delta = None
         for i, layer in enumerate(self.layers):
             native.rmsnorm(self.hidden, delta, layer.input_norm, self.normed, eps)
             qkv = layer.qkv(self.normed)
-            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads, dims.rope_theta)
+            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads,
+                               dims.rope_theta, paired=True)
             native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
                                     self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
             delta = layer.o(self.attn)
@@ -280,6 +320,27 @@ class LlamaDecoder(nn.Module):
             delta = layer.down(self.act)
             self.tp.all_reduce(delta)
         native.rmsnorm(self.hidden, delta, self.final_norm, self.normed, eps)
+        logits = self._logits()
+        self.position += 1
+        return logits
+
+    def _forward_glue_fused(self) -> Tensor:
+        """The same step in five kernels per layer: the q|k|v projection applies the input RMSNorm
+        while it stages x and the rotary embedding + KV append in its epilogue; the o and down
+        projections add their result to the residual stream and leave the sums of squares for the
+        next norm; the gate|up projection applies the post-attention norm and SiLU(gate) * up."""
+        dims, eps, b = self.dims, self.dims.rms_norm_eps, self.batch
+        native.rope_table(self.position, self.rope_tab, dims.rope_theta)
+        native.sumsq_tiles(self.hidden, self.sumsq)
+        for i, layer in enumerate(self.layers):
+            f_qkv, f_resid, f_gate = self.fusions[i]
+            layer.qkv.fused(None, None, b, f_qkv)
+            native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
+                                    self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
+            layer.o.fused(self.attn, None, b, f_resid)
+            layer.gate_up.fused(None, self.act, b, f_gate, silu_pairs=True)
+            layer.down.fused(self.act, None, b, f_resid)
+        native.rmsnorm(self.hidden, None, self.final_norm, self.normed, eps)
         logits = self._logits()
         self.position += 1
         return logits
@@ -304,7 +365,8 @@ class LlamaDecoder(nn.Module):
             else:
                 native.rmsnorm_reduce(self.hidden, ex, layer.input_norm, self.normed, eps)
             qkv = layer.qkv(self.normed)
-            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads, dims.rope_theta)
+            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads,
+                               dims.rope_theta, paired=True)
             native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
                                     self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
             layer.o.push(self.attn, ex)

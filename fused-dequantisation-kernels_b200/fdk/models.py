@@ -129,6 +129,16 @@ class QuantisedLinear(nn.Module):
         else:
             native.silu_mul(self.forward(x), out, group=32)
 
+    def fused(self, x: Tensor | None, out: Tensor | None, rows: int, fusion: "native.LinearFusion",
+              silu_pairs: bool = False) -> None:
+        """The projection with the decode-step fusions of `fusion` (RMSNorm on the input side;
+        residual add or rotary embedding + KV append on the output side): bf16, up to 16 rows."""
+        assert self.kernel != "torch.compile" and rows <= 16
+        native.linear_lut_fused(
+            x, self.tiled(), self.lut, out, rows, self.out_features, self.in_features, self.bits, fusion,
+            pdl=True, lut_bytes=self.lut_bytes(), silu_pairs=silu_pairs,
+        )
+
     def push(self, x: Tensor, exchange: "native.TpExchange") -> None:
         """Row-parallel use in tensor-parallel decode: this rank's partial product goes straight
         into every rank's exchange buffer (no output tensor); native.rmsnorm_reduce sums them."""

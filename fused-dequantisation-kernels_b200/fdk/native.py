@@ -46,7 +46,36 @@ class TpExchange(ctypes.Structure):
     ]
 
 
+class LinearFusion(ctypes.Structure):
+    """`fdk_linear_fusion` of the C header: what the projection kernel does besides the product."""
+
+    _fields_ = [
+        ("norm_h", ctypes.c_void_p),
+        ("norm_weight", ctypes.c_void_p),
+        ("norm_sumsq", ctypes.c_void_p),
+        ("norm_tiles", ctypes.c_int),
+        ("norm_eps", ctypes.c_float),
+        ("resid_h", ctypes.c_void_p),
+        ("resid_sumsq", ctypes.c_void_p),
+        ("rope_pos", ctypes.c_void_p),
+        ("rope_table", ctypes.c_void_p),
+        ("q_out", ctypes.c_void_p),
+        ("k_cache", ctypes.c_void_p),
+        ("v_cache", ctypes.c_void_p),
+        ("q_heads", ctypes.c_int),
+        ("kv_heads", ctypes.c_int),
+        ("max_len", ctypes.c_int),
+    ]
+
+
 _SIGNATURES = {
+    "fdk_linear_lut_fused": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5
+        + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.POINTER(LinearFusion), ctypes.c_void_p],
+    ),
+    "fdk_rope_table": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p]),
+    "fdk_sumsq_tiles": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "fdk_tp_exchange_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_longlong]),
     "fdk_tp_buffer_create": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
     "fdk_tp_buffer_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
@@ -77,8 +106,10 @@ _SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_uint, ctypes.c_void_p],
     ),
+    "fdk_static_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "fdk_rmsnorm": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 2 + [ctypes.c_float, ctypes.c_void_p]),
     "fdk_rope_append": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_void_p]),
+    "fdk_rope_append_paired": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_void_p]),
     "fdk_silu_mul": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "fdk_decode_attention_scratch": (ctypes.c_int, [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_size_t)] * 2),
     "fdk_decode_attention": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_int] * 6 + [ctypes.c_void_p]),
@@ -222,6 +253,13 @@ def device_status(device: torch.device | None = None) -> int:
     return out.value
 
 
+def static_status() -> int:
+    """Device-side status word of the scratch built into fdk_linear_lut_static (synchronises)."""
+    out = ctypes.c_int(0)
+    check(lib().fdk_static_status(ctypes.byref(out)))
+    return out.value
+
+
 _host_luts: dict[int, tuple[weakref.ref, int, bytes]] = {}
 
 
@@ -257,6 +295,43 @@ def linear_lut(
                 (FLAG_PDL if pdl else 0) | (FLAG_SILU_PAIRS if silu_pairs else 0), _stream(),
             )
         )
+
+
+def linear_lut_fused(
+    x: Tensor | None, tiled: Tensor, lut: Tensor, out: Tensor | None, m: int, n: int, k: int, bits: int,
+    fusion: LinearFusion, pdl: bool = False, lut_bytes: bytes | None = None, silu_pairs: bool = False,
+) -> None:
+    """fdk_linear_lut with the decode-step fusions of `fusion` (see the C header): RMSNorm on the
+    input side; residual add + sums of squares, or rotary embedding + KV append, on the output side."""
+    _require_cuda(tiled, lut)
+    ws = workspace(tiled.device)
+    if lut_bytes is None:
+        lut_bytes = host_lut(lut)
+    with torch.cuda.device(tiled.device):
+        check(
+            lib().fdk_linear_lut_fused(
+                None if x is None else x.data_ptr(), tiled.data_ptr(), lut.data_ptr(), lut_bytes,
+                None if out is None else out.data_ptr(), m, n, k, bits, DTYPE_BF16, ws.data_ptr(), ws.numel(),
+                (FLAG_PDL if pdl else 0) | (FLAG_SILU_PAIRS if silu_pairs else 0), ctypes.byref(fusion), _stream(),
+            )
+        )
+
+
+def rope_table(pos: Tensor, table: Tensor, theta: float) -> None:
+    """table[64] int32 = {bf16 cos, bf16 sin} of the rotary angles at position `pos` (device int64)."""
+    _require_cuda(pos, table)
+    assert pos.dtype == torch.int64 and table.dtype == torch.int32 and table.numel() == 64
+    with torch.cuda.device(pos.device):
+        check(lib().fdk_rope_table(pos.data_ptr(), table.data_ptr(), theta, _stream()))
+
+
+def sumsq_tiles(h: Tensor, sumsq: Tensor) -> None:
+    """sumsq[rows, ceil(width / 64)] float32 = sums of squares of h per 64 elements."""
+    _require_cuda(h, sumsq)
+    rows, width = h.shape
+    assert sumsq.dtype == torch.float32 and sumsq.shape == (rows, (width + 63) // 64)
+    with torch.cuda.device(h.device):
+        check(lib().fdk_sumsq_tiles(h.data_ptr(), sumsq.data_ptr(), rows, width, _stream()))
 
 
 def rmsnorm(h: Tensor, delta: Tensor | None, weight: Tensor, out: Tensor, eps: float) -> None:
@@ -353,15 +428,16 @@ def rmsnorm_reduce(h: Tensor, ex: TpExchange, weight: Tensor, out: Tensor, eps: 
 
 def rope_append(
     qkv: Tensor, pos: Tensor, q_out: Tensor, k_cache: Tensor, v_cache: Tensor,
-    q_heads: int, kv_heads: int, theta: float,
+    q_heads: int, kv_heads: int, theta: float, paired: bool = False,
 ) -> None:
     """Rotary embedding of the fused q|k|v projection at position `pos` (device int64 scalar),
-    k and v appended to the caches [rows, kv_heads, max_len, 128]."""
+    k and v appended to the caches [rows, kv_heads, max_len, 128].  paired: the q and k heads come
+    in the row order of the projection kernel's rotary output ([0..31, 64..95, 32..63, 96..127])."""
     _require_cuda(qkv, pos, q_out, k_cache, v_cache)
     assert pos.dtype == torch.int64
     with torch.cuda.device(qkv.device):
         check(
-            lib().fdk_rope_append(
+            (lib().fdk_rope_append_paired if paired else lib().fdk_rope_append)(
                 qkv.data_ptr(), pos.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                 qkv.shape[0], q_heads, kv_heads, 128, k_cache.shape[2], theta, _stream(),
             )

@@ -162,6 +162,13 @@ int fdk_rope_append(const void* qkv, const void* pos, void* q_out, void* k_cache
                     int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
                     void* stream);
 
+/* The same for a q|k|v projection whose q and k heads come in the row order of the rotary output
+ * side of fdk_linear_lut_fused ([0..31, 64..95, 32..63, 96..127] per head; v heads in their own
+ * order): for batches that the fused form does not take.  q_out and the caches get the usual order. */
+int fdk_rope_append_paired(const void* qkv, const void* pos, void* q_out, void* k_cache, void* v_cache,
+                           int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
+                           void* stream);
+
 /* out[rows, width] = silu(gate) * up, gate_up [rows, 2 width] being the output of the fused
  * gate|up projection, whose columns alternate `group` gate values and the `group` matching up
  * values (group = width: all gates, then all ups; group = 32: the row order that
@@ -180,6 +187,55 @@ int fdk_decode_attention_scratch(int batch, int q_heads, int kv_heads, int split
 int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache, const void* pos,
                          void* out, void* scratch, void* counters, int batch, int q_heads,
                          int kv_heads, int head_dim, int max_len, int splits, void* stream);
+
+/* ---- decode-step fusions of fdk_linear_lut (bf16, m <= 16) -------------------------------
+ * Around each quantised projection the reference's model (transformers' Llama, called from
+ * Generator.step, src/fdk/models.py:245-255) runs an RMSNorm, a residual add or a rotary
+ * embedding as separate framework kernels.  Here the projection kernel does them itself:
+ *   input side   x = norm_weight * bf16(h * rsqrt(mean(h^2) + eps)) computed while x is staged
+ *                (the `x` argument is ignored); mean(h^2) of batch row b is the sum of
+ *                norm_sumsq[b][0 .. norm_tiles) divided by k: what the projection that last
+ *                updated h left behind (resid_sumsq), or fdk_sumsq_tiles.  x [m, k] must fit in
+ *                shared memory beside the kernel's tables (FDK_ERR_SHAPE otherwise).
+ *   output side, at most one of
+ *     residual   h[m, n] += bf16(y) in place (bf16 add, as the framework model does) instead of
+ *                writing `out`; resid_sumsq[b][t] = sum of squares of the new h over rows
+ *                64 t .. 64 t + 63 (fp32, fixed order);
+ *     rotary     the rows are the fused q|k|v projection, the rows of every q and k head
+ *                ordered [0..31, 64..95, 32..63, 96..127] (a pair of the rotate-half formula sits
+ *                in one 64-row tile); q is rotated into q_out [m, q_heads * 128], k rotated and v
+ *                copied into the caches [m, kv_heads, max_len, 128] at *rope_pos, with the
+ *                roundings of fdk_rope_append; rope_table as fdk_rope_table fills it.
+ *   FDK_FLAG_SILU_PAIRS may be combined with the input side.
+ * Results equal the unfused sequence of calls up to the order of the fp32 sum of squares. */
+typedef struct fdk_linear_fusion {
+  const void* norm_h;       /* [m, k] or NULL */
+  const void* norm_weight;  /* [k] */
+  const float* norm_sumsq;  /* [m, norm_tiles] */
+  int norm_tiles;
+  float norm_eps;
+  void* resid_h;            /* [m, n] or NULL */
+  float* resid_sumsq;       /* [m, ceil(n / 64)] */
+  const void* rope_pos;     /* device int64 or NULL */
+  const void* rope_table;   /* [64] {bf16 cos, bf16 sin} */
+  void* q_out;
+  void* k_cache;
+  void* v_cache;
+  int q_heads, kv_heads, max_len;
+} fdk_linear_fusion;
+
+int fdk_linear_lut_fused(const void* x, const void* tiled, const void* lut, const void* lut_host,
+                         void* out, int m, int n, int k, int bits, int dtype, void* workspace,
+                         size_t workspace_bytes, unsigned flags, const fdk_linear_fusion* fusion,
+                         void* stream);
+
+/* table[i] = {bf16 cos, bf16 sin} of the angle *pos * theta^(-2 i / 128), i = 0 .. 63: once per
+ * decode step, for the rotary output side above. */
+int fdk_rope_table(const void* pos, void* table, float theta, void* stream);
+
+/* sumsq[b][t] = sum of squares of h[b][64 t .. 64 t + 63] (fp32): the input-side fusion's
+ * sums for a residual stream that no projection has written yet (the embedding). */
+int fdk_sumsq_tiles(const void* h, float* sumsq, int rows, int width, void* stream);
 
 /* fdk_linear_lut for callers that cannot allocate device memory where they call it -- a
  * plugin inside a host runtime that owns all device allocations, or code running while a
@@ -200,6 +256,12 @@ int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache
 int fdk_linear_lut_static(const void* x, const void* tiled, const void* lut, const void* lut_host,
                           void* out, int m, int n, int k, int bits, int dtype, unsigned flags,
                           void* stream);
+
+/* The device-side status word of the built-in scratch of fdk_linear_lut_static on the current
+ * device, as fdk_workspace_status reports it for a caller's workspace (synchronous copy of one
+ * word; allocates nothing): 0 when every call so far ran normally.  No counterpart in the
+ * reference. */
+int fdk_static_status(int* status_host);
 
 /* ---- tensor-parallel exchange: row-parallel projection fused with its all-reduce ----------
  * The reference runs on one GPU (its src/ has no collective).  Here a row-parallel projection

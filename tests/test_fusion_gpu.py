@@ -1,0 +1,170 @@
+"""The decode-step fusions of the projection kernel (fdk_linear_lut_fused) against the unfused
+sequence of C-ABI calls they replace:
+
+  * residual output: fdk_linear_lut followed by a bf16 add into the residual stream, and the
+    per-tile sums of squares computed by torch -- the new h bit for bit;
+  * RMSNorm input: fdk_rmsnorm followed by fdk_linear_lut -- equal up to the order in which the
+    sum of squares is added (a last-place difference of the norm factor at most);
+  * rotary output: fdk_linear_lut followed by fdk_rope_append on the same (row-paired) weight --
+    q and the KV caches bit for bit;
+  * the whole decode step with and without the fusions.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import fdk_oracle as O
+from gpu_util import from_bits, random_problem, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native():
+    from fdk import native as nat
+
+    nat.lib()
+    return nat
+
+
+def _problem(native, n, k, bits, m, seed, scale_up=8.0):
+    codes, lut, scale, x = random_problem(n, k, bits, m, seed=seed)
+    scale = O.f32_to_bf16(O.bf16_to_f32(scale) * np.float32(scale_up))  # outputs of order one
+    tiled = native.repack(torch.from_numpy(codes).cuda(), from_bits(scale), n, k, bits, 64)
+    return tiled, from_bits(lut), from_bits(x)
+
+
+@pytest.mark.parametrize("bits,m,n,k", [(4, 1, 3072, 3072), (4, 3, 1000, 512), (2, 8, 3072, 8192), (4, 12, 512, 1024), (1, 2, 192, 256)])
+def test_residual_output(native, bits, m, n, k):
+    tiled, lut, x = _problem(native, n, k, bits, m, seed=n + m)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    native.linear_lut(x, tiled, lut, y, n, k, bits)
+    h0 = torch.randn((m, n), device="cuda").bfloat16()
+    tiles = (n + 63) // 64
+    for repeat in range(2):
+        h = h0.clone()
+        sumsq = torch.full((m, tiles), float("nan"), device="cuda")
+        fusion = native.LinearFusion(resid_h=h.data_ptr(), resid_sumsq=sumsq.data_ptr())
+        native.linear_lut_fused(x, tiled, lut, None, m, n, k, bits, fusion)
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        if m <= 8:
+            want = h0 + y  # bf16 add
+            assert torch.equal(h, want), f"{(h != want).sum().item()} elements of h differ"
+        else:  # the plain call runs the tensor-core kernel from 9 rows on: another fp32 summation order
+            assert (h.float() - (h0 + y).float()).abs().max().item() <= 2.0**-6 * (h0 + y).float().abs().max().item()
+        pad = torch.zeros((m, tiles * 64), device="cuda")
+        pad[:, :n] = h.float()
+        want_sq = pad.view(m, tiles, 64).pow(2).sum(-1)
+        assert torch.allclose(sumsq, want_sq, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("bits,m,n,k,silu", [(4, 1, 5120, 3072, False), (4, 2, 16384, 3072, True), (2, 8, 1024, 2048, False), (4, 12, 640, 1024, True)])
+def test_norm_input(native, bits, m, n, k, silu):
+    tiled, lut, _ = _problem(native, n, k, bits, m, seed=n + k + m)
+    h = (torch.randn((m, k), device="cuda") * 3).bfloat16()
+    weight = (1 + 0.1 * torch.randn(k, device="cuda")).bfloat16()
+    eps = 1e-6
+    normed = torch.empty_like(h)
+    native.rmsnorm(h, None, weight, normed, eps)
+    n_out = n // 2 if silu else n
+    want = torch.empty((m, n_out), dtype=torch.bfloat16, device="cuda")
+    if m <= 8 or silu:
+        native.linear_lut(normed, tiled, lut, want, n, k, bits, silu_pairs=silu)
+    sumsq = torch.empty((m, k // 64), device="cuda")
+    native.sumsq_tiles(h, sumsq)
+    assert torch.allclose(sumsq.sum(-1), h.float().pow(2).sum(-1), rtol=1e-5)
+    got = torch.full((m, n_out), float("nan"), dtype=torch.bfloat16, device="cuda")
+    fusion = native.LinearFusion(norm_h=h.data_ptr(), norm_weight=weight.data_ptr(), norm_sumsq=sumsq.data_ptr(),
+                                 norm_tiles=k // 64, norm_eps=eps)
+    native.linear_lut_fused(None, tiled, lut, got, m, n, k, bits, fusion, silu_pairs=silu)
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    err = (got.float() - want.float()).pow(2).sum().div(want.float().pow(2).sum()).sqrt().item()
+    assert err < 2e-3, f"rel-RMS difference {err}"
+    assert (got != want).float().mean().item() < 0.05  # a last-place difference of the norm factor at most
+
+
+@pytest.mark.parametrize("m,q_heads,kv_heads,k,pos_value", [(1, 24, 8, 3072, 1030), (3, 4, 2, 512, 0), (8, 6, 1, 1024, 2175), (16, 2, 2, 256, 63)])
+def test_rotary_output(native, m, q_heads, kv_heads, k, pos_value):
+    n, bits, max_len, theta = (q_heads + 2 * kv_heads) * 128, 4, 2304 if pos_value > 100 else 64, 500000.0
+    tiled, lut, x = _problem(native, n, k, bits, m, seed=q_heads + m)
+    pos = torch.tensor(pos_value, device="cuda", dtype=torch.int64)
+
+    def caches():
+        return (torch.full((m, kv_heads, max_len, 128), 7.0, device="cuda", dtype=torch.bfloat16),
+                torch.full((m, kv_heads, max_len, 128), 7.0, device="cuda", dtype=torch.bfloat16))
+
+    # unfused: projection, then the rotary kernel reading the paired row order
+    qkv = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    if m <= 8:
+        native.linear_lut(x, tiled, lut, qkv, n, k, bits)
+    want_k, want_v = caches()
+    want_q = torch.empty((m, q_heads * 128), dtype=torch.bfloat16, device="cuda")
+    table = torch.zeros(64, dtype=torch.int32, device="cuda")
+    native.rope_table(pos, table, theta)
+    got_k, got_v = caches()
+    got_q = torch.full((m, q_heads * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    fusion = native.LinearFusion(rope_pos=pos.data_ptr(), rope_table=table.data_ptr(), q_out=got_q.data_ptr(),
+                                 k_cache=got_k.data_ptr(), v_cache=got_v.data_ptr(), q_heads=q_heads, kv_heads=kv_heads,
+                                 max_len=max_len)
+    native.linear_lut_fused(x, tiled, lut, None, m, n, k, bits, fusion)
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    assert not bool(torch.isnan(got_q.float()).any())
+    if m <= 8:
+        native.rope_append(qkv, pos, want_q, want_k, want_v, q_heads, kv_heads, theta, paired=True)
+        torch.cuda.synchronize()
+        assert torch.equal(got_q, want_q) and torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
+    else:  # 9 rows and more: only the cache bookkeeping is checked here (the products by the case above)
+        untouched = torch.ones(max_len, dtype=torch.bool, device="cuda")
+        untouched[pos_value] = False
+        assert bool((got_k[:, :, untouched] == 7.0).all()) and bool((got_v[:, :, untouched] == 7.0).all())
+        assert not bool((got_k[:, :, pos_value] == 7.0).all())
+
+
+def test_paired_row_order_of_the_rotary_kernel(native):
+    """fdk_rope_append_paired on a head given in the paired row order = fdk_rope_append on the usual order."""
+    from fdk.llama import ROPE_ROW_ORDER
+
+    rows, q_heads, kv_heads, max_len = 2, 3, 1, 32
+    qkv = torch.randn((rows, (q_heads + 2 * kv_heads) * 128), device="cuda").bfloat16()
+    order = torch.tensor(ROPE_ROW_ORDER, device="cuda")
+    heads = qkv.view(rows, -1, 128).clone()
+    heads[:, : q_heads + kv_heads] = heads[:, : q_heads + kv_heads][:, :, order]
+    pos = torch.tensor(17, device="cuda")
+    outs = []
+    for tensor, paired in ((qkv, False), (heads.view(rows, -1).contiguous(), True)):
+        k_cache = torch.zeros((rows, kv_heads, max_len, 128), device="cuda", dtype=torch.bfloat16)
+        v_cache = torch.zeros_like(k_cache)
+        q_out = torch.empty((rows, q_heads * 128), device="cuda", dtype=torch.bfloat16)
+        native.rope_append(tensor, pos, q_out, k_cache, v_cache, q_heads, kv_heads, 500000.0, paired=paired)
+        outs.append((q_out, k_cache, v_cache))
+    torch.cuda.synchronize()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("batch", [1, 5, 12])
+def test_decode_step_with_and_without_fusions(batch):
+    from fdk import llama, models
+
+    device = torch.device("cuda")
+    dims = models.LlamaDims("tiny", 512, 3, 8, 2, 1024, vocab_size=640)
+    model = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(4, 64), device, seed=5, std=0.05)
+    steps = 6
+    ids = torch.randint(0, 640, (batch, steps), generator=torch.Generator().manual_seed(2)).to(device)
+    logits = []
+    for fused in (True, False):
+        model.allocate(batch, steps + 1)
+        assert model.fusions is not None
+        if not fused:
+            model.fusions = None
+        with torch.no_grad():
+            logits.append(torch.stack([model(ids[:, t].contiguous()).float() for t in range(steps)], dim=1))
+    torch.cuda.synchronize()
+    err = (logits[0] - logits[1]).pow(2).sum().div(logits[1].pow(2).sum()).sqrt().item()
+    # up to 8 rows both ways run the same projection kernel; from 9 rows on the unfused step takes the
+    # tensor-core kernel for its plain projections (bf16 W, another summation order)
+    assert err < (1e-2 if batch <= 8 else 3e-2), f"rel-RMS difference of the logits {err}"

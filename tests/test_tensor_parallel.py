@@ -28,17 +28,20 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         qkv_w, o_w, gu_w, down_w = llama.LlamaDecoder._shard_layer_weights(q, k, v, o, gate, up, down, dims, tp)
         x = (torch.randn((3, 256), generator=g)).bfloat16()
 
-        # column parallel: this rank's q rows equal the matching rows of the unsharded layer
+        # column parallel: this rank's q rows equal the matching rows of the unsharded layer (every
+        # head's rows in the order the rotary epilogue wants: ROPE_ROW_ORDER)
         full_q = models.QuantisedLinear.create(q, cfg)
         mine = models.QuantisedLinear.create(qkv_w, cfg)
         rows = llama.shard_rows(4, tp)
         n_q = (rows.stop - rows.start) * d
-        assert torch.equal(mine.weight_data[:n_q], full_q.weight_data[rows.start * d: rows.stop * d])
-        assert torch.equal(mine.scale[:n_q], full_q.scale[rows.start * d: rows.stop * d])
+        order = torch.tensor(llama.ROPE_ROW_ORDER)
+        paired = lambda t: t.unflatten(0, (-1, d))[:, order].flatten(0, 1)  # rows of every head reordered
+        assert torch.equal(mine.weight_data[:n_q], paired(full_q.weight_data[rows.start * d: rows.stop * d]))
+        assert torch.equal(mine.scale[:n_q], paired(full_q.scale[rows.start * d: rows.stop * d]))
         y_mine = mine(x)[:, :n_q].contiguous()
         gathered = [torch.empty_like(y_mine) for _ in range(world)]
         dist.all_gather(gathered, y_mine)
-        assert torch.equal(torch.cat(gathered, dim=1), full_q(x))
+        assert torch.equal(torch.cat(gathered, dim=1), paired(full_q(x).T).T)
 
         # row parallel: packed shard = byte-column slice; partial products all-reduce to the full one
         full_down = models.QuantisedLinear.create(down, cfg)

@@ -11,13 +11,12 @@ Collected last (file name) so that a run that stops at the first failure has alr
 every other test; it passes alone in a fresh process as well as after the others.
 """
 
-import gc
-
 import numpy as np
 import pytest
 import torch
 
-from gpu_util import from_bits, random_problem, to_bits
+import fdk_oracle as O
+from gpu_util import from_bits, oracle_dense, random_problem, to_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -45,16 +44,22 @@ def test_static_scratch_entry_matches_workspace_entry(bits, m, n, k):
     native.linear_lut(d_x, tiled, d_lut, expected, n, k, bits)
     torch.cuda.synchronize()
 
+    oracle = O.mm_dense(x, oracle_dense(codes, lut, scale, bits, k))
+    _call_static(native, d_x, tiled, d_lut, torch.empty_like(expected), n, k, bits)  # the one-time set-up call
+    torch.cuda.synchronize()
     for call in range(2):  # the second call reuses the array exactly as the first left it
         out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-        gc.collect()  # garbage of earlier tests freed during the call would change the count too
-        before = torch.cuda.memory_allocated()
-        _call_static(native, d_x, tiled, d_lut, out, n, k, bits)
-        assert torch.cuda.memory_allocated() == before  # nothing went through torch's allocator either
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()  # the driver's view: sees a cudaMalloc inside the library too
+        _call_static(native, d_x, tiled, d_lut, out, n, k, bits)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after >= free_before, f"call {call}: {free_before - free_after} bytes of device memory were allocated"
+        assert native.static_status() == 0
+        assert O.rmsen(O.bf16_to_f32(oracle), O.bf16_to_f32(to_bits(out))) < 4e-3
         if m <= 8:
             bad = np.argwhere(to_bits(out) != to_bits(expected))
-            assert len(bad) == 0, f"call {call}: {len(bad)} outputs differ, first at {bad[:4].tolist()}, status {native.device_status()}"
+            assert len(bad) == 0, f"call {call}: {len(bad)} outputs differ, first at {bad[:4].tolist()}, status {native.static_status()}"
         else:  # 9 rows and more run the tensor-core kernel, whose K range is split over CTAs only
             # where the workspace has room for the parked partial tiles: another fp32 summation order
             assert (out.float() - expected.float()).abs().max() <= 0.02 * expected.float().abs().max()
