@@ -4,10 +4,11 @@
 
 Workload (N = 1): y = x . W^T with K = N = 8192, batch 1, 4-bit codes, block 64, a
 16-entry k-means-like codebook -- the largest shape of the reference's kernel sweep
-(`python -m fdk.bench -k 8192 -b 4 -m 1`, README of the reference).  One STEP is one pass
+(`python -m fdk.bench -k 8192 -b 4 -m 1`, README of the reference).  One STEP is 32 passes
 over `copies` independent weight sets (8 x 35.7 MB, more than the 126 MB L2, so every
-pass streams from HBM), captured once as a CUDA graph the way the reference's harness
-does (src/fdk/bench.py:67-99) and replayed per step.
+pass streams from HBM), 256 GEMV launches captured once as a CUDA graph the way the
+reference's harness does (src/fdk/bench.py:67-99) and replayed per step: about 3 ms, so that
+even a 20-step run is timed over more than 50 ms and the clock samples fall under load.
 
 Printed JSON line: `value` = packed-weight bytes (codes + block scales) of all GPUs per
 second, device-timed with inputs resident in HBM; `e2e` = the same bytes per second
@@ -44,8 +45,25 @@ BITS = 4
 BLOCK = 64
 BATCH = 1
 COPIES = 8
+PASSES = 32  # passes over the weight sets per step (one CUDA graph): a step is ~3 ms, 20 steps > 50 ms
 WORKLOAD = f"gemv_lut k={K} n={N} m={BATCH} bits={BITS} g={BLOCK} codebook=kmeans16 copies={COPIES}"
 PACKED_BYTES = N * K * BITS // 8 + N * (K // BLOCK) * 2  # codes + bf16 block scales
+
+
+def measured_traffic(key: str):
+    """DRAM bytes (read + write) of one launch, from the table kept beside the ncu summaries
+    (profiles/dram_traffic.json); null when the kernel's source has changed since the capture."""
+    import hashlib
+
+    try:
+        table = json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())
+        entry = table[key]
+        source = ROOT / "fused-dequantisation-kernels_b200" / "csrc" / entry["source"]
+        if hashlib.sha256(source.read_bytes()).hexdigest()[:16] != entry["source_sha16"]:
+            return None
+        return int(entry["dram_bytes"])
+    except Exception:
+        return None
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -96,12 +114,17 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []  # (time the line was read, line)
+        self.window = (0.0, float("inf"))
+
+    def mark(self, start: float, end: float) -> None:
+        """Only samples read between these two time.monotonic() values count (the timed region)."""
+        self.window = (start, end)
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "10"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
             self.thread = threading.Thread(target=self._read, daemon=True)
@@ -112,11 +135,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.03)  # let the last sample of the region be read
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -126,7 +149,9 @@ class ClockSampler:
     def summary(self) -> dict:
         sm, sm_max, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for when, line in self.lines:
+            if not (self.window[0] <= when <= self.window[1] + 0.02):
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) != 6:
                 continue
@@ -247,7 +272,8 @@ def run_gpu_arm(args) -> None:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            one_pass()
+            for _ in range(PASSES):
+                one_pass()
         for _ in range(max(args.warmup, 3)):
             graph.replay()
         torch.cuda.synchronize()
@@ -259,17 +285,20 @@ def run_gpu_arm(args) -> None:
 
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local_rank) as clocks:
+            time.sleep(0.05)  # the sampler is up before the region starts
             barrier()
+            t_start = time.monotonic()
             start.record()
             for _ in range(args.steps):
                 graph.replay()
             end.record()
             barrier()
+            clocks.mark(t_start, time.monotonic())
         elapsed_ms = start.elapsed_time(end)
 
         # end to end through the module call with host buffers, per GEMV: pinned x -> device,
         # forward, y -> host (the device->host copy synchronises).
-        e2e_steps = max(1, min(args.steps, 20))
+        e2e_steps = max(1, min(args.steps, 5))
         e2e_s = float("nan")
         if not args.kernel_only:
             x_host = [x.cpu().pin_memory() for x in xs]
@@ -278,7 +307,7 @@ def run_gpu_arm(args) -> None:
                 y_host.copy_(layer(xh.to(device, non_blocking=True)))
             barrier()
             t0 = time.perf_counter()
-            for _ in range(e2e_steps):
+            for _ in range(e2e_steps * PASSES):
                 for layer, xh in zip(layers, x_host):
                     y_host.copy_(layer(xh.to(device, non_blocking=True)))
             torch.cuda.synchronize()
@@ -293,10 +322,10 @@ def run_gpu_arm(args) -> None:
     if not args.kernel_only and not args.no_decode:
         decode = decode_extra(device, world, rank)
 
-    launches = COPIES * args.steps
+    launches = PASSES * COPIES * args.steps
     ms_per_step = elapsed_ms / args.steps
-    value = world * COPIES * PACKED_BYTES / (ms_per_step * 1e-3) / 1e9
-    e2e_value = world * COPIES * e2e_steps * PACKED_BYTES / e2e_s / 1e9
+    value = world * PASSES * COPIES * PACKED_BYTES / (ms_per_step * 1e-3) / 1e9
+    e2e_value = world * PASSES * COPIES * e2e_steps * PACKED_BYTES / e2e_s / 1e9
     per_launch_s = elapsed_ms * 1e-3 / launches
     achieved = PACKED_BYTES / per_launch_s / 1e9
     peak, peak_kind = measured_peak_gbs()
@@ -307,9 +336,7 @@ def run_gpu_arm(args) -> None:
             cpu_times, cores, sample = cpu_reference_times(reps=20, warmup=2)
             cpu_value = PACKED_BYTES / statistics.fmean(cpu_times) / 1e9
             cpu_baseline = {"value": cpu_value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this shape,
-        # from the ncu capture summarised in profiles/linear_lut_kernel_4bit_8192_m1.md
-        traffic = 35_711_488
+        traffic = measured_traffic(f"linear_lut_kernel bits={BITS} n={N} k={K} m={BATCH}")
         line = {
             "metric": "packed_weight_gbs_gemv",
             "value": value,
@@ -325,7 +352,7 @@ def run_gpu_arm(args) -> None:
             "data": "synthetic",
             "config": {
                 "workload": WORKLOAD,
-                "step": f"{COPIES} GEMV launches, one per weight set, one CUDA graph, programmatic dependent launch",
+                "step": f"{PASSES} passes over {COPIES} weight sets = {PASSES * COPIES} GEMV launches, one CUDA graph, programmatic dependent launch",
                 "cache": f"inputs larger than L2: {COPIES} x {PACKED_BYTES} B of weights cycled",
                 "parallelism": "replicas" if world > 1 else "single",
             },
@@ -344,8 +371,8 @@ def run_gpu_arm(args) -> None:
             "e2e": {
                 "value": e2e_value,
                 "unit": "GB/s",
-                "h2d_bytes_per_step": COPIES * BATCH * K * 2,
-                "d2h_bytes_per_step": COPIES * BATCH * N * 2,
+                "h2d_bytes_per_step": PASSES * COPIES * BATCH * K * 2,
+                "d2h_bytes_per_step": PASSES * COPIES * BATCH * N * 2,
             },
             "gpu_launches": launches,
             "clocks": clocks.summary(),
@@ -362,50 +389,119 @@ def run_gpu_arm(args) -> None:
 
 
 def decode_extra(device, world: int, rank: int) -> dict:
-    """Second figure of the metric: greedy-decode tokens/s of the custom-llama "b200-4B" shape
-    (32 layers, d 3072, FFN 8192, 24/8 heads), 4-bit block-64 weights, batch 1, 1024 tokens of
-    (synthetic) context, one decode step per CUDA-graph replay as the reference times it
-    (src/fdk/models.py:313-340).  With N ranks the model is tensor parallel over them: the o and
-    down projections push their partial sums to every rank from the kernel and the next RMSNorm
-    adds them; the same run with NCCL all-reduces instead is timed beside it.  At N = 1 the
-    same loop with bf16 nn.Linear layers (cuBLAS) is timed beside it."""
+    """Second figure of the metric: greedy-decode tokens/s of the custom-llama shapes with 4-bit
+    block-64 weights, one decode step per CUDA-graph replay as the reference times it
+    (src/fdk/models.py:313-340), synthetic KV-cache contents of the stated context.
+      N = 1: "b200-4B" (32 layers, d 3072, FFN 8192, 24/8 heads), context 1024, batch 1 to 256,
+             beside the same loop with bf16 nn.Linear layers (cuBLAS) at batch 1 and 16; and
+             "b200-31B" (64 layers, d 6144, FFN 20480, 48/8 heads), context 2048, batch 1.
+      N > 1: the models tensor parallel over the N ranks (31B at context 2048, batch 1 and 16; 4B
+             at context 1024, batch 1): the o and down projections push their partial sums to
+             every rank from the kernel and the next RMSNorm adds them; the same run with NCCL
+             all-reduces instead is timed beside it; and the logits of a two-layer slice are
+             compared with those of the same slice run on one rank."""
     import torch
 
-    from fdk import llama, models
+    from fdk import llama, models, native
 
-    dims = models.get_custom_llama_dims("b200-4B")
-    tp = llama.TensorParallel(rank, world, fused=True)
-    out = {"model": "custom-llama-b200-4B", "bits": 4, "block_size": 64, "batch": 1, "context": 1024, "tp": world}
+    lut = kmeans_codebook(4, 0).to(device)
+    config = models.QuantisationConfig(4, 64)
+    out = {"bits": 4, "block_size": 64, "tp": world, "runs": []}
+
+    def run(model, name, batch, context, reps=30):
+        r = models.benchmark(model, batch, reps, context)
+        return {"model": name, "batch": batch, "context": context, "tokens_per_s": batch / r.avg_time,
+                "weight_gbs": r.bytes_rw / r.avg_time / 1e9}
+
     try:
-        model = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(4, 64), device, tp, lut=kmeans_codebook(4, 0).to(device))
-        r = models.benchmark(model, 1, 30, 1024)
-        out["tokens_per_s"] = 1 / r.avg_time
-        out["weight_gbs"] = r.bytes_rw / r.avg_time / 1e9
-        if world > 1:
-            from fdk import native
-
-            out["tp_reduce"] = "fused push" if model.exchange is not None else "nccl"
-            if model.exchange is not None:
-                out["exchange_status"] = native.tp_exchange_status(model.exchange)
-            model.close()
-            model.tp = llama.TensorParallel(rank, world)
-            rn = models.benchmark(model, 1, 30, 1024)
-            out["nccl_tokens_per_s"] = 1 / rn.avg_time
-        del model
-        torch.cuda.empty_cache()
+        tp = llama.TensorParallel(rank, world, fused=True)
         if world == 1:
+            dims = models.get_custom_llama_dims("b200-4B")
+            model = llama.LlamaDecoder.random_init(dims, config, device, tp, lut=lut)
+            for batch in (1, 4, 16, 64, 256):
+                out["runs"].append(run(model, "custom-llama-b200-4B", batch, 1024))
+            del model
+            torch.cuda.empty_cache()
             base = llama.LlamaDecoder.random_init(dims, None, device, tp)
-            rb = models.benchmark(base, 1, 30, 1024)
-            out["bf16_cublas_tokens_per_s"] = 1 / rb.avg_time
+            for batch in (1, 16):
+                entry = run(base, "custom-llama-b200-4B", batch, 1024)
+                entry["layers"] = "bf16 cuBLAS"
+                out["runs"].append(entry)
             del base
             torch.cuda.empty_cache()
+            big = llama.LlamaDecoder.random_init(models.get_custom_llama_dims("b200-31B"), config, device, tp, lut=lut)
+            out["runs"].append(run(big, "custom-llama-b200-31B", 1, 2048, reps=10))
+            del big
+            torch.cuda.empty_cache()
+        else:
+            out["slice_check"] = tp_slice_check(device, world, rank, lut)
+            for name, context, batches in (("b200-31B", 2048, (1, 16)), ("b200-4B", 1024, (1,))):
+                dims = models.get_custom_llama_dims(name)
+                model = llama.LlamaDecoder.random_init(dims, config, device, tp, lut=lut)
+                for batch in batches:
+                    entry = run(model, f"custom-llama-{name}", batch, context, reps=20)
+                    entry["tp_reduce"] = "fused push" if model.exchange is not None else "nccl"
+                    if model.exchange is not None:
+                        entry["exchange_status"] = native.tp_exchange_status(model.exchange)
+                    model.close()
+                    model.tp = llama.TensorParallel(rank, world)
+                    entry["nccl_tokens_per_s"] = batch / models.benchmark(model, batch, 20, context).avg_time
+                    model.tp = tp
+                    out["runs"].append(entry)
+                model.close()
+                del model
+                torch.cuda.empty_cache()
+        # the flat keys of the first run, as earlier records had them
+        first = out["runs"][0]
+        out.update(model=first["model"], batch=first["batch"], context=first["context"], tokens_per_s=first["tokens_per_s"],
+                   weight_gbs=first["weight_gbs"])
+        bf16 = [r for r in out["runs"] if r.get("layers") == "bf16 cuBLAS" and r["batch"] == 1]
+        if bf16:
+            out["bf16_cublas_tokens_per_s"] = bf16[0]["tokens_per_s"]
     except Exception as e:  # the headline line must still be printed
         out["error"] = repr(e)
     return out
 
 
+def tp_slice_check(device, world: int, rank: int, lut) -> dict:
+    """Values, not just status words: a two-layer slice of the 4B shape decoded for four steps on
+    all ranks (fused exchange) and on one rank alone (rank 0, same seed); the logits must agree
+    to the tolerance of the tensor-parallel tests (rel-RMS 2e-2: the ranks add partial sums of
+    bf16-rounded products in another order) and be identical on every rank."""
+    import dataclasses
+
+    import torch
+    import torch.distributed as dist
+
+    from fdk import llama, models
+
+    dims = dataclasses.replace(models.get_custom_llama_dims("b200-4B"), num_hidden_layers=2, vocab_size=4096)
+    config = models.QuantisationConfig(4, 64)
+    ids = torch.randint(0, dims.vocab_size, (2, 4), generator=torch.Generator().manual_seed(3)).to(device)
+
+    def decode(tp):
+        model = llama.LlamaDecoder.random_init(dims, config, device, tp, seed=11, lut=lut)
+        model.allocate(2, 8)
+        with torch.no_grad():
+            logits = torch.stack([model(ids[:, t].contiguous()).float() for t in range(4)], dim=1)
+        torch.cuda.synchronize()
+        model.close()
+        return logits
+
+    sharded = decode(llama.TensorParallel(rank, world, fused=True))
+    gathered = [torch.empty_like(sharded) for _ in range(world)]
+    dist.all_gather(gathered, sharded)
+    same = all(torch.equal(g, gathered[0]) for g in gathered)
+    result = {"identical_on_all_ranks": bool(same)}
+    if rank == 0:
+        alone = decode(llama.TensorParallel(0, 1))
+        err = (sharded - alone).pow(2).sum().div(alone.pow(2).sum()).sqrt().item()
+        result.update(rel_rms_vs_one_rank=err, ok=bool(same and err < 2e-2))
+    return result
+
+
 def main() -> None:
-    global COPIES, WORKLOAD
+    global COPIES, PASSES, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -413,9 +509,11 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     # profiling aids (the defaults are the benchmark): smaller footprint, kernel launches only
     ap.add_argument("--copies", type=int, default=COPIES, help="weight sets cycled per step")
+    ap.add_argument("--passes", type=int, default=PASSES, help="passes over the weight sets per step")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end, CPU and decode legs")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode tokens/s leg")
     args = ap.parse_args()
+    PASSES = args.passes
     if args.copies != COPIES:
         COPIES = args.copies
         WORKLOAD = f"gemv_lut k={K} n={N} m={BATCH} bits={BITS} g={BLOCK} codebook=kmeans16 copies={COPIES}"

@@ -471,17 +471,37 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                             uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
                             int q_heads, int kv_heads, int max_len, int chunk) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float part[kAttnWarps][G][132];
   __shared__ float wbuf[kAttnWarps][16 * 4 > 8 * G ? 16 * 4 : 8 * G];  // softmax weights of a round, per warp: U * G
   __shared__ int is_last;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // the current token's key and value are already in the cache; a position outside the cache is
-  // clamped (no key at all gives zeros)
+  // The position only changes between decode steps, and the keys and values of earlier
+  // positions were written in earlier steps: both may be read before the kernel that feeds
+  // this one (it writes q and the current position's key and value) has finished.
+  // A position outside the cache is clamped (no key at all gives zeros).
   const long long pos_now = *pos_ptr;
   const int len = pos_now < 0 ? 0 : (pos_now >= max_len ? max_len : (int)pos_now + 1);
   const int p0 = split * chunk, p1 = min(len, p0 + chunk);
+  const uint16_t* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
+  const uint16_t* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
+  // U positions per warp and iteration, all their loads in flight together: with a slice of up
+  // to 8 * U keys a warp pays the memory latency once -- and for its first U positions before
+  // the wait, beside the previous kernel
+  constexpr int U = (G <= 4) ? 16 : 8;
+  uint2 kk[U], vv[U];
+  const int pb_first = p0 + warp * U;
+  if (pb_first < p1) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int p = min(pb_first + u, p1 - 1);  // clamped reads, masked below
+      if (p != len - 1) {  // the current position is read after the wait
+        kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
+        vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
+      }
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   float qf[G][4], acc[G][4], mx[G], sum[G];
   const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
@@ -494,18 +514,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
     mx[j] = -INFINITY;
     sum[j] = 0.f;
   }
-  const uint16_t* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
-  const uint16_t* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
-  // U positions per warp and iteration, all their loads in flight together: with a slice of up
-  // to 8 * U keys a warp pays the memory latency once
-  constexpr int U = (G <= 4) ? 16 : 8;
-  for (int pb = p0 + warp * U; pb < p1; pb += kAttnWarps * U) {
-    uint2 kk[U], vv[U];
+  for (int pb = pb_first; pb < p1; pb += kAttnWarps * U) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int p = min(pb + u, p1 - 1);  // clamped reads, masked below
-      kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
-      vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
+      const int p = min(pb + u, p1 - 1);
+      if (pb != pb_first || p == len - 1) {
+        kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
+        vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
+      }
     }
     float s[U][G];
 #pragma unroll
@@ -625,11 +641,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   __threadfence();
   // merge the slices: first the per-slice weights (one thread per (head, slice)), then the sums
   __shared__ float coef[G][kMaxSplits];
+  __shared__ float lpart[G][kMaxSplits];
   __shared__ float denom[G];
   const float* base = scratch + ((size_t)b * kv_heads + kvh) * splits * (G * 130);
-  for (int idx = threadIdx.x; idx < G * splits; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < G * splits; idx += blockDim.x) {  // every slice's max and sum, all loads in flight
     const int j = idx / splits, s2 = idx - j * splits;
     coef[j][s2] = __ldcg(base + s2 * (G * 130) + j * 130 + 128);  // the slice's max for now
+    lpart[j][s2] = __ldcg(base + s2 * (G * 130) + j * 130 + 129);
   }
   __syncthreads();
   if (threadIdx.x < G) {
@@ -639,7 +657,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
     float l = 0.f;
     for (int s2 = 0; s2 < splits; ++s2) {
       const float c = (coef[j][s2] == -INFINITY) ? 0.f : __expf(coef[j][s2] - m);
-      l += __ldcg(base + s2 * (G * 130) + j * 130 + 129) * c;
+      l += lpart[j][s2] * c;
       coef[j][s2] = c;
     }
     denom[j] = l;
