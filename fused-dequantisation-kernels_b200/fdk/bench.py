@@ -19,6 +19,7 @@ import gc
 import itertools
 import json
 import math
+import os
 import re
 import subprocess
 import sys
@@ -224,16 +225,38 @@ class LutBenchmark(Benchmark):
         return fn
 
 
-class MarlinBenchmark(LutBenchmark):
-    """The reference's Marlin row (bench.py:335-379): fp16, 4 bits, g in {64, 128}."""
+class MarlinBenchmark(Benchmark):
+    """The reference's Marlin row (bench.py:335-379): fp16, 4 bits, g in {64, 128}, inputs drawn
+    as there (random int32 words in Marlin format, randn scales, a random [256, 2] table), through
+    `fdk.marlin.mul`."""
 
     def __init__(self) -> None:
-        super().__init__("marlin", kernels.run_mm_lut, vector=False, dtype=torch.float16)
+        super().__init__("marlin")
+
+    def bytes_rw(self, s: Settings) -> int:
+        # the lookup table and the workspace are not counted: they are shared by all copies
+        return s.n * (s.k * 4) // 8 + (s.m * s.k + s.n * (s.k // s.g) + s.m * s.n) * torch.float16.itemsize
 
     def setup(self, s: Settings) -> Callable[[int], None]:
         if s.bits != 4 or s.g not in (64, 128):
             raise UnsupportedSettings("marlin: bits=4, g=64 or 128 only")
-        return super().setup(s)
+        assert s.k % s.g == 0, "k must be divisible by g"
+        if s.k % 128 != 0 or s.n % 256 != 0:
+            raise UnsupportedSettings("marlin: k a multiple of 128 and n of 256 only")
+        from . import marlin
+
+        torch.manual_seed(42)
+        a = torch.randn((s.copies, s.m, s.k), device="cuda", dtype=torch.float16)
+        ii = torch.iinfo(torch.int32)
+        b = [torch.randint(ii.min, ii.max, (s.k // 16, 2 * s.n), device="cuda", dtype=torch.int32) for _ in range(s.copies)]
+        bs = [torch.randn((s.k // s.g, s.n), device="cuda", dtype=torch.float16) for _ in range(s.copies)]
+        out = torch.empty((s.copies, s.m, s.n), device="cuda", dtype=torch.float16)
+        centroids = torch.randn((256, 2), device="cuda", dtype=torch.float16)
+        workspace = torch.zeros(s.n // 128 * 16, dtype=torch.int)
+        fn = lambda i: marlin.mul(a[i % s.copies], b[i % s.copies], out[i % s.copies], bs[i % s.copies], centroids, workspace)
+        for i in range(s.copies):  # the one-time conversion of every weight set stays out of the timing
+            fn(i)
+        return fn
 
 
 def mm_lut_ref_unscaled(a: Tensor, bq: Tensor, lut8: Tensor, bs: Tensor, out: Tensor | None = None) -> Tensor:
@@ -297,14 +320,48 @@ def run_tests() -> None:
 
 
 def hbm_peak_gbs() -> tuple[float, str]:
-    for parent in Path(__file__).resolve().parents:
-        path = parent / "MEASURED_PEAKS.json"
-        if path.exists():
-            try:
-                return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
-            except Exception:
-                break
+    """The HBM bandwidth that fractions are quoted against: a measured value handed in through
+    FDK_HBM_PEAK_GBS, else an earlier measurement on B200 as a fallback."""
+    value = os.environ.get("FDK_HBM_PEAK_GBS")
+    if value:
+        try:
+            return float(value), "measured"
+        except ValueError:
+            pass
     return 6650.0, "fallback"
+
+
+def run_attention_benchmark(batches: list[int], context: int, q_heads: int, kv_heads: int, log: "Log") -> None:
+    """Times the decode attention kernel alone: one query token per batch row against a static
+    bf16 KV cache (the layout of fdk.llama), a CUDA graph of 20 launches replayed 10 times;
+    logs microseconds per launch, the rate at which keys and values are read and the largest
+    deviation from torch's scaled_dot_product_attention on the same inputs."""
+    from . import native
+
+    device = torch.device("cuda")
+    peak, peak_kind = hbm_peak_gbs()
+    for batch in batches:
+        max_len = context + 129
+        splits = max(1, min(max_len // 128, 148 // (batch * kv_heads), 16))  # as fdk.llama picks
+        k_cache = torch.randn((batch, kv_heads, max_len, 128), device=device).bfloat16()
+        v_cache = torch.randn((batch, kv_heads, max_len, 128), device=device).bfloat16()
+        q = torch.randn((batch, q_heads * 128), device=device).bfloat16()
+        out = torch.empty_like(q)
+        pos = torch.tensor(context, device=device)
+        scratch, counters = native.attention_scratch(batch, q_heads, kv_heads, splits, device)
+        call = lambda _: native.decode_attention(q, k_cache, v_cache, pos, out, scratch, counters, q_heads, kv_heads, splits)
+        time_s, stderr_s = measure_time(call, inner_reps=20, outer_reps=10)
+        kv_bytes = batch * kv_heads * (context + 1) * 128 * 2 * 2
+        ref = torch.nn.functional.scaled_dot_product_attention(
+            q.view(batch, q_heads, 1, 128), k_cache[:, :, : context + 1], v_cache[:, :, : context + 1], enable_gqa=True
+        ).view(batch, -1)
+        err = (out.float() - ref.float()).abs().max().item()
+        print(f"attention batch {batch:3d} context {context} slices {splits:2d}: {time_s * 1e6:7.2f} us  "
+              f"{kv_bytes / time_s / 1e9:7.1f} GB/s  max error {err:.2e}", file=sys.stderr)
+        log(dict(test="decode_attention", batch=batch, context=context, q_heads=q_heads, kv_heads=kv_heads, slices=splits,
+                 avg_time=time_s, avg_time_stderr=stderr_s, kv_bytes=kv_bytes, kv_gbs=kv_bytes / time_s / 1e9,
+                 hbm_peak_gbs=peak, hbm_peak_kind=peak_kind, max_abs_error=err))
+        del k_cache, v_cache
 
 
 def run_benchmarks(settings: Settings, only: str, include: str, exclude: str, log: Log) -> None:
@@ -362,7 +419,16 @@ def _main() -> None:
     parser.add_argument("--profile", default="", help="Select a specific method to profile (skip tests)")
     parser.add_argument("--include", default="", help="Methods to include (regex)")
     parser.add_argument("--exclude", default="_ref", help="Methods to exclude (regex)")
+    parser.add_argument("--attention", action="store_true",
+                        help="Time the decode attention kernel instead (batch sizes from -m, see --context, --heads)")
+    parser.add_argument("--context", default=1024, type=int, help="--attention: positions in the KV cache")
+    parser.add_argument("--heads", default=[24, 8], type=int, nargs=2, help="--attention: query heads, KV heads")
     args = parser.parse_args()
+
+    if args.attention:
+        with Log("py") as log:
+            run_attention_benchmark(args.m, args.context, args.heads[0], args.heads[1], log)
+        return
 
     if args.profile == "":
         run_tests()

@@ -9,9 +9,10 @@ libfdk_b200 on a tiled copy of the packed weights built once per module.
 Kernel selectors (QuantisationConfig.kernel):
   "triton"         native fused kernel (name kept so existing configs keep working); bf16
   "torch.compile"  the torch reference, dequantise then matmul (eager here)
-  "marlin", "marlin-lut"  the reference's fp16 4-bit selectors (models.py:107-125): same
-                   numbers (scale = absmax / 7, codes = round(w / s) + 8 clamped, values
-                   arange(-8, 8)), run by the same native kernel in its fp16 instantiation.
+  "marlin", "marlin-lut"  the reference's fp16 4-bit selectors (models.py:107-125): quantise()
+                   returns an `fdk.marlin.Layer` holding Marlin-format tensors (scale = absmax / 7,
+                   codes = round(w / s) + 8 clamped, values arange(-8, 8)); its product runs on
+                   the same native kernel in its fp16 instantiation.
 """
 
 from __future__ import annotations
@@ -25,7 +26,7 @@ from typing import Iterable, Literal
 import torch
 from torch import Tensor, nn
 
-from . import kernels, native
+from . import kernels, marlin, native
 
 # Quantised models
 
@@ -190,6 +191,26 @@ class QuantisedLinear(nn.Module):
         return cls(*weight.T.shape, _pack_codes(codes, 4), scale, table, kernel=c.kernel)
 
 
+def _create_marlin_layer(weight: Tensor, c: QuantisationConfig) -> nn.Module:
+    """The reference's Marlin selectors (models.py:107-125): an `fdk.marlin.Layer` packed from the
+    fp16 weight, with the linear grid as lookup table for the "marlin-lut" variant too."""
+    assert c.bits == 4, "Marlin backend only supports 4-bit quantisation"
+    assert c.block_size in (64, 128), "Marlin backend requires block_size 64 or 128"
+    assert weight.dtype == torch.half, "Marlin backend requires float16 weights"
+    out_features, in_features = weight.shape
+    layer = marlin.Layer(in_features, out_features, groupsize=c.block_size,
+                         is_linear={"marlin": True, "marlin-lut": False}[c.kernel]).to(weight.device)
+    if not layer.is_linear:
+        centroids = torch.arange(-8, 8, dtype=torch.half, device=weight.device)
+        layer.centroids[...] = torch.cartesian_prod(centroids, centroids).flip(1)
+    scale = weight.unflatten(-1, (-1, c.block_size)).abs().amax(dim=-1) / 7
+    scale.clamp_min_(1e-12)
+    source = nn.Linear(in_features, out_features, bias=False, device="meta")
+    source.weight = nn.Parameter(weight, requires_grad=False)
+    layer.pack(source, scale)
+    return layer
+
+
 def quantise(
     source: nn.Module,
     config: QuantisationConfig | None,
@@ -212,7 +233,7 @@ def quantise(
         assert source.in_features % 64 == 0, f"in_features must be multiple of 64, got {source.in_features}"
         weight = source.weight.data.to(device, dtype)
         if config.kernel.startswith("marlin"):
-            module: nn.Module = QuantisedLinear.create_marlin(weight, config)
+            module: nn.Module = _create_marlin_layer(weight, config)
         else:
             module = QuantisedLinear.create(weight, config, lut=lut)
     else:
@@ -242,6 +263,8 @@ def count_ops(model: nn.Module) -> int:
     for module in model.modules():
         if isinstance(module, QuantisedLinear):
             ops += 2 * module.in_features * module.out_features
+        elif isinstance(module, marlin.Layer):
+            ops += 2 * module.k * module.n
         else:
             ops += sum(2 * p.numel() for p in module.parameters(recurse=False))
     return ops
@@ -252,9 +275,12 @@ def count_parameter_read_bytes(model: nn.Module) -> int:
     table is a buffer and is not counted."""
     bytes_r = 0
     for module in model.modules():
-        if isinstance(module, nn.Embedding):
+        if isinstance(module, marlin.Layer):  # elements and scales only, like QuantisedLinear
+            bytes_r += sum(b.numel() * b.element_size() for b in (module.B, module.s))
+        elif isinstance(module, nn.Embedding):
             continue
-        bytes_r += sum(p.numel() * p.element_size() for p in module.parameters(recurse=False))
+        else:
+            bytes_r += sum(p.numel() * p.element_size() for p in module.parameters(recurse=False))
     return bytes_r
 
 
@@ -408,10 +434,146 @@ def benchmark(model: nn.Module, batch_size: int, reps: int, context: int = 2, se
     )
 
 
+def _estimate_fits_on_device(settings: BenchmarkSettings, device: torch.device, dtype: torch.dtype) -> bool:
+    """The reference's pre-check (models.py:438-453): parameters from the model name's size
+    suffix times bytes per parameter against 80 % of the device memory."""
+    _, total_mem_bytes = torch.cuda.mem_get_info(device.index)
+    if m := re.search(r"(\d[0-9.]*)[bB]$", settings.model):
+        bytes_per_param = (
+            dtype.itemsize
+            if settings.quantisation is None
+            else settings.quantisation.bits / 8 + dtype.itemsize / settings.quantisation.block_size
+        )
+        if settings.quantisation is not None and settings.quantisation.kernel != "torch.compile":
+            bytes_per_param *= 2  # the packed tensors and their tiled copy
+        return float(m[1]) * 1e9 * bytes_per_param / max(settings.tp, 1) < total_mem_bytes * 0.8
+    print(f"No size for model {settings.model} - assuming it fits", file=sys.stderr)
+    return True
+
+
+def load_host_model(model_name: str):
+    """transformers model in fp32 on the host, as the reference loads it (models.py:461-473):
+    custom-llama-* from its config (random weights), anything else from a local Hugging Face
+    checkpoint.  The tokenizer is attached when it can be had without a download."""
+    import transformers
+
+    if model_name.startswith("custom-llama-"):
+        model = transformers.AutoModelForCausalLM.from_config(
+            get_custom_llama_config(model_name.replace("custom-llama-", "")), dtype=torch.float32
+        )
+        tokenizer_name = "meta-llama/Llama-3.2-3B"
+    else:
+        model = transformers.AutoModelForCausalLM.from_pretrained(model_name, dtype=torch.float32)
+        tokenizer_name = model_name
+    try:
+        model.tokenizer = transformers.AutoTokenizer.from_pretrained(tokenizer_name, local_files_only=True)
+    except Exception:
+        model.tokenizer = None  # gated or absent: the benchmark then uses random token ids
+    return model
+
+
+def build_decoder(model_name: str, config: QuantisationConfig | None, device: torch.device, tp, lut: Tensor | None = None):
+    """The native decode loop for `model_name`: custom-llama-* shapes are created shard by shard on
+    the device (a 31B fp32 host model would need 125 GB of host memory); any other name is loaded
+    with load_host_model and its weights handed to the decoder."""
+    from . import llama
+
+    if model_name.startswith("custom-llama-"):
+        return llama.LlamaDecoder.random_init(resolve_model_dims(model_name), config, device, tp, lut=lut)
+    host = load_host_model(model_name)
+    assert type(host).__name__ == "LlamaForCausalLM", f"the native decode loop takes Llama models, got {type(host).__name__}"
+    return llama.LlamaDecoder.from_hf(host, config, device, tp, lut=lut)
+
+
+def kmeans_like_codebook(bits: int, seed: int = 0) -> Tensor:
+    """Sorted 2^bits centroids of N(0,1) samples (a few Lloyd iterations): stands in for the trained
+    codebooks of the paper's checkpoints (`--lut kmeans`)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(20000, generator=g).sort().values
+    c = torch.quantile(x, (torch.arange(2**bits) + 0.5) / 2**bits)
+    for _ in range(8):
+        idx = torch.bucketize(x, (c[1:] + c[:-1]) / 2)
+        c = torch.stack([x[idx == i].mean() if (idx == i).any() else c[i] for i in range(2**bits)])
+    return c.sort().values.bfloat16()
+
+
+def load_kmeans_state_dict(module: nn.Module, state: dict, prefix: str = "") -> list[str]:
+    """Loads externally trained quantised layers -- per layer a triple `weight_data` (packed codes
+    as QuantisedLinear stores them), `scale` and `lut` (either the [256, 8 / bits] byte table or the
+    plain 2^bits codebook, which is expanded) -- into the QuantisedLinear layers of `module`
+    (e.g. the result of quantise() on the architecture), and everything else as load_state_dict
+    would.  Returns the names of the quantised layers that were filled."""
+    filled = []
+    for name, layer in module.named_modules():
+        if not isinstance(layer, QuantisedLinear):
+            continue
+        key = f"{prefix}{name}." if name else prefix
+        if key + "weight_data" not in state:
+            continue
+        lut = state[key + "lut"]
+        bits = layer.bits
+        if lut.ndim == 1:  # plain codebook -> byte table
+            assert lut.shape[0] == 2**bits, f"{name}: codebook of {lut.shape[0]} entries for {bits}-bit codes"
+            lut = torch.cartesian_prod(*([lut] * (8 // bits))).view(256, -1) if 8 % bits == 0 else lut.reshape(-1, 1)
+        data, scale = state[key + "weight_data"], state[key + "scale"]
+        assert data.shape == layer.weight_data.shape and data.dtype == torch.uint8, f"{name}: weight_data {tuple(data.shape)}"
+        assert scale.shape == layer.scale.shape, f"{name}: scale {tuple(scale.shape)}"
+        with torch.no_grad():
+            layer.weight_data.copy_(data)
+            layer.scale.copy_(scale.to(layer.scale.dtype))
+            layer.lut.copy_(lut.to(layer.lut.dtype))
+        filled.append(name)
+    rest = {k: v for k, v in state.items() if not any(k.startswith(f"{prefix}{n}.") for n in filled)}
+    module.load_state_dict(rest, strict=False)
+    return filled
+
+
 def resolve_model_dims(name: str) -> LlamaDims:
     """'custom-llama-4B' (reference shapes) or 'custom-llama-b200-4B' (the B200 measurement shapes)."""
     assert name.startswith("custom-llama-"), f"only custom-llama-* models are built offline, got {name}"
     return get_custom_llama_dims(name.replace("custom-llama-", ""))
+
+
+def run_benchmark(settings: BenchmarkSettings, device: torch.device, tp, log, lut_kind: str = "linear") -> None:
+    """One model x batch x quantisation setting, as the reference's run_benchmark (models.py:476-516):
+    memory released first, a pre-check that the model fits, the result (or the error) logged."""
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    config = settings.quantisation
+    dtype = torch.float16 if config is not None and config.kernel.startswith("marlin") else torch.bfloat16
+    out = dict(**settings.__dict__)
+    if config is not None:
+        out.update(config.__dict__)
+    del out["quantisation"]
+    model = None
+    try:
+        if not _estimate_fits_on_device(settings, device, dtype):
+            raise RuntimeError(f"Model {settings.model} is too large for device")
+        if dtype == torch.float16:
+            raise RuntimeError("the decode loop is bf16; the fp16 Marlin selectors run at layer level (fdk.bench, quantise())")
+        lut = None
+        if config is not None and lut_kind == "kmeans":
+            lut = kmeans_like_codebook(config.bits).to(device)
+        model = build_decoder(settings.model, config, device, tp, lut=lut)
+        result = benchmark(model, settings.batch_size, settings.reps, settings.context)
+        out.update(result.__dict__)
+        if tp.rank == 0:
+            print(f"{str(settings):>60}:  {result}", file=sys.stderr)
+        if getattr(model, "exchange", None) is not None:
+            out.update(tp_reduce="fused", exchange_status=native.tp_exchange_status(model.exchange))
+    except Exception as e:  # as the reference: log and carry on
+        out.update(error=repr(e))
+        if tp.rank == 0:
+            print(f"{str(settings):>60}:  ERROR {e}", file=sys.stderr)
+    finally:
+        if model is not None:
+            model.close()
+            del model
+    torch.cuda.empty_cache()
+    if log is not None:
+        log(out)
 
 
 def _main() -> None:
@@ -424,15 +586,21 @@ def _main() -> None:
 
     parser = argparse.ArgumentParser()
     parser.add_argument("--model", default=["custom-llama-4B"], nargs="+",
-                        help=f"custom-llama-<size>, sizes {list(custom_llama_configs) + list(b200_llama_configs)}")
+                        help=f"custom-llama-<size> (sizes {list(custom_llama_configs) + list(b200_llama_configs)}) "
+                             "or a local Hugging Face Llama checkpoint")
     parser.add_argument("--batch-size", default=[1], type=int, nargs="+", help="Generation batch sizes")
     parser.add_argument("--bits", default=[16, 4, 1], type=int, nargs="+", help="Quantisation bit widths")
     parser.add_argument("--skip", default="^lm_head$", help="Regex of parameters to skip during quantisation")
     parser.add_argument("--block-size", default=[64], type=int, nargs="+", help="Quantisation block sizes")
     parser.add_argument("--kernel", default=["triton"], choices=["triton", "torch.compile", "marlin", "marlin-lut"],
                         nargs="+", help="Kernel implementation(s) (ignored for 16-bit)")
-    parser.add_argument("--reps", type=int, default=100, help="Number of generation steps to measure")
+    parser.add_argument("--reps", "--gen-tokens", dest="reps", type=int, default=100,
+                        help="Number of generation steps (generated tokens) to measure")
     parser.add_argument("--context", type=int, default=2, help="Tokens already in the KV cache")
+    parser.add_argument("--lut", default="linear", choices=["linear", "kmeans"],
+                        help="Codebook: the reference's default linspace grid, or sorted k-means-like centroids of N(0,1)")
+    parser.add_argument("--tp", type=int, default=None,
+                        help="Tensor-parallel ranks; must equal the number of processes torchrun started")
     parser.add_argument("--tp-reduce", default="fused", choices=["fused", "nccl"],
                         help="Under torchrun: how the row-parallel projections' partial sums are added "
                              "(fused = pushed from the kernel over NVLink, batches up to 16; else NCCL)")
@@ -441,6 +609,9 @@ def _main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.tp is not None and args.tp != world:
+        raise SystemExit(f"--tp {args.tp}: start {args.tp} processes, e.g. python -m torch.distributed.run "
+                         f"--nproc-per-node {args.tp} --master-addr 127.0.0.1 -m fdk.models ... (found {world})")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
@@ -449,33 +620,10 @@ def _main() -> None:
 
     log = bench.Log("models") if rank == 0 else None
     for name in args.model:
-        dims = resolve_model_dims(name)
         for batch_size in args.batch_size:
             for config in _quantisation_configs(args.bits, args.block_size, args.kernel, args.skip):
-                if config is not None and config.kernel.startswith("marlin"):
-                    continue  # fp16 selectors are exercised at layer level, the decode loop is bf16
-                settings = BenchmarkSettings(name, batch_size, config, args.reps, args.context, world)
-                out = dict(**settings.__dict__)
-                if config is not None:
-                    out.update(config.__dict__)
-                del out["quantisation"]
-                try:
-                    model = llama.LlamaDecoder.random_init(dims, config, device, tp)
-                    result = benchmark(model, batch_size, args.reps, args.context)
-                    out.update(result.__dict__)
-                    if rank == 0:
-                        print(f"{str(settings):>60}:  {result}", file=sys.stderr)
-                    if getattr(model, "exchange", None) is not None:
-                        out.update(tp_reduce="fused", exchange_status=native.tp_exchange_status(model.exchange))
-                    model.close()
-                    del model
-                except Exception as e:  # as the reference: log and carry on
-                    out.update(error=repr(e))
-                    if rank == 0:
-                        print(f"{str(settings):>60}:  ERROR {e}", file=sys.stderr)
-                torch.cuda.empty_cache()
-                if log is not None:
-                    log(out)
+                run_benchmark(BenchmarkSettings(name, batch_size, config, args.reps, args.context, world), device, tp, log,
+                              lut_kind=args.lut)
     if world > 1:
         # captured graphs that hold collectives must be gone before the communicator is
         import gc

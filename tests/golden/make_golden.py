@@ -150,6 +150,37 @@ def main(ref_root: str) -> None:
             dtype=np.int64,
         )
     np.savez_compressed(HERE / "llama_configs.npz", **out)
+
+    # ---- 6. Marlin packing: the reference's own Layer.pack on CPU ----
+    # The reference module builds its CUDA extension when it is imported; the build is replaced
+    # by a dummy so that the pure-Python packing code can run here.
+    import importlib.util
+
+    import torch.utils.cpp_extension as cpp_extension
+
+    real_load = cpp_extension.load
+    cpp_extension.load = lambda *a, **kw: types.SimpleNamespace()
+    try:
+        spec = importlib.util.spec_from_file_location("ref_marlin", Path(ref_root) / "src" / "fdk" / "marlin" / "__init__.py")
+        ref_marlin = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref_marlin)
+    finally:
+        cpp_extension.load = real_load
+    out = {}
+    for name, (k, n, groupsize, is_linear) in {
+        "g64_linear": (256, 256, 64, True), "g128_lut": (256, 512, 128, False), "single_linear": (128, 256, -1, True),
+    }.items():
+        torch.manual_seed(len(name))
+        linear = torch.nn.Linear(k, n, bias=False, dtype=torch.half)
+        g = k if groupsize == -1 else groupsize
+        scale = (linear.weight.data.unflatten(-1, (-1, g)).abs().amax(dim=-1) / 7).clamp_min_(1e-12)
+        layer = ref_marlin.Layer(k, n, groupsize=groupsize, is_linear=is_linear)
+        layer.pack(linear, scale)
+        out[name + "_weight"] = bits_of(linear.weight.data)
+        out[name + "_scale"] = bits_of(scale)
+        out[name + "_B"] = layer.B.numpy().copy()
+        out[name + "_s"] = bits_of(layer.s)
+    np.savez_compressed(HERE / "marlin_pack.npz", **out)
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 
