@@ -291,6 +291,62 @@ class LlamaDecoder(nn.Module):
         self.position.fill_(context)
         self.host_position = context
 
+    # ---- prefill -----------------------------------------------------------------------
+
+    def prefill(self, ids: Tensor) -> Tensor:
+        """ids [batch, T] at positions 0 .. T - 1 of freshly allocated caches -> logits of the last
+        position [batch, vocab]; fills the KV caches and leaves the position at T.  One pass over
+        the whole prompt, as the reference's Generator does with transformers' model
+        (src/fdk/models.py:241-243): the projections run the fused kernels on [batch * T, K]
+        (the tensor-core kernel from 9 rows on), the norms the RMSNorm kernel; rotary embedding and
+        causal attention over the prompt are torch ops (this path runs once per sequence)."""
+        dims, eps = self.dims, self.dims.rms_norm_eps
+        batch, t = ids.shape
+        assert batch == self.batch and t <= self.max_len, f"prompt {tuple(ids.shape)} for caches of {self.batch} x {self.max_len}"
+        dev = ids.device
+        rows = batch * t
+        hidden = self.embed.weight[ids.reshape(-1)].contiguous()  # [rows, hidden]
+        normed = torch.empty_like(hidden)
+        unpair = torch.argsort(torch.tensor(ROPE_ROW_ORDER, device=dev))  # paired row order -> dimensions 0 .. 127
+        inv_freq = 1.0 / (dims.rope_theta ** (torch.arange(0, 128, 2, dtype=torch.float32, device=dev) / 128))
+        angles = torch.arange(t, dtype=torch.float32, device=dev)[:, None] * inv_freq[None, :]
+        emb = torch.cat((angles, angles), dim=-1)
+        cos, sin = emb.cos().bfloat16()[None, :, None, :], emb.sin().bfloat16()[None, :, None, :]  # [1, T, 1, 128]
+
+        def rotate(x):  # [batch, T, heads, 128], transformers' rotate-half form
+            return x * cos + torch.cat((-x[..., 64:], x[..., :64]), dim=-1) * sin
+
+        delta = None
+        for i, layer in enumerate(self.layers):
+            native.rmsnorm(hidden, delta, layer.input_norm, normed, eps)
+            qkv = layer.qkv(normed).view(batch, t, self.q_heads + 2 * self.kv_heads, 128)
+            q = rotate(qkv[:, :, : self.q_heads][..., unpair])
+            k = rotate(qkv[:, :, self.q_heads: self.q_heads + self.kv_heads][..., unpair])
+            v = qkv[:, :, self.q_heads + self.kv_heads:]
+            self.k_cache[i][:, :, :t] = k.transpose(1, 2)
+            self.v_cache[i][:, :, :t] = v.transpose(1, 2)
+            attn = nn.functional.scaled_dot_product_attention(
+                q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True
+            ).transpose(1, 2).reshape(rows, self.q_heads * 128).contiguous()
+            delta = layer.o(attn)
+            self.tp.all_reduce(delta)
+            native.rmsnorm(hidden, delta, layer.post_norm, normed, eps)
+            if isinstance(layer.gate_up, QuantisedLinear):
+                act = torch.empty((rows, layer.gate_up.out_features // 2), device=dev, dtype=torch.bfloat16)
+                layer.gate_up.forward_silu_pairs(normed, act)
+            else:
+                act = torch.empty((rows, layer.gate_up.out_features // 2), device=dev, dtype=torch.bfloat16)
+                native.silu_mul(layer.gate_up(normed), act, group=PAIR_GROUP)
+            delta = layer.down(act)
+            self.tp.all_reduce(delta)
+        last = hidden.view(batch, t, -1)[:, -1].contiguous()
+        last_delta = delta.view(batch, t, -1)[:, -1].contiguous()
+        native.rmsnorm(last, last_delta, self.final_norm, self.normed, eps)
+        self.hidden.copy_(last)
+        self.position.fill_(t)
+        self.host_position = t
+        return self._logits()
+
     # ---- one decode step --------------------------------------------------------------
 
     def forward(self, tokens: Tensor) -> Tensor:
@@ -382,7 +438,7 @@ class LlamaDecoder(nn.Module):
 
 class Generator:
     """Greedy decoding with the reference Generator's interface (src/fdk/models.py:225-259):
-    construct with a prompt (prefilled token by token through the decode step), call step() per
+    construct with a prompt (prefilled in one pass, LlamaDecoder.prefill), call step() per
     generated token, read `tokens`.  step() is capturable in a CUDA graph."""
 
     def __init__(self, model: LlamaDecoder, prompt_ids: Tensor, steps: int, synthetic_context: int | None = None) -> None:
@@ -396,9 +452,12 @@ class Generator:
         with torch.no_grad():
             if synthetic_context is None:
                 self.input_ids[:, :prompt_n] = prompt_ids
-                logits = None
-                for t in range(prompt_n):
-                    logits = model(self.input_ids[:, t].contiguous())
+                if prompt_n > 1 and model.exchange is None:
+                    logits = model.prefill(prompt_ids)  # the whole prompt in one pass
+                else:
+                    logits = None
+                    for t in range(prompt_n):
+                        logits = model(self.input_ids[:, t].contiguous())
             else:  # keys and values of a made-up context; only the last prompt token is run
                 self.input_ids[:, context - 1] = prompt_ids[:, -1]
                 model.fill_cache_synthetic(context - 1)

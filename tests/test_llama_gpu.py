@@ -115,3 +115,32 @@ def test_lm_head_is_quantised_when_the_skip_pattern_does_not_match_it():
     want = kernels.mm_lut_ref(model.normed, head.weight_data, head.lut, head.scale)
     err = (logits.float() - want.float()).pow(2).sum().div(want.float().pow(2).sum()).sqrt().item()
     assert err < 1e-2, err
+
+
+@pytest.mark.parametrize("bits", [4])
+def test_prefill_equals_token_by_token_decode(bits):
+    """The one-pass prefill (projections on [batch * T, K], causal attention over the prompt) leaves
+    the caches and the logits of the last position as T decode steps do, up to the kernels'
+    different summation orders; and decoding goes on from there."""
+    from fdk import llama, models
+
+    device = torch.device("cuda")
+    dims = models.LlamaDims("tiny", 512, 2, 8, 2, 1024, vocab_size=640)
+    model = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(bits, 64), device, seed=9, std=0.05)
+    batch, t = 3, 21
+    ids = torch.randint(0, 640, (batch, t + 1), generator=torch.Generator().manual_seed(4)).to(device)
+    with torch.no_grad():
+        model.allocate(batch, t + 4)
+        for step in range(t):
+            stepwise = model(ids[:, step].contiguous()).float()
+        after_stepwise = model(ids[:, t].contiguous()).float()
+        k_stepwise = [c[:, :, :t].clone() for c in model.k_cache]
+        model.allocate(batch, t + 4)
+        once = model.prefill(ids[:, :t]).float()
+        after_once = model(ids[:, t].contiguous()).float()
+    torch.cuda.synchronize()
+    rel = lambda a, b: (a - b).pow(2).sum().div(b.pow(2).sum()).sqrt().item()
+    assert rel(once, stepwise) < 3e-2
+    assert rel(after_once, after_stepwise) < 3e-2
+    for a, b in zip(model.k_cache, k_stepwise):
+        assert rel(a[:, :, :t].float(), b.float()) < 3e-2
