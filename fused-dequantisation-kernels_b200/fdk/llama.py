@@ -230,10 +230,14 @@ class LlamaDecoder(nn.Module):
             for l in self.layers for m in (l.qkv, l.o, l.gate_up, l.down)
         )
         self.fusions = None
-        if native_layers and self.tp.size == 1 and batch <= 16 and batch * (2 * h + 16) <= 64 * 1024 and h % 64 == 0:
-            self.sumsq = torch.zeros((batch, h // 64), device=dev, dtype=torch.float32)
+        self.rope_fusions = None
+        if native_layers and batch <= 16:
             self.rope_tab = torch.zeros(64, device=dev, dtype=torch.int32)
-            self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
+            self.sumsq = torch.zeros((batch, h // 64), device=dev, dtype=torch.float32)
+            if self.tp.size == 1 and batch * (2 * h + 16) <= 64 * 1024 and h % 64 == 0:
+                self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
+            else:  # tensor parallel: the norms add the ranks' partial sums; the rotary epilogue still applies
+                self.rope_fusions = [self._layer_fusions(i, rope_only=True) for i in range(len(self.layers))]
         # fused push + reduce instead of NCCL: quantised row-parallel projections, batch <= 16
         self.close()
         can_push = all(
@@ -242,9 +246,14 @@ class LlamaDecoder(nn.Module):
         if self.tp.size > 1 and self.tp.fused and batch <= 16 and can_push and h % 64 == 0:
             self.exchange = self.tp.open_exchange(16 * h, dev)
 
-    def _layer_fusions(self, i: int):
-        """The four fusion descriptors of layer i (pointers into this decoder's buffers)."""
+    def _layer_fusions(self, i: int, rope_only: bool = False):
+        """The fusion descriptors of layer i (pointers into this decoder's buffers)."""
         layer, eps = self.layers[i], self.dims.rms_norm_eps
+        if rope_only:
+            return native.LinearFusion(
+                rope_pos=self.position.data_ptr(), rope_table=self.rope_tab.data_ptr(), q_out=self.q.data_ptr(),
+                k_cache=self.k_cache[i].data_ptr(), v_cache=self.v_cache[i].data_ptr(), q_heads=self.q_heads,
+                kv_heads=self.kv_heads, max_len=self.max_len)
 
         def norm(weight: Tensor) -> dict:
             return dict(norm_h=self.hidden.data_ptr(), norm_weight=weight.data_ptr(), norm_sumsq=self.sumsq.data_ptr(),
@@ -415,14 +424,19 @@ class LlamaDecoder(nn.Module):
         """The same step with each row-parallel projection pushing its partial sums to all ranks
         and the following RMSNorm adding them: no collective launches."""
         dims, eps, ex = self.dims, self.dims.rms_norm_eps, self.exchange
+        if self.rope_fusions is not None:
+            native.rope_table(self.position, self.rope_tab, dims.rope_theta)
         for i, layer in enumerate(self.layers):
             if i == 0:
                 native.rmsnorm(self.hidden, None, layer.input_norm, self.normed, eps)
             else:
                 native.rmsnorm_reduce(self.hidden, ex, layer.input_norm, self.normed, eps)
-            qkv = layer.qkv(self.normed)
-            native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads, self.kv_heads,
-                               dims.rope_theta, paired=True)
+            if self.rope_fusions is not None:  # rotary embedding + KV append in the projection's epilogue
+                layer.qkv.fused(self.normed, None, self.batch, self.rope_fusions[i])
+            else:
+                qkv = layer.qkv(self.normed)
+                native.rope_append(qkv, self.position, self.q, self.k_cache[i], self.v_cache[i], self.q_heads,
+                                   self.kv_heads, dims.rope_theta, paired=True)
             native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
                                     self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
             layer.o.push(self.attn, ex)
