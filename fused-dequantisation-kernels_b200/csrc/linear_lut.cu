@@ -193,6 +193,19 @@ extern "C" int fdk_linear_lut_fused(const void* x, const void* tiled, const void
                          nullptr, fusion, stream);
 }
 
+extern "C" int fdk_linear_norm_fits(int m, int k, int bits, int* fits_host) {
+  FDK_CHECK_ARG(fits_host != nullptr, FDK_ERR_BAD_ARG, "fits_host is null");
+  *fits_host = 0;
+  if (m <= 0 || m > 16 || k <= 0 || k % kBlock != 0 || !bits_supported(bits)) return FDK_OK;
+  switch (bits) {
+    case 1: return norm_fits_bits<1>(m, k, fits_host);
+    case 2: return norm_fits_bits<2>(m, k, fits_host);
+    case 3: return norm_fits_bits<3>(m, k, fits_host);
+    case 4: return norm_fits_bits<4>(m, k, fits_host);
+    default: return norm_fits_bits<8>(m, k, fits_host);
+  }
+}
+
 extern "C" int fdk_linear_lut_push(const void* x, const void* tiled, const void* lut, const void* lut_host, int m,
                                    int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
                                    unsigned flags, const fdk_tp_exchange* ex, void* stream) {

@@ -179,17 +179,19 @@ __device__ __forceinline__ int cta_of(const LinearParams& p, int item) {
 
 // Owner of a split tile: adds the sums published by the CTAs after this one, up to the one
 // holding the tile's last slab, in CTA order, into stash[0, E).  Run by one warp, lane l taking
-// elements 4 l .. 4 l + 3 of every 128; the words of up to four CTAs are in flight together,
-// and a round that finds a stale tag is repeated after a short sleep.  Returns false if that
-// ran out.
+// elements 4 l .. 4 l + 3 of every 128.  Every trip to L2 fetches sixteen words per lane (more
+// for two n-tiles): four CTAs' words of one 128-element group where a tile has one group (small
+// batches: several CTAs may share a tile), otherwise one CTA's words of four (eight) groups, so
+// that the number of trips does not grow with the batch.  A round that finds a stale tag is
+// repeated after a short sleep.  Returns false if that ran out.
 template <int NB>
-__device__ __forceinline__ bool fetch_foreign(const LinearParams& p, float* stash, int rt, uint32_t tag, int E) {
+__device__ __noinline__ bool fetch_foreign(const LinearParams& p, float* stash, int rt, uint32_t tag, int E) {
   constexpr int EMAX = 512 * NB;
   const int lane = threadIdx.x & 31;
   const int last = cta_of(p, (rt + 1) * p.k_slabs - 1);
   bool ok = true;
-#pragma unroll 1
-  for (int e0 = lane * 4; e0 < E; e0 += 128) {
+  if (E <= 128) {
+    const int e0 = lane * 4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
     for (int cb0 = blockIdx.x + 1; cb0 <= last; cb0 += 4) {
@@ -219,6 +221,46 @@ __device__ __forceinline__ bool fetch_foreign(const LinearParams& p, float* stas
         for (int j = 0; j < 4; ++j) acc[j] += __uint_as_float(v[ci][j].x);  // CTA order
     }
     *reinterpret_cast<float4*>(stash + e0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    return ok;
+  }
+  constexpr int GROUPS = 4 * NB;  // 128-element groups fetched together
+#pragma unroll 1
+  for (int g0 = 0; g0 * 128 < E; g0 += GROUPS) {
+    float acc[GROUPS][4];
+#pragma unroll
+    for (int gi = 0; gi < GROUPS; ++gi) acc[gi][0] = acc[gi][1] = acc[gi][2] = acc[gi][3] = 0.f;
+#pragma unroll 1
+    for (int cb = blockIdx.x + 1; cb <= last; ++cb) {
+      uint2 v[GROUPS][4];
+      const uint2* src = p.partial + (size_t)cb * EMAX + g0 * 128 + lane * 4;
+      for (uint32_t round = 0;; ++round) {
+        bool fresh = true;
+#pragma unroll
+        for (int gi = 0; gi < GROUPS; ++gi)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            v[gi][j] = (g0 + gi) * 128 < E ? ld_relaxed_v2(src + gi * 128 + j) : make_uint2(0u, tag);
+#pragma unroll
+        for (int gi = 0; gi < GROUPS; ++gi)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) fresh = fresh && v[gi][j].y == tag;
+        if (__all_sync(0xffffffffu, fresh)) break;
+        if (round > (kSpinLimit >> 4)) {
+          ok = false;
+          break;
+        }
+        __nanosleep(64);
+      }
+#pragma unroll
+      for (int gi = 0; gi < GROUPS; ++gi)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[gi][j] += __uint_as_float(v[gi][j].x);  // CTA order
+    }
+#pragma unroll
+    for (int gi = 0; gi < GROUPS; ++gi)
+      if ((g0 + gi) * 128 < E)
+        *reinterpret_cast<float4*>(stash + (g0 + gi) * 128 + lane * 4) =
+            make_float4(acc[gi][0], acc[gi][1], acc[gi][2], acc[gi][3]);
   }
   return ok;
 }
@@ -227,10 +269,11 @@ __device__ __forceinline__ bool fetch_foreign(const LinearParams& p, float* stas
 // this row tile: per warp one block of E = NB * 4 * SW floats laid out
 // [sub-tile][n-tile][t][g][4].  `foreign`: stash holds the other CTAs' sums (owner of a split
 // tile).  `publish`: the sums go to `mine` in the workspace as tagged words and nothing else is done.
-template <int NB, int WARPS, bool FP16, int EPI>
-__device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots, const float* stash, uint2* mine,
-                                            bool foreign, bool publish, uint32_t tag, int rt, uint32_t push_seq,
-                                            const uint32_t (&hpre)[8 * NB], const uint8_t* smem_head) {
+template <int NB, bool FP16, int EPI>
+__device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots, int deposits, uint16_t* gathered,
+                                            const float* stash, uint2* mine, bool foreign, bool publish, uint32_t tag,
+                                            int rt, uint32_t push_seq, const uint32_t (&hpre)[8 * NB],
+                                            const uint8_t* smem_head) {
   const int lane = threadIdx.x & 31;
   const int tt = p.slot_t, sw = 32 * tt;
   const int E = NB * kSubTiles * sw;
@@ -244,14 +287,14 @@ __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots,
   for (int e0 = lane * 4; e0 < E; e0 += 128) {
     float4 even = make_float4(0.f, 0.f, 0.f, 0.f), odd = even;
 #pragma unroll 5
-    for (int w = 0; w + 1 < WARPS; w += 2) {
+    for (int w = 0; w + 1 < deposits; w += 2) {
       const float4 a = *reinterpret_cast<const float4*>(slots + w * E + e0);
       const float4 b = *reinterpret_cast<const float4*>(slots + (w + 1) * E + e0);
       even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
       odd.x += b.x; odd.y += b.y; odd.z += b.z; odd.w += b.w;
     }
-    if (WARPS & 1) {
-      const float4 a = *reinterpret_cast<const float4*>(slots + (WARPS - 1) * E + e0);
+    if (deposits & 1) {
+      const float4 a = *reinterpret_cast<const float4*>(slots + (deposits - 1) * E + e0);
       even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
     }
     float acc[4] = {even.x + odd.x, even.y + odd.y, even.z + odd.z, even.w + odd.w};
@@ -281,14 +324,13 @@ __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots,
   __syncwarp();
 
   // 2. write the outputs: element (blk, tq, lane) with blk = sub-tile * NB + n-tile.  In a
-  //    tensor-parallel push they are first gathered as bf16 in the slot block of warp 1 (summed
-  //    above, free now), [batch row][64 tile rows], then stored into this rank's slot of the
+  //    tensor-parallel push they are first gathered as bf16 in `gathered` (the slot block of warp
+  //    1, summed above and free now, or a block of its own), [batch row][64 tile rows], then stored into this rank's slot of the
   //    current half of every rank's exchange buffer (plain peer stores) as 8-byte words {two
   //    outputs, tag}: a word is valid once its tag is that of this push, so no fence, flag or
   //    second crossing of the link is needed.
   {
     const int g = lane >> 2, c = lane & 3;
-    uint16_t* gathered = reinterpret_cast<uint16_t*>(slots + E);
 #pragma unroll 1
     for (int blk = 0; blk < kSubTiles * NB; ++blk) {
       const int r = blk / NB, nb = blk - r * NB;
@@ -475,7 +517,17 @@ __device__ __forceinline__ bool wait_shared_word(volatile int* word, int want) {
 
 // WARPS compute warps and one finisher warp (the last one).
 // NORM: x is the RMSNorm of p.norm_h, applied while x is staged (needs XRES).
-template <int BITS, int NB, int WARPS, bool FP16, int EPI, bool XRES, bool NORM = false>
+// XM: where a warp finds x -- kXDirect: fragments read from L2 as they are needed; kXResident:
+// all of x copied once per CTA into shared memory; kXStreamed: every lane copies the fragments
+// of its warp's next slab into a two-stage ring of its own with cp.async while it works on the
+// current one (larger batches: the copy of x no longer stands before the loop).
+constexpr int kXDirect = 0, kXResident = 1, kXStreamed = 2;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM = false>
 __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
@@ -548,12 +600,12 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       if (lane == 0) *reinterpret_cast<long long*>(smem_raw + kSmemPos) = *reinterpret_cast<const volatile long long*>(p.rope_pos);
     }
   }
-  if constexpr (XRES && NORM) {
+  if constexpr (XM == kXResident && NORM) {
     // x = norm_w * round(h * rsqrt(mean(h^2) + eps)), the roundings of the separate RMSNorm
     // kernel; mean(h^2) from the sums of squares the previous projection left per 64 elements.
     // A thread's first two vectors of h and of the norm weight are requested before the
     // factors are computed, so that all of it costs one round trip to L2.
-    static_assert(!NORM || XRES, "the norm is applied while x is staged in shared memory");
+    static_assert(!NORM || XM == kXResident, "the norm is applied while x is staged in shared memory");
     const int vecs = p.k >> 3, total = p.m * vecs;
     float* inv_smem = reinterpret_cast<float*>(smem_raw + kSmemInv);
     uint4 hv[2], wv[2];
@@ -594,37 +646,70 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       const int i = threadIdx.x + u * kThreads;
       if (i < total) stage(i, hv[u], wv[u]);
     }
+    // the rest four vectors per thread at a time: their eight loads are in flight together
 #pragma unroll 1
-    for (int i = threadIdx.x + 2 * kThreads; i < total; i += kThreads)
-      stage(i, ldg_l2(p.norm_h + (size_t)i * 8), ldg_l2(p.norm_w + (size_t)(i % vecs) * 8));
-  } else if constexpr (XRES) {  // x fits: one copy per CTA
-    const int vecs = p.k >> 3;
+    for (int i0 = threadIdx.x + 2 * kThreads; i0 < total; i0 += 4 * kThreads) {
+      uint4 h4[4], w4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < total) {
+          h4[u] = ldg_l2(p.norm_h + (size_t)i * 8);
+          w4[u] = ldg_l2(p.norm_w + (size_t)(i % vecs) * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < total) stage(i, h4[u], w4[u]);
+      }
+    }
+  } else if constexpr (XM == kXResident) {
+    // x fits: one copy per CTA.  x is contiguous ([m, k]), so the copy runs over all of its
+    // 16-byte vectors at once, eight loads per thread in flight (one trip to L2 per eight
+    // vectors instead of one per batch row); a row of the copy is 16 bytes longer than k.
+    const int vecs = p.k >> 3, total = p.m * vecs;
+    constexpr int kStageBatch = 8;
+    int row = 0, c = threadIdx.x;
 #pragma unroll 1
-    for (int row = 0; row < p.m; ++row) {
-      const uint16_t* src = p.x + (size_t)row * p.k;
-      const uint32_t dst = xres_addr + row * p.xres_row;
-#pragma unroll 2
-      for (int c = threadIdx.x; c < vecs; c += kThreads) {
-        const uint4 xv = ldg_l2(src + c * 8);
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + c * 16), "r"(xv.x), "r"(xv.y), "r"(xv.z), "r"(xv.w)
-                     : "memory");
+    for (int i0 = threadIdx.x; i0 < total; i0 += kStageBatch * kThreads) {
+      uint4 xv[kStageBatch];
+#pragma unroll
+      for (int u = 0; u < kStageBatch; ++u)
+        if (i0 + u * kThreads < total) xv[u] = ldg_l2(p.x + (size_t)(i0 + u * kThreads) * 8);
+#pragma unroll
+      for (int u = 0; u < kStageBatch; ++u) {
+        while (c >= vecs) {
+          c -= vecs;
+          ++row;
+        }
+        if (i0 + u * kThreads < total)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xres_addr + row * p.xres_row + c * 16), "r"(xv[u].x),
+                       "r"(xv[u].y), "r"(xv[u].z), "r"(xv[u].w)
+                       : "memory");
+        c += kThreads;
       }
     }
   }
   __syncthreads();  // table, x and the epilogue's sync words are in place
 
   const int tt = p.slot_t, sw = 32 * tt;
-  const uint32_t slot_set_floats = W * kSubTiles * NB * sw;
+  const int E = NB * kSubTiles * sw;  // sums of one row tile
+  const uint32_t slot_set_floats = W * E;
+  // Team mode (large deposits): the compute warps add their deposits themselves, every warp a
+  // slice, into one of two blocks of E sums; the finisher starts from those.
+  const bool team = p.team != 0;
+  float* tsum = reinterpret_cast<float*>(smem_raw + p.tsum_off);
   bool timed_out = false;
 
   if (warp == W) {
     // ---- finisher ----
-    const int E = NB * kSubTiles * sw;
     float* stash = reinterpret_cast<float*>(smem_raw + p.stash_off);
     for (int rt = rt_first; rt <= rt_last; ++rt) {
       const int seg = rt - rt_first;
       const int set = p.slot_sets == 2 ? (seg & 1) : 0;
-      float* my_slots = slots + set * slot_set_floats;
+      float* my_slots = team ? tsum + set * E : slots + set * slot_set_floats;
+      uint16_t* gathered = reinterpret_cast<uint16_t*>(team ? tsum + 2 * E : my_slots + E);
       const int seg_lo = rt * p.k_slabs, seg_hi = seg_lo + p.k_slabs;
       const bool full = (c0 <= seg_lo) && (c1 >= seg_hi);
       const bool owner = (c0 <= seg_lo);  // holds the tile's first slab
@@ -650,8 +735,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       }
       if (!wait_shared_word(&esync->count[set], W)) timed_out = true;
       __threadfence_block();
-      tile_finish<NB, WARPS, FP16, EPI>(p, my_slots, stash, p.partial + (size_t)cta * (512 * NB), !full && owner,
-                                        !full && !owner, tag, rt, push_seq, hpre, smem_raw);
+      tile_finish<NB, FP16, EPI>(p, my_slots, team ? 1 : W, gathered, stash, p.partial + (size_t)cta * (512 * NB),
+                                 !full && owner, !full && !owner, tag, rt, push_seq, hpre, smem_raw);
       __syncwarp();
       if (lane == 0) {
         if (!full && owner) p.counters[rt] = (uses + 1) & 0x7FFFF;  // this use of the split tile is done
@@ -687,16 +772,59 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       float* my_slots = slots + set * slot_set_floats;
       // the slot set is free once the finisher has summed the tile that used it before
       if (!wait_shared_word(&esync->gen[set], turn)) timed_out = true;
+      if (team) {
+        // one block of deposits, filled and added up in `slot_phases` parts of the tile's four
+        // sub-tiles (fewer sub-tiles at a time where shared memory is short); the adding follows
+        // the finisher's order, so the sums do not depend on the mode
+        const int rshift = p.slot_phases == 1 ? 2 : p.slot_phases == 2 ? 1 : 0, rpp = 1 << rshift;
+        const int Eph = rpp * NB * sw;
+        float* sums = tsum + set * E;
+#pragma unroll 1
+        for (int ph = 0; ph < (int)p.slot_phases; ++ph) {
 #pragma unroll
-      for (int r = 0; r < kSubTiles; ++r)
+          for (int r = 0; r < kSubTiles; ++r)
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-          if (t < tt) {
-            float4 dv = make_float4(tot[r][nb][0], tot[r][nb][1], tot[r][nb][2], tot[r][nb][3]);
-            *reinterpret_cast<float4*>(my_slots + ((warp * kSubTiles + r) * NB + nb) * sw + t * 32 + g * 4) = dv;
+            for (int nb = 0; nb < NB; ++nb)
+              if ((r >> rshift) == ph && t < tt) {
+                float4 dv = make_float4(tot[r][nb][0], tot[r][nb][1], tot[r][nb][2], tot[r][nb][3]);
+                *reinterpret_cast<float4*>(slots + ((warp * rpp + (r & (rpp - 1))) * NB + nb) * sw + t * 32 + g * 4) = dv;
+              }
+          asm volatile("bar.sync 1, %0;" ::"r"(W * 32) : "memory");
+#pragma unroll 1
+          for (int e0 = 4 * (warp * 32 + lane); e0 < Eph; e0 += 4 * W * 32) {
+            float4 even = make_float4(0.f, 0.f, 0.f, 0.f), odd = even;
+#pragma unroll 5
+            for (int w = 0; w + 1 < W; w += 2) {
+              const float4 a = *reinterpret_cast<const float4*>(slots + w * Eph + e0);
+              const float4 b = *reinterpret_cast<const float4*>(slots + (w + 1) * Eph + e0);
+              even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
+              odd.x += b.x; odd.y += b.y; odd.z += b.z; odd.w += b.w;
+            }
+            if (W & 1) {
+              const float4 a = *reinterpret_cast<const float4*>(slots + (W - 1) * Eph + e0);
+              even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
+            }
+            *reinterpret_cast<float4*>(sums + ph * Eph + e0) =
+                make_float4(even.x + odd.x, even.y + odd.y, even.z + odd.z, even.w + odd.w);
           }
-          tot[r][nb][0] = tot[r][nb][1] = tot[r][nb][2] = tot[r][nb][3] = 0.f;
+          asm volatile("bar.sync 1, %0;" ::"r"(W * 32) : "memory");
         }
+#pragma unroll
+        for (int r = 0; r < kSubTiles; ++r)
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) tot[r][nb][0] = tot[r][nb][1] = tot[r][nb][2] = tot[r][nb][3] = 0.f;
+      } else {
+#pragma unroll
+        for (int r = 0; r < kSubTiles; ++r)
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            if (t < tt) {
+              float4 dv = make_float4(tot[r][nb][0], tot[r][nb][1], tot[r][nb][2], tot[r][nb][3]);
+              *reinterpret_cast<float4*>(my_slots + ((warp * kSubTiles + r) * NB + nb) * sw + t * 32 + g * 4) = dv;
+            }
+            tot[r][nb][0] = tot[r][nb][1] = tot[r][nb][2] = tot[r][nb][3] = 0.f;
+          }
+      }
       __threadfence_block();
       __syncwarp();
       if (lane == 0) atomicAdd(&esync->count[set], 1);
@@ -714,8 +842,34 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     x_ptr[nb] = p.x + (size_t)b * p.k + t * 16;
   }
 
-  // Works on the slab held in `s`, at position `kpos` inside its row tile.
-  auto compute = [&](const SlabRegs<BITS>& s, int kpos) {
+  // streamed x: a lane's private ring, [stage][block][n-tile][half] vectors 512 bytes apart
+  constexpr uint32_t kRingStage = L::KSB * NB * 1024;
+  const uint32_t ring_lane = raw + p.xring_off + warp * (2 * kRingStage) + lane * 16;
+  auto issue_x = [&](int stage, int kpos) {  // the fragments of the slab at position kpos of its row tile
+#pragma unroll
+    for (int jb = 0; jb < L::KSB; ++jb) {
+      const int col = (kpos * L::KSB + jb) * kBlock;
+      if (L::KSB == 1 || col < p.k) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          // lanes of unused batch columns copy nothing: what they multiply is never stored
+          if (g + 8 * nb < p.m) {
+            const uint32_t dst = ring_lane + stage * kRingStage + (jb * NB + nb) * 1024;
+            cp_async16(dst, x_ptr[nb] + col);
+            cp_async16(dst + 512, x_ptr[nb] + col + 8);
+          }
+        }
+      }
+    }
+  };
+  if constexpr (XM == kXStreamed) {
+    if (it < c1) issue_x(0, ks);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  // Works on the slab held in `s`, at position `kpos` inside its row tile; `stage` is its half
+  // of the ring of x fragments.
+  auto compute = [&](const SlabRegs<BITS>& s, int kpos, int stage) {
     auto block = [&](auto jbc) {
       constexpr int JB = decltype(jbc)::value;
       const int col = (kpos * L::KSB + JB) * kBlock;
@@ -724,9 +878,12 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
         uint4 lo, hi;
-        if constexpr (XRES) {
+        if constexpr (XM == kXResident) {
           lo = ring128(x_lane[nb] + col * 2);
           hi = ring128(x_lane[nb] + col * 2 + 16);
+        } else if constexpr (XM == kXStreamed) {
+          lo = ring128(ring_lane + stage * kRingStage + (JB * NB + nb) * 1024);
+          hi = ring128(ring_lane + stage * kRingStage + (JB * NB + nb) * 1024 + 512);
         } else {
           lo = ldg_l2(x_ptr[nb] + col);
           hi = ldg_l2(x_ptr[nb] + col + 8);
@@ -769,12 +926,21 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
 
   // One step: start loading the warp's next slab into `nxt`, ask L2 for the one after it, work
   // on the slab in `cur`, move on.  Returns false when the warp has no slab left.
-  auto step = [&](const SlabRegs<BITS>& cur, SlabRegs<BITS>& nxt) {
+  auto step = [&](const SlabRegs<BITS>& cur, SlabRegs<BITS>& nxt, int stage) {
     if (it >= c1) return false;
     if (rt != cur_rt) flush_until(rt);
     if (it + W < c1) load_slab<BITS>(nxt, wp + kStep, lane);
+    if constexpr (XM == kXStreamed) {
+      if (it + W < c1) {
+        int ks_next = ks + W;  // where the warp's next slab sits in its row tile
+        while (ks_next >= p.k_slabs) ks_next -= p.k_slabs;
+        issue_x(stage ^ 1, ks_next);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the copies just issued: this slab's x is in
+    }
     if (it + 2 * W < c1) prefetch_slab_l2<BITS>(wp + 2 * (size_t)kStep, lane);
-    compute(cur, ks);
+    compute(cur, ks, stage);
     wp += kStep;
     it += W;
     ks += W;
@@ -785,7 +951,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     return true;
   };
   // two register sets, used alternately
-  while (step(s, s2) && step(s2, s)) {
+  while (step(s, s2, 0) && step(s2, s, 1)) {
   }
   flush_until(rt_last + 1);
   if (timed_out && lane == 0) atomicOr(p.counters + kStatusWord, kStatusTimeout);
@@ -798,47 +964,67 @@ inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 // Plans the shared-memory layout of one CTA as offsets from the start of its dynamic shared
 // memory, which kernels see at address `base` of the shared window:
 //   [sync words] ... [table, at a multiple of 64 KB of the window when it is the wide one] ...
-// with the reduction slots and (when it fits) x placed below the table if there is room, above
-// it otherwise.  Returns the dynamic size needed; `resident` tells whether x is staged.
+// with the reduction slots, the sums and x (all of it, or the ring of the streamed mode) placed
+// below the table where there is room, above it otherwise.  Chooses how the kernel finds x
+// (*xmode): the fused RMSNorm needs all of x in shared memory; otherwise x is streamed (measured
+// equal to or faster than the copy per CTA at every batch: no staging phase before the loop),
+// staged whole where the ring does not fit (1-bit and 3-bit slabs of 256 columns), and read
+// straight from L2 as the last resort.  Returns the dynamic size needed.
 template <int BITS, int NB>
-size_t plan_smem(uint32_t base, int warps, size_t limit, LinearParams& p, bool* resident) {
+size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, LinearParams& p, int* xmode) {
   constexpr bool WIDE = BITS != 3;
   using T = Table<BITS, WIDE>;
+  using L = Layout<BITS>;
   const uint32_t tt = ((p.m < 8 ? p.m : 8) + 1) / 2;
-  // two sets let a warp deposit its next row tile while the last one is being summed; large
-  // deposits (batches of five rows and more) get one set
-  const uint32_t sets = tt >= 3 ? 1 : 2;
-  p.slot_sets = sets;
-  p.slot_t = tt;
-  const uint32_t slot_bytes = align_up(sets * warps * kSubTiles * NB * 32 * tt * sizeof(float), 128);
+  const uint32_t e_bytes = NB * kSubTiles * 32 * tt * sizeof(float);  // the sums of one row tile
+  // large deposits (batches of five rows and more, or two n-tiles) are added up by the compute
+  // warps themselves; small ones by the finisher, from two slot sets used in turn
+  const bool team = tt >= 3 || NB == 2;
   const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
   const uint32_t xres_bytes = align_up((uint32_t)p.m * xres_row, 128);
+  const uint32_t ring_bytes = (uint32_t)warps * 2 * L::KSB * NB * 1024;
+  p.team = team ? 1 : 0;
+  p.slot_sets = 2;
+  p.slot_t = tt;
   p.xres_row = xres_row;
-  uint32_t low = kSmemHead;                                             // cursor below the table
-  const uint32_t table_off = WIDE ? align_up(base + low, 65536) - base : low;
-  uint32_t high = table_off + T::kBytes;                               // cursor above it
+  const uint32_t table_off = WIDE ? align_up(base + kSmemHead, 65536) - base : kSmemHead;
   p.table_off = table_off;
-  auto place = [&](uint32_t bytes) {
-    if (low + bytes <= table_off) {
-      const uint32_t at = low;
-      low += bytes;
+
+  // lays everything out for a number of deposit phases and an x mode; returns the size needed
+  auto layout = [&](uint32_t phases, int mode) -> size_t {
+    uint32_t low = kSmemHead, high = table_off + T::kBytes;  // cursors below and above the table
+    auto place = [&](uint32_t bytes) {
+      bytes = align_up(bytes, 128);
+      if (low + bytes <= table_off) {
+        const uint32_t at = low;
+        low += bytes;
+        return at;
+      }
+      const uint32_t at = high;
+      high += bytes;
       return at;
-    }
-    const uint32_t at = high;
-    high += bytes;
-    return at;
+    };
+    p.slot_phases = phases;
+    p.slots_off = place(team ? warps * e_bytes / phases : 2 * warps * e_bytes);
+    p.tsum_off = team ? place(3 * e_bytes) : 0;  // two blocks of sums used in turn + the gather block of the push
+    p.stash_off = place(e_bytes);
+    p.xres_off = mode == kXResident ? place(xres_bytes) : 0;
+    p.xring_off = mode == kXStreamed ? place(ring_bytes) : 0;
+    return high;
   };
-  p.slots_off = place(slot_bytes);
-  p.stash_off = place(NB * kSubTiles * 32 * tt * sizeof(float));
-  const uint32_t high_before = high, low_before = low;
-  p.xres_off = place(xres_bytes);
-  *resident = high <= limit;
-  if (!*resident) {
-    high = high_before;
-    low = low_before;
-    p.xres_off = 0;
+  const int order[3] = {need_resident ? kXResident : kXStreamed, need_resident ? kXStreamed : kXResident, kXDirect};
+  for (int mode : order) {
+    if (need_resident && mode != kXResident) break;
+    for (uint32_t phases = 1; phases <= (team ? 4u : 1u); phases *= 2) {
+      const size_t need = layout(phases, mode);
+      if (need <= limit) {
+        *xmode = mode;
+        return need;
+      }
+    }
   }
-  return high;
+  *xmode = -1;  // nothing fits (the fused RMSNorm on too large an x)
+  return layout(1, kXDirect);
 }
 
 // Sets the kernel's shared-memory limit once per device and launches it.
@@ -866,11 +1052,11 @@ int launch_kernel(Kernel kernel, std::atomic<size_t> (&configured)[64], const Li
   return FDK_OK;
 }
 
-template <int BITS, int NB, int WARPS, bool FP16, int EPI, bool XRES, bool NORM>
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM>
 int launch_instance(const LinearParams& p, const InlineLut<BITS>& inl, int grid, size_t smem, unsigned flags,
                     cudaStream_t stream) {
   static std::atomic<size_t> configured[64] = {};
-  return launch_kernel(linear_lut_kernel<BITS, NB, WARPS, FP16, EPI, XRES, NORM>, configured, p, inl, grid,
+  return launch_kernel(linear_lut_kernel<BITS, NB, WARPS, FP16, EPI, XM, NORM>, configured, p, inl, grid,
                        (WARPS + 1) * 32, smem, flags, stream);
 }
 
@@ -880,8 +1066,10 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
   if (int st = dynamic_smem_base(&base)) return st;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
-  bool xres = false;
-  const size_t smem = plan_smem<BITS, NB>(base, WARPS, (size_t)di.max_smem_optin, p, &xres);
+  const bool norm = p.norm_h != nullptr;
+  int xm = kXDirect;
+  const size_t smem = plan_smem<BITS, NB>(base, WARPS, (size_t)di.max_smem_optin, norm, p, &xm);
+  FDK_CHECK_ARG(xm >= 0, FDK_ERR_SHAPE, "the fused RMSNorm needs x [%d, %d] to fit in shared memory", p.m, p.k);
   FDK_CHECK_ARG(smem <= (size_t)di.max_smem_optin, FDK_ERR_CUDA, "shared-memory plan of %zu bytes exceeds %d", smem,
                 di.max_smem_optin);
   // one CTA per SM, fewer when there are fewer slabs than that
@@ -891,38 +1079,30 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
   p.rem = p.total % grid;
 
   const int epi = p.tp > 0 ? kEpiPush : p.silu ? kEpiSilu : p.resid_h != nullptr ? kEpiResid : p.rope_pos != nullptr ? kEpiRope : kEpiStore;
-  const bool norm = p.norm_h != nullptr;
-#define FDK_LAUNCH(EPI_, XRES_, NORM_) \
-  return launch_instance<BITS, NB, WARPS, FP16, EPI_, XRES_, NORM_>(p, inl, grid, smem, flags, stream)
+#define FDK_LAUNCH(EPI_, XM_, NORM_) \
+  return launch_instance<BITS, NB, WARPS, FP16, EPI_, XM_, NORM_>(p, inl, grid, smem, flags, stream)
+#define FDK_LAUNCH_X(EPI_)                                 \
+  do {                                                     \
+    if (xm == kXResident) FDK_LAUNCH(EPI_, kXResident, false); \
+    if (xm == kXStreamed) FDK_LAUNCH(EPI_, kXStreamed, false); \
+    FDK_LAUNCH(EPI_, kXDirect, false);                     \
+  } while (0)
   if constexpr (!FP16) {  // the decode fusions exist for bf16 only
     if (norm) {
-      FDK_CHECK_ARG(xres, FDK_ERR_SHAPE, "the fused RMSNorm needs x [%d, %d] to fit in shared memory", p.m, p.k);
-      if (epi == kEpiStore) FDK_LAUNCH(kEpiStore, true, true);
-      if (epi == kEpiSilu) FDK_LAUNCH(kEpiSilu, true, true);
-      if (epi == kEpiRope) FDK_LAUNCH(kEpiRope, true, true);
+      if (epi == kEpiStore) FDK_LAUNCH(kEpiStore, kXResident, true);
+      if (epi == kEpiSilu) FDK_LAUNCH(kEpiSilu, kXResident, true);
+      if (epi == kEpiRope) FDK_LAUNCH(kEpiRope, kXResident, true);
       FDK_CHECK_ARG(false, FDK_ERR_BAD_ARG, "the fused RMSNorm goes with the plain, SiLU or rotary output only");
     }
-    if (epi == kEpiResid) {
-      if (xres) FDK_LAUNCH(kEpiResid, true, false);
-      FDK_LAUNCH(kEpiResid, false, false);
-    }
-    if (epi == kEpiRope) {
-      if (xres) FDK_LAUNCH(kEpiRope, true, false);
-      FDK_LAUNCH(kEpiRope, false, false);
-    }
+    if (epi == kEpiResid) FDK_LAUNCH_X(kEpiResid);
+    if (epi == kEpiRope) FDK_LAUNCH_X(kEpiRope);
   } else {
     FDK_CHECK_ARG(!norm && epi != kEpiResid && epi != kEpiRope, FDK_ERR_BAD_ARG, "the decode fusions take bf16 only");
   }
-  if (epi == kEpiPush) {
-    if (xres) FDK_LAUNCH(kEpiPush, true, false);
-    FDK_LAUNCH(kEpiPush, false, false);
-  }
-  if (epi == kEpiSilu) {
-    if (xres) FDK_LAUNCH(kEpiSilu, true, false);
-    FDK_LAUNCH(kEpiSilu, false, false);
-  }
-  if (xres) FDK_LAUNCH(kEpiStore, true, false);
-  FDK_LAUNCH(kEpiStore, false, false);
+  if (epi == kEpiPush) FDK_LAUNCH_X(kEpiPush);
+  if (epi == kEpiSilu) FDK_LAUNCH_X(kEpiSilu);
+  FDK_LAUNCH_X(kEpiStore);
+#undef FDK_LAUNCH_X
 #undef FDK_LAUNCH
 }
 
@@ -950,6 +1130,26 @@ int launch_bits(const LinearParams& p, const void* lut_host, int grid, int dtype
   }
   return wide ? launch<BITS, 2, false>(p, lut_host, grid, flags, stream)
               : launch<BITS, 1, false>(p, lut_host, grid, flags, stream);
+}
+
+// Whether the fused RMSNorm (all of x in shared memory) can take a batch of m rows of k columns.
+template <int BITS>
+int norm_fits_bits(int m, int k, int* fits) {
+  uint32_t base = 0;
+  if (int st = dynamic_smem_base(&base)) return st;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  LinearParams p{};
+  p.m = m;
+  p.k = k;
+  int xm = -1;
+  if (m > 8) {
+    plan_smem<BITS, 2>(base, kGemvWarps<2>, (size_t)di.max_smem_optin, true, p, &xm);
+  } else {
+    plan_smem<BITS, 1>(base, kGemvWarps<1>, (size_t)di.max_smem_optin, true, p, &xm);
+  }
+  *fits = xm >= 0 ? 1 : 0;
+  return FDK_OK;
 }
 
 }  // namespace fdk

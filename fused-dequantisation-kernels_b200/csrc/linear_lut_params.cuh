@@ -25,8 +25,12 @@ struct LinearParams {
   uint32_t table_off;
   uint32_t slots_off;
   uint32_t slot_t;        // fragment column pairs kept per row in the reduction slots: ceil(min(m, 8) / 2)
-  uint32_t slot_sets;     // slot sets used in turn by consecutive row tiles: 2, or 1 where they are large
-  uint32_t xres_off;      // all of x staged once per CTA at this offset (kernels instantiated with XRES)
+  uint32_t slot_sets;     // blocks of sums (slot sets, or the team's sums) used in turn by consecutive row tiles
+  uint32_t team;          // 1: the compute warps add their deposits themselves into tsum, the finisher starts there
+  uint32_t slot_phases;   // team mode: the deposits of a tile are made and added in this many parts (1, 2, 4)
+  uint32_t tsum_off;      // team mode: [2][E] sums used in turn + [E] gather block of the tensor-parallel push
+  uint32_t xring_off;     // streamed x: per warp two stages of [block][n-tile][2][32 lanes][16 B]
+  uint32_t xres_off;      // all of x staged once per CTA at this offset (resident x)
   uint32_t xres_row;      // bytes between its rows
   uint32_t stash_off;     // E floats: the other CTAs' sums of a split row tile, fetched ahead by the finisher
   // input side of the decode fusion (norm_h != null): x = norm_w * bf16(h * rsqrt(mean(h^2) + eps)),
@@ -62,5 +66,9 @@ struct LinearParams {
 // translation unit of its own so that they compile in parallel.
 template <int BITS>
 int launch_bits(const LinearParams& p, const void* lut_host, int grid, int dtype, unsigned flags, cudaStream_t stream);
+
+// Whether the kernel's fused RMSNorm, which needs all of x in shared memory, can take x [m, k].
+template <int BITS>
+int norm_fits_bits(int m, int k, int* fits);
 
 }  // namespace fdk

@@ -234,7 +234,8 @@ class LlamaDecoder(nn.Module):
         if native_layers and batch <= 16:
             self.rope_tab = torch.zeros(64, device=dev, dtype=torch.int32)
             self.sumsq = torch.zeros((batch, h // 64), device=dev, dtype=torch.float32)
-            if self.tp.size == 1 and batch * (2 * h + 16) <= 64 * 1024 and h % 64 == 0:
+            normed = [m for l in self.layers for m in (l.qkv, l.gate_up)]
+            if self.tp.size == 1 and h % 64 == 0 and all(native.linear_norm_fits(batch, h, m.bits) for m in normed):
                 self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
             else:  # tensor parallel: the norms add the ranks' partial sums; the rotary epilogue still applies
                 self.rope_fusions = [self._layer_fusions(i, rope_only=True) for i in range(len(self.layers))]

@@ -107,6 +107,7 @@ _SIGNATURES = {
         [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_uint, ctypes.c_void_p],
     ),
     "fdk_static_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "fdk_linear_norm_fits": (ctypes.c_int, [ctypes.c_int] * 3 + [ctypes.POINTER(ctypes.c_int)]),
     "fdk_rmsnorm": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int] * 2 + [ctypes.c_float, ctypes.c_void_p]),
     "fdk_rope_append": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_void_p]),
     "fdk_rope_append_paired": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_void_p]),
@@ -258,6 +259,13 @@ def static_status() -> int:
     out = ctypes.c_int(0)
     check(lib().fdk_static_status(ctypes.byref(out)))
     return out.value
+
+
+def linear_norm_fits(m: int, k: int, bits: int) -> bool:
+    """Whether `linear_lut_fused` can apply its RMSNorm to a batch of m rows of k columns."""
+    out = ctypes.c_int(0)
+    check(lib().fdk_linear_norm_fits(m, k, bits, ctypes.byref(out)))
+    return bool(out.value)
 
 
 _host_luts: dict[int, tuple[weakref.ref, int, bytes]] = {}

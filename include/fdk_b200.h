@@ -229,6 +229,13 @@ int fdk_linear_lut_fused(const void* x, const void* tiled, const void* lut, cons
                          size_t workspace_bytes, unsigned flags, const fdk_linear_fusion* fusion,
                          void* stream);
 
+/* Whether fdk_linear_lut_fused can apply its RMSNorm (norm_h != NULL) to a batch of m rows of k
+ * columns: the normalised x has to fit in a CTA's shared memory beside the lookup table
+ * (16 rows of 3072 columns do, 16 of 8192 do not).  *fits_host = 1 or 0; shapes the entry point
+ * rejects anyway give 0.  The first call on a device asks the device once for the address of
+ * its shared window (as fdk_workspace_init does).  No counterpart in the reference. */
+int fdk_linear_norm_fits(int m, int k, int bits, int* fits_host);
+
 /* table[i] = {bf16 cos, bf16 sin} of the angle *pos * theta^(-2 i / 128), i = 0 .. 63: once per
  * decode step, for the rotary output side above. */
 int fdk_rope_table(const void* pos, void* table, float theta, void* stream);
