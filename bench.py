@@ -312,6 +312,9 @@ def run_gpu_arm(args) -> None:
                     y_host.copy_(layer(xh.to(device, non_blocking=True)))
             torch.cuda.synchronize()
             e2e_s = time.perf_counter() - t0
+        status = native.device_status(device)
+        if status != 0:  # a bounded wait ran out inside the timed region: the numbers mean nothing
+            raise RuntimeError(f"device-side status word {status} after the timed region")
 
     t = torch.tensor([elapsed_ms, e2e_s], device=device, dtype=torch.float64)
     if world > 1:

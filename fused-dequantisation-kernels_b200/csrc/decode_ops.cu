@@ -10,6 +10,7 @@
 #include <type_traits>
 
 #include "fdk_common.cuh"
+#include "linear_lut_params.cuh"
 #include "tp_exchange.cuh"
 
 namespace fdk {
@@ -63,9 +64,16 @@ __device__ __forceinline__ uint4 ld_words(const uint2* p) {  // two staging word
                : "memory");
   return v;
 }
-// Reads the two words again until both carry `tag` (bounded: two seconds).
+// Reads the two words again until both carry `tag` (bounded: two seconds).  Once a wait has
+// run out on this rank (status bit set, by this or an earlier reduce) later words are taken as
+// they are, so that a rank whose peer stopped pushing fails within seconds instead of waiting
+// two seconds per word.
 __device__ __forceinline__ void settle(uint4& v, const uint2* p, uint32_t tag, int* status) {
   unsigned long long t0 = 0;
+  if ((v.y != tag || v.w != tag) && (*reinterpret_cast<volatile int*>(status) & 1)) {
+    v = make_uint4(0u, tag, 0u, tag);
+    return;
+  }
   for (uint32_t i = 0; v.y != tag || v.w != tag; ++i) {
     v = ld_words(p);
     if ((i & 63u) == 63u) {
@@ -455,8 +463,8 @@ extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width,
 // [batch, kv_heads, max_len, 128].  Grid (splits, kv_heads, batch): a CTA of 4 warps takes one
 // slice of the context for all the query heads that share a KV head (so every key/value byte
 // is read once), keeps a running softmax per head, and leaves {max, sum, 128 weighted values}
-// per head in scratch; the last CTA of a (batch, kv head) to finish merges the slices and
-// writes the bf16 output.  HBM-bound at large batch (2 x 256 B per position per KV head).
+// per head in scratch as tagged words; the CTA of slice 0 polls them (bounded), merges the
+// slices and writes the bf16 output.  HBM-bound at large batch (2 x 256 B per position per KV head).
 namespace fdk {
 namespace {
 
@@ -473,7 +481,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ float part[kAttnWarps][G][132];
   __shared__ float wbuf[kAttnWarps][16 * 4 > 8 * G ? 16 * 4 : 8 * G];  // softmax weights of a round, per warp: U * G
-  __shared__ int is_last;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // The position only changes between decode steps, and the keys and values of earlier
@@ -605,7 +612,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   // threads 0..127: one output dimension each from here on
   const int d = threadIdx.x & 127;
   const bool writer = threadIdx.x < 128;
-  float* mine = scratch + (((size_t)b * kv_heads + kvh) * splits + split) * (G * 130);
+  // Every slice leaves its numbers in scratch as 8-byte words {value, tag}, tag = number of this
+  // use of the (batch row, KV head) + 1: a word is valid once its tag is this launch's, so the
+  // slices need no fence, counter or second trip through L2 to hand their sums over.
+  const int group = b * kv_heads + kvh;
+  const uint32_t uses = splits == 1 ? 0u : (uint32_t)ld_relaxed_s32(counters + group);
+  const uint32_t tag = uses + 1u;
+  uint2* mine = reinterpret_cast<uint2*>(scratch) + ((size_t)group * splits + split) * (G * 130);
   if (writer) {
     for (int j = 0; j < G; ++j) {
       float m = -INFINITY;
@@ -621,33 +634,54 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       if (splits == 1) {
         out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(l > 0.f ? a / l : 0.f);
       } else {
-        __stcg(mine + j * 130 + d, a);
+        st_relaxed_v2(mine + j * 130 + d, make_uint2(__float_as_uint(a), tag));
         if (d == 0) {
-          __stcg(mine + j * 130 + 128, m);
-          __stcg(mine + j * 130 + 129, l);
+          st_relaxed_v2(mine + j * 130 + 128, make_uint2(__float_as_uint(m), tag));
+          st_relaxed_v2(mine + j * 130 + 129, make_uint2(__float_as_uint(l), tag));
         }
       }
     }
   }
-  if (splits == 1) return;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const int old = atomicAdd(counters + b * kv_heads + kvh, 1);
-    is_last = (old == splits - 1);
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  // merge the slices: first the per-slice weights (one thread per (head, slice)), then the sums
+  if (splits == 1 || split != 0) return;
+
+  // The CTA of slice 0 merges.  Thread (d, half) takes output dimension d of every second
+  // slice; its first words are requested before the slices' maxima and sums are polled, so
+  // that the merge costs one trip to L2 once the last slice has written.  All polls are bounded.
   __shared__ float coef[G][kMaxSplits];
   __shared__ float lpart[G][kMaxSplits];
   __shared__ float denom[G];
-  const float* base = scratch + ((size_t)b * kv_heads + kvh) * splits * (G * 130);
-  for (int idx = threadIdx.x; idx < G * splits; idx += blockDim.x) {  // every slice's max and sum, all loads in flight
+  __shared__ float other_half[G][128];
+  constexpr int SB = G <= 4 ? 8 : 4;  // slices per thread in flight (SB * G words)
+  constexpr uint32_t kPollLimit = 1u << 20;
+  const uint2* base = reinterpret_cast<const uint2*>(scratch) + (size_t)group * splits * (G * 130);
+  const int half = threadIdx.x >> 7;
+  bool ok = true;
+  uint2 av[SB][G];
+  auto request = [&](int s0) {  // slices s0 + half, s0 + half + 2, ...
+#pragma unroll
+    for (int i = 0; i < SB; ++i) {
+      const int s2 = s0 + half + 2 * i;
+#pragma unroll
+      for (int j = 0; j < G; ++j)
+        av[i][j] = s2 < splits ? ld_relaxed_v2(base + (size_t)s2 * (G * 130) + j * 130 + d) : make_uint2(0u, tag);
+    }
+  };
+  request(0);
+  for (int idx = threadIdx.x; idx < G * splits; idx += blockDim.x) {
     const int j = idx / splits, s2 = idx - j * splits;
-    coef[j][s2] = __ldcg(base + s2 * (G * 130) + j * 130 + 128);  // the slice's max for now
-    lpart[j][s2] = __ldcg(base + s2 * (G * 130) + j * 130 + 129);
+    const uint2* w = base + (size_t)s2 * (G * 130) + j * 130 + 128;
+    uint2 mm = ld_relaxed_v2(w), ll = ld_relaxed_v2(w + 1);
+    for (uint32_t spins = 0; mm.y != tag || ll.y != tag; ++spins) {
+      if (spins > kPollLimit) {
+        ok = false;
+        break;
+      }
+      __nanosleep(64);
+      mm = ld_relaxed_v2(w);
+      ll = ld_relaxed_v2(w + 1);
+    }
+    coef[j][s2] = __uint_as_float(mm.x);  // the slice's max for now
+    lpart[j][s2] = __uint_as_float(ll.x);
   }
   __syncthreads();
   if (threadIdx.x < G) {
@@ -663,15 +697,48 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
     denom[j] = l;
   }
   __syncthreads();
-  if (writer) {
+  float total[G];
+#pragma unroll
+  for (int j = 0; j < G; ++j) total[j] = 0.f;
+  for (int s0 = 0; s0 < splits; s0 += 2 * SB) {
+    if (s0 > 0) request(s0);
+    for (uint32_t spins = 0;; ++spins) {  // a slice's maximum can land before its last sums
+      bool fresh = true;
+#pragma unroll
+      for (int i = 0; i < SB; ++i)
+#pragma unroll
+        for (int j = 0; j < G; ++j) fresh = fresh && av[i][j].y == tag;
+      if (fresh) break;
+      if (spins > kPollLimit) {
+        ok = false;
+        break;
+      }
+      __nanosleep(64);
+      request(s0);
+    }
+#pragma unroll
+    for (int i = 0; i < SB; ++i) {
+      const int s2 = s0 + half + 2 * i;
+      if (s2 < splits) {
+#pragma unroll
+        for (int j = 0; j < G; ++j) total[j] += __uint_as_float(av[i][j].x) * coef[j][s2];
+      }
+    }
+  }
+  if (half == 1) {
+#pragma unroll
+    for (int j = 0; j < G; ++j) other_half[j][d] = total[j];
+  }
+  __syncthreads();
+  if (half == 0) {
+#pragma unroll
     for (int j = 0; j < G; ++j) {
-      float a = 0.f;
-#pragma unroll 8
-      for (int s2 = 0; s2 < splits; ++s2) a += __ldcg(base + s2 * (G * 130) + j * 130 + d) * coef[j][s2];
+      const float a = total[j] + other_half[j][d];
       out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(denom[j] > 0.f ? a / denom[j] : 0.f);
     }
   }
-  if (threadIdx.x == 0) counters[b * kv_heads + kvh] = 0;
+  if (threadIdx.x == 0) counters[group] = (int)((uses + 1u) & 0x3FFFFFFFu);  // this use is done
+  if (!ok) atomicOr(counters + gridDim.z * kv_heads, kStatusTimeout);
 }
 
 template <int G>
@@ -702,8 +769,14 @@ extern "C" int fdk_decode_attention_scratch(int batch, int q_heads, int kv_heads
   FDK_CHECK_ARG(scratch_bytes_host && counter_bytes_host, FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(batch > 0 && q_heads > 0 && kv_heads > 0 && splits > 0 && q_heads % kv_heads == 0, FDK_ERR_BAD_ARG,
                 "bad sizes");
-  *scratch_bytes_host = (size_t)batch * q_heads * splits * 130 * sizeof(float);
-  *counter_bytes_host = (size_t)batch * kv_heads * sizeof(int);
+  *scratch_bytes_host = (size_t)batch * q_heads * splits * 130 * sizeof(uint2);  // {value, tag} words
+  *counter_bytes_host = ((size_t)batch * kv_heads + 1) * sizeof(int);           // use counts + a status word
+  return FDK_OK;
+}
+
+extern "C" int fdk_decode_attention_status(const void* counters, int batch, int kv_heads, int* status_host) {
+  FDK_CHECK_ARG(counters != nullptr && status_host != nullptr && batch > 0 && kv_heads > 0, FDK_ERR_BAD_ARG, "bad argument");
+  FDK_CUDA(cudaMemcpy(status_host, (const int*)counters + (size_t)batch * kv_heads, sizeof(int), cudaMemcpyDeviceToHost));
   return FDK_OK;
 }
 

@@ -185,7 +185,7 @@ __device__ __forceinline__ int cta_of(const LinearParams& p, int item) {
 // that the number of trips does not grow with the batch.  A round that finds a stale tag is
 // repeated after a short sleep.  Returns false if that ran out.
 template <int NB>
-__device__ __noinline__ bool fetch_foreign(const LinearParams& p, float* stash, int rt, uint32_t tag, int E) {
+__device__ __forceinline__ bool fetch_foreign(const LinearParams& p, float* stash, int rt, uint32_t tag, int E) {
   constexpr int EMAX = 512 * NB;
   const int lane = threadIdx.x & 31;
   const int last = cta_of(p, (rt + 1) * p.k_slabs - 1);
@@ -269,8 +269,8 @@ __device__ __noinline__ bool fetch_foreign(const LinearParams& p, float* stash, 
 // this row tile: per warp one block of E = NB * 4 * SW floats laid out
 // [sub-tile][n-tile][t][g][4].  `foreign`: stash holds the other CTAs' sums (owner of a split
 // tile).  `publish`: the sums go to `mine` in the workspace as tagged words and nothing else is done.
-template <int NB, bool FP16, int EPI>
-__device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots, int deposits, uint16_t* gathered,
+template <int NB, int DEPOSITS, bool FP16, int EPI>
+__device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots, uint16_t* gathered,
                                             const float* stash, uint2* mine, bool foreign, bool publish, uint32_t tag,
                                             int rt, uint32_t push_seq, const uint32_t (&hpre)[8 * NB],
                                             const uint8_t* smem_head) {
@@ -287,14 +287,14 @@ __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots,
   for (int e0 = lane * 4; e0 < E; e0 += 128) {
     float4 even = make_float4(0.f, 0.f, 0.f, 0.f), odd = even;
 #pragma unroll 5
-    for (int w = 0; w + 1 < deposits; w += 2) {
+    for (int w = 0; w + 1 < DEPOSITS; w += 2) {
       const float4 a = *reinterpret_cast<const float4*>(slots + w * E + e0);
       const float4 b = *reinterpret_cast<const float4*>(slots + (w + 1) * E + e0);
       even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
       odd.x += b.x; odd.y += b.y; odd.z += b.z; odd.w += b.w;
     }
-    if (deposits & 1) {
-      const float4 a = *reinterpret_cast<const float4*>(slots + (deposits - 1) * E + e0);
+    if (DEPOSITS & 1) {
+      const float4 a = *reinterpret_cast<const float4*>(slots + (DEPOSITS - 1) * E + e0);
       even.x += a.x; even.y += a.y; even.z += a.z; even.w += a.w;
     }
     float acc[4] = {even.x + odd.x, even.y + odd.y, even.z + odd.z, even.w + odd.w};
@@ -527,7 +527,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM = false>
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM, bool TEAM>
 __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
@@ -679,15 +679,16 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
         if (i0 + u * kThreads < total) xv[u] = ldg_l2(p.x + (size_t)(i0 + u * kThreads) * 8);
 #pragma unroll
       for (int u = 0; u < kStageBatch; ++u) {
-        while (c >= vecs) {
-          c -= vecs;
-          ++row;
-        }
-        if (i0 + u * kThreads < total)
+        if (i0 + u * kThreads < total) {
+          while (c >= vecs) {
+            c -= vecs;
+            ++row;
+          }
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xres_addr + row * p.xres_row + c * 16), "r"(xv[u].x),
                        "r"(xv[u].y), "r"(xv[u].z), "r"(xv[u].w)
                        : "memory");
-        c += kThreads;
+          c += kThreads;
+        }
       }
     }
   }
@@ -697,8 +698,9 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
   const int E = NB * kSubTiles * sw;  // sums of one row tile
   const uint32_t slot_set_floats = W * E;
   // Team mode (large deposits): the compute warps add their deposits themselves, every warp a
-  // slice, into one of two blocks of E sums; the finisher starts from those.
-  const bool team = p.team != 0;
+  // slice, into one of two blocks of E sums; the finisher starts from those.  A template
+  // parameter: the kernels of small batches carry none of it.
+  constexpr bool team = TEAM;
   float* tsum = reinterpret_cast<float*>(smem_raw + p.tsum_off);
   bool timed_out = false;
 
@@ -735,8 +737,13 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       }
       if (!wait_shared_word(&esync->count[set], W)) timed_out = true;
       __threadfence_block();
-      tile_finish<NB, FP16, EPI>(p, my_slots, team ? 1 : W, gathered, stash, p.partial + (size_t)cta * (512 * NB),
-                                 !full && owner, !full && !owner, tag, rt, push_seq, hpre, smem_raw);
+      if constexpr (team) {  // one block of sums, made by the compute warps
+        tile_finish<NB, 1, FP16, EPI>(p, my_slots, gathered, stash, p.partial + (size_t)cta * (512 * NB), !full && owner,
+                                      !full && !owner, tag, rt, push_seq, hpre, smem_raw);
+      } else {
+        tile_finish<NB, WARPS, FP16, EPI>(p, my_slots, gathered, stash, p.partial + (size_t)cta * (512 * NB),
+                                          !full && owner, !full && !owner, tag, rt, push_seq, hpre, smem_raw);
+      }
       __syncwarp();
       if (lane == 0) {
         if (!full && owner) p.counters[rt] = (uses + 1) & 0x7FFFF;  // this use of the split tile is done
@@ -772,7 +779,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       float* my_slots = slots + set * slot_set_floats;
       // the slot set is free once the finisher has summed the tile that used it before
       if (!wait_shared_word(&esync->gen[set], turn)) timed_out = true;
-      if (team) {
+      if constexpr (team) {
         // one block of deposits, filled and added up in `slot_phases` parts of the tile's four
         // sub-tiles (fewer sub-tiles at a time where shared memory is short); the adding follows
         // the finisher's order, so the sums do not depend on the mode
@@ -833,13 +840,11 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
   };
 
   // per-lane address of this lane's x fragment of column 0, per batch-column group
-  uint32_t x_lane[NB];
-  const uint16_t* x_ptr[NB];
+  uint32_t x_lane[NB];  // resident x: shared-memory address; otherwise: element offset into x
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {
     const int b = min(g + 8 * nb, p.m - 1);  // lanes of unused batch columns read a live row
-    x_lane[nb] = xres_addr + b * p.xres_row + t * 32;
-    x_ptr[nb] = p.x + (size_t)b * p.k + t * 16;
+    x_lane[nb] = XM == kXResident ? xres_addr + b * p.xres_row + t * 32 : (uint32_t)(b * p.k + t * 16);
   }
 
   // streamed x: a lane's private ring, [stage][block][n-tile][half] vectors 512 bytes apart
@@ -855,8 +860,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
           // lanes of unused batch columns copy nothing: what they multiply is never stored
           if (g + 8 * nb < p.m) {
             const uint32_t dst = ring_lane + stage * kRingStage + (jb * NB + nb) * 1024;
-            cp_async16(dst, x_ptr[nb] + col);
-            cp_async16(dst + 512, x_ptr[nb] + col + 8);
+            cp_async16(dst, p.x + x_lane[nb] + col);
+            cp_async16(dst + 512, p.x + x_lane[nb] + col + 8);
           }
         }
       }
@@ -885,8 +890,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
           lo = ring128(ring_lane + stage * kRingStage + (JB * NB + nb) * 1024);
           hi = ring128(ring_lane + stage * kRingStage + (JB * NB + nb) * 1024 + 512);
         } else {
-          lo = ldg_l2(x_ptr[nb] + col);
-          hi = ldg_l2(x_ptr[nb] + col + 8);
+          lo = ldg_l2(p.x + x_lane[nb] + col);
+          hi = ldg_l2(p.x + x_lane[nb] + col + 8);
         }
         xb[nb][0] = lo.x; xb[nb][1] = lo.y; xb[nb][2] = lo.z; xb[nb][3] = lo.w;
         xb[nb][4] = hi.x; xb[nb][5] = hi.y; xb[nb][6] = hi.z; xb[nb][7] = hi.w;
@@ -966,12 +971,15 @@ inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 //   [sync words] ... [table, at a multiple of 64 KB of the window when it is the wide one] ...
 // with the reduction slots, the sums and x (all of it, or the ring of the streamed mode) placed
 // below the table where there is room, above it otherwise.  Chooses how the kernel finds x
-// (*xmode): the fused RMSNorm needs all of x in shared memory; otherwise x is streamed (measured
-// equal to or faster than the copy per CTA at every batch: no staging phase before the loop),
-// staged whole where the ring does not fit (1-bit and 3-bit slabs of 256 columns), and read
-// straight from L2 as the last resort.  Returns the dynamic size needed.
+// (*xmode): the fused RMSNorm needs all of x in shared memory.  Otherwise x is streamed where a
+// CTA has few slabs (no staging phase before a short loop: measured 0.1-0.2 us faster up to ~40
+// slabs per CTA) or x is large (a copy per CTA of more than 40 KB costs more than it saves), and
+// staged whole for long loops over a small x (0.2-0.3 us faster from ~80 slabs per CTA on: no
+// cp.async in the loop); whichever does not fit falls back to the other, then to reading
+// fragments straight from L2.  Returns the dynamic size needed.
 template <int BITS, int NB>
-size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, LinearParams& p, int* xmode) {
+size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, int slabs_per_cta, LinearParams& p,
+                 int* xmode) {
   constexpr bool WIDE = BITS != 3;
   using T = Table<BITS, WIDE>;
   using L = Layout<BITS>;
@@ -1012,7 +1020,8 @@ size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, Lin
     p.xring_off = mode == kXStreamed ? place(ring_bytes) : 0;
     return high;
   };
-  const int order[3] = {need_resident ? kXResident : kXStreamed, need_resident ? kXStreamed : kXResident, kXDirect};
+  const bool stage_whole = need_resident || (xres_bytes <= 40 * 1024 && slabs_per_cta >= 64);
+  const int order[3] = {stage_whole ? kXResident : kXStreamed, stage_whole ? kXStreamed : kXResident, kXDirect};
   for (int mode : order) {
     if (need_resident && mode != kXResident) break;
     for (uint32_t phases = 1; phases <= (team ? 4u : 1u); phases *= 2) {
@@ -1052,12 +1061,22 @@ int launch_kernel(Kernel kernel, std::atomic<size_t> (&configured)[64], const Li
   return FDK_OK;
 }
 
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM, bool TEAM>
+int launch_team(const LinearParams& p, const InlineLut<BITS>& inl, int grid, size_t smem, unsigned flags,
+                cudaStream_t stream) {
+  static std::atomic<size_t> configured[64] = {};
+  return launch_kernel(linear_lut_kernel<BITS, NB, WARPS, FP16, EPI, XM, NORM, TEAM>, configured, p, inl, grid,
+                       (WARPS + 1) * 32, smem, flags, stream);
+}
+
+// Two n-tiles always run in team mode; one n-tile from five batch rows on.
 template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM>
 int launch_instance(const LinearParams& p, const InlineLut<BITS>& inl, int grid, size_t smem, unsigned flags,
                     cudaStream_t stream) {
-  static std::atomic<size_t> configured[64] = {};
-  return launch_kernel(linear_lut_kernel<BITS, NB, WARPS, FP16, EPI, XM, NORM>, configured, p, inl, grid,
-                       (WARPS + 1) * 32, smem, flags, stream);
+  if constexpr (NB == 1) {
+    if (!p.team) return launch_team<BITS, NB, WARPS, FP16, EPI, XM, NORM, false>(p, inl, grid, smem, flags, stream);
+  }
+  return launch_team<BITS, NB, WARPS, FP16, EPI, XM, NORM, true>(p, inl, grid, smem, flags, stream);
 }
 
 template <int BITS, int NB, int WARPS, bool FP16>
@@ -1068,7 +1087,8 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
   if (int st = device_info(&di)) return st;
   const bool norm = p.norm_h != nullptr;
   int xm = kXDirect;
-  const size_t smem = plan_smem<BITS, NB>(base, WARPS, (size_t)di.max_smem_optin, norm, p, &xm);
+  const int ctas = sm_count < p.total ? sm_count : p.total;
+  const size_t smem = plan_smem<BITS, NB>(base, WARPS, (size_t)di.max_smem_optin, norm, p.total / ctas, p, &xm);
   FDK_CHECK_ARG(xm >= 0, FDK_ERR_SHAPE, "the fused RMSNorm needs x [%d, %d] to fit in shared memory", p.m, p.k);
   FDK_CHECK_ARG(smem <= (size_t)di.max_smem_optin, FDK_ERR_CUDA, "shared-memory plan of %zu bytes exceeds %d", smem,
                 di.max_smem_optin);
@@ -1144,9 +1164,9 @@ int norm_fits_bits(int m, int k, int* fits) {
   p.k = k;
   int xm = -1;
   if (m > 8) {
-    plan_smem<BITS, 2>(base, kGemvWarps<2>, (size_t)di.max_smem_optin, true, p, &xm);
+    plan_smem<BITS, 2>(base, kGemvWarps<2>, (size_t)di.max_smem_optin, true, 0, p, &xm);
   } else {
-    plan_smem<BITS, 1>(base, kGemvWarps<1>, (size_t)di.max_smem_optin, true, p, &xm);
+    plan_smem<BITS, 1>(base, kGemvWarps<1>, (size_t)di.max_smem_optin, true, 0, p, &xm);
   }
   *fits = xm >= 0 ? 1 : 0;
   return FDK_OK;

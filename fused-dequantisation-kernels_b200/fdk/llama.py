@@ -235,7 +235,9 @@ class LlamaDecoder(nn.Module):
             self.rope_tab = torch.zeros(64, device=dev, dtype=torch.int32)
             self.sumsq = torch.zeros((batch, h // 64), device=dev, dtype=torch.float32)
             normed = [m for l in self.layers for m in (l.qkv, l.gate_up)]
-            if self.tp.size == 1 and h % 64 == 0 and all(native.linear_norm_fits(batch, h, m.bits) for m in normed):
+            # up to 8 rows (one n-tile of the fused kernel); from 9 rows on the tensor-core kernel
+            # with separate glue kernels is the faster step
+            if self.tp.size == 1 and batch <= 8 and h % 64 == 0 and all(native.linear_norm_fits(batch, h, m.bits) for m in normed):
                 self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
             else:  # tensor parallel: the norms add the ranks' partial sums; the rotary epilogue still applies
                 self.rope_fusions = [self._layer_fusions(i, rope_only=True) for i in range(len(self.layers))]
@@ -246,6 +248,21 @@ class LlamaDecoder(nn.Module):
         )
         if self.tp.size > 1 and self.tp.fused and batch <= 16 and can_push and h % 64 == 0:
             self.exchange = self.tp.open_exchange(16 * h, dev)
+
+    def check_status(self) -> None:
+        """Reads the device-side status words the kernels of this decoder report to (synchronises):
+        the workspace of the projections, the attention scratch and the tensor-parallel exchange.
+        Raises if a bounded wait ran out or a kernel found shared memory laid out differently
+        from the host's plan -- outputs computed since the last check are then not to be trusted."""
+        dev = self.final_norm.device
+        words = {"projection workspace": native.device_status(dev)}
+        if getattr(self, "attn_counters", None) is not None and self.splits > 1:
+            words["attention scratch"] = native.attention_status(self.attn_counters, self.batch, self.kv_heads)
+        if self.exchange is not None:
+            words["tensor-parallel exchange"] = native.tp_exchange_status(self.exchange)
+        bad = {k: v for k, v in words.items() if v}
+        if bad:
+            raise native.FdkError(-1, "device-side status", f"non-zero status words: {bad}")
 
     def _layer_fusions(self, i: int, rope_only: bool = False):
         """The fusion descriptors of layer i (pointers into this decoder's buffers)."""
@@ -481,6 +498,7 @@ class Generator:
             self.input_ids[:, context] = self.last_token
         self.last_index = torch.tensor(context, device=device)
         self.last_logits = logits
+        model.check_status()
 
     def step(self) -> None:
         with torch.no_grad():

@@ -424,6 +424,7 @@ def benchmark(model: nn.Module, batch_size: int, reps: int, context: int = 2, se
     with torch.no_grad():
         generator = llama.Generator(model, prompt_ids, reps + 4, synthetic_context=max(context, 1))
         avg_time, avg_time_stderr = bench.measure_time(lambda _: generator.step(), inner_reps=1, outer_reps=reps)
+    model.check_status()  # a timed-out wait inside the timed steps would make the number meaningless
     return Result(
         batch_size=batch_size,
         bytes_rw=count_parameter_read_bytes(model),

@@ -114,6 +114,7 @@ _SIGNATURES = {
     "fdk_silu_mul": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "fdk_decode_attention_scratch": (ctypes.c_int, [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_size_t)] * 2),
     "fdk_decode_attention": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_int] * 6 + [ctypes.c_void_p]),
+    "fdk_decode_attention_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]),
     "fdk_workspace_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "fdk_linear_lut": (
         ctypes.c_int,
@@ -464,7 +465,16 @@ def silu_mul(gate_up: Tensor, out: Tensor, group: int | None = None) -> None:
 def attention_scratch(batch: int, q_heads: int, kv_heads: int, splits: int, device: torch.device) -> tuple[Tensor, Tensor]:
     a, b = ctypes.c_size_t(0), ctypes.c_size_t(0)
     check(lib().fdk_decode_attention_scratch(batch, q_heads, kv_heads, splits, ctypes.byref(a), ctypes.byref(b)))
-    return (torch.empty(a.value // 4, dtype=torch.float32, device=device), torch.zeros(b.value // 4, dtype=torch.int32, device=device))
+    # both zero-filled once: the slices' words are tagged with the use count kept in the counters
+    return (torch.zeros(a.value // 4, dtype=torch.float32, device=device), torch.zeros(b.value // 4, dtype=torch.int32, device=device))
+
+
+def attention_status(counters: Tensor, batch: int, kv_heads: int) -> int:
+    """Status word of a decode-attention scratch (synchronises): 0, or 1 after a wait ran out."""
+    out = ctypes.c_int(0)
+    with torch.cuda.device(counters.device):
+        check(lib().fdk_decode_attention_status(counters.data_ptr(), batch, kv_heads, ctypes.byref(out)))
+    return out.value
 
 
 def decode_attention(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, out: Tensor,

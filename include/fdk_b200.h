@@ -179,11 +179,17 @@ int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, int group,
  * [batch, kv_heads, max_len, 128] (bf16), keys 0 .. *pos (device int64; the current token's
  * key and value must already be appended), grouped-query (q_heads / kv_heads in 1..8).
  * q, out: [batch, q_heads * 128].  The context is cut into `splits` slices handled by
- * different CTAs; with splits > 1, `scratch` and zero-initialised `counters` of the sizes
- * given by fdk_decode_attention_scratch are needed (counters are left zeroed).  Stands in for
- * the attention of transformers' Llama over its StaticCache (src/fdk/models.py:238-251). */
+ * different CTAs; with splits > 1, `scratch` and `counters` of the sizes given by
+ * fdk_decode_attention_scratch are needed, BOTH zero-filled once before their first use and
+ * then left to the library: the slices hand their sums over as {value, tag} words whose tag
+ * is the use count kept in `counters`, so nothing is cleared between calls, and calls that
+ * share a scratch must be ordered on one stream.  The last word of `counters` is a status
+ * word (fdk_decode_attention_status: 0, or 1 after a bounded wait for a slice ran out; the
+ * output of that call is then undefined).  Stands in for the attention of transformers'
+ * Llama over its StaticCache (src/fdk/models.py:238-251). */
 int fdk_decode_attention_scratch(int batch, int q_heads, int kv_heads, int splits,
                                  size_t* scratch_bytes_host, size_t* counter_bytes_host);
+int fdk_decode_attention_status(const void* counters, int batch, int kv_heads, int* status_host);
 int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache, const void* pos,
                          void* out, void* scratch, void* counters, int batch, int q_heads,
                          int kv_heads, int head_dim, int max_len, int splits, void* stream);

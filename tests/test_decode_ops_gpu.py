@@ -3,9 +3,9 @@ restatements of what the reference takes from transformers' Llama (src/fdk/model
 
   * fdk_decode_attention vs softmax(q K^T / sqrt(d)) V computed in fp32 on the same bf16 cache:
     every grouped-query ratio the models use (3: 4B, 5: 12B, 6: 31B) and the extremes, one and
-    several context slices (the split path with its last-arriver merge, empty slices, clamped
+    several context slices (the split path with its merge by the first slice, empty slices, clamped
     tail reads), positions at slice boundaries and beyond 2048, each launch repeated on the same
-    scratch and counters;
+    scratch and counters (use counts and tagged words);
   * fdk_rope_append vs the rotate-half formula with cos/sin rounded to bf16, at positions 0, 1024
     and 2175 (angles up to ~2176 rad), and a position outside the cache.
 """
@@ -61,15 +61,19 @@ def test_decode_attention_matches_fp32_reference(native, group, splits, batch):
     k_cache, v_cache = _cache(batch)
     scratch, counters = native.attention_scratch(batch, q_heads, KV_HEADS, splits, torch.device("cuda"))
     gen = torch.Generator(device="cuda").manual_seed(7 * group + splits + batch)
+    launches = 0
     for pos_value in (0, 127, 128, 1023, 2175):
         q = torch.randn((batch, q_heads * 128), generator=gen, device="cuda").bfloat16()
         pos = torch.tensor(pos_value, device="cuda", dtype=torch.int64)
         expected = attention_reference(q.view(batch, q_heads, 128), k_cache, v_cache, pos_value, group)
-        for repeat in range(2):  # the second launch finds scratch and counters as the first left them
+        for repeat in range(2):  # later launches find scratch and counters as the earlier ones left them
             out = torch.full((batch, q_heads * 128), float("nan"), device="cuda", dtype=torch.bfloat16)
             native.decode_attention(q, k_cache, v_cache, pos, out, scratch, counters, q_heads, KV_HEADS, splits)
             torch.cuda.synchronize()
-            assert int(counters.abs().sum()) == 0, "slice counters must be left at zero"
+            launches += 1
+            if splits > 1:  # every (batch row, KV head) counts its uses; the last word is the status
+                assert counters[:-1].tolist() == [launches] * (batch * KV_HEADS)
+            assert native.attention_status(counters, batch, KV_HEADS) == 0
             err = (out.float() - expected).pow(2).sum().div(expected.pow(2).sum()).sqrt().item()
             assert err < 6e-3, f"pos={pos_value} repeat={repeat}: rel-RMS error {err}"  # bf16 output rounding ~2e-3
             worst = (out.float() - expected).abs().max().item()
@@ -90,6 +94,7 @@ def test_decode_attention_position_outside_the_cache_is_clamped(native):
     expected = attention_reference(q.view(batch, q_heads, 128), k_cache, v_cache, MAX_LEN - 1, group)
     torch.cuda.synchronize()
     assert (out.float() - expected).pow(2).sum().div(expected.pow(2).sum()).sqrt().item() < 6e-3
+    assert native.attention_status(counters, batch, KV_HEADS) == 0
 
 
 def rope_reference(x, pos: int, theta: float):
