@@ -717,12 +717,10 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       const bool owner = (c0 <= seg_lo);  // holds the tile's first slab
       const int uses = rt == rt_first ? uses_first : uses_last;  // only those two can be split
       const uint32_t tag = ((uint32_t)(uses + 1) << 12) | (uint32_t)rt;
-      if (!full && owner) {
-        if (!fetch_foreign<NB>(p, stash, rt, tag, E)) timed_out = true;
-        __syncwarp();
-      }
       uint32_t hpre[8 * NB] = {};
-      if constexpr (EPI == kEpiResid) {  // the tile's part of the residual stream, fetched while the deposits come in
+      // the tile's part of the residual stream, requested before the other CTAs' sums are polled
+      // and the deposits come in
+      if constexpr (EPI == kEpiResid) {
         if (full || owner) {
 #pragma unroll
           for (int b = 0; b < 8 * NB; ++b) {
@@ -734,6 +732,10 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
             }
           }
         }
+      }
+      if (!full && owner) {
+        if (!fetch_foreign<NB>(p, stash, rt, tag, E)) timed_out = true;
+        __syncwarp();
       }
       if (!wait_shared_word(&esync->count[set], W)) timed_out = true;
       __threadfence_block();
