@@ -274,6 +274,56 @@ __global__ void sumsq_tiles_kernel(const uint16_t* __restrict__ h, float* __rest
   if (lane == 0) sumsq[(size_t)row * tiles + t] = sq;
 }
 
+// out[row] = index of the largest of x[row][0 .. n) (the lowest such index; a NaN counts as
+// larger than any number, as torch.argmax has it): greedy decoding's token choice.  One CTA of
+// 1024 threads per row; values are compared as keys whose unsigned order is the numeric order,
+// packed with the complemented index so that one 64-bit maximum decides both.
+template <bool FP16>
+__global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* __restrict__ x, long long* __restrict__ out, int n) {
+  pdl_prologue();
+  __shared__ unsigned long long best_of_warp[32];
+  const uint16_t* row = x + (size_t)blockIdx.x * n;
+  auto key_of = [](uint16_t bits) -> uint32_t {
+    // 16-bit floats order like sign-magnitude integers: flip negatives, lift positives
+    const uint32_t b = bits;
+    const uint32_t nan_limit = FP16 ? 0x7C00u : 0x7F80u;
+    if ((b & 0x7FFFu) > nan_limit) return 0xFFFFu;  // NaN of either sign
+    return (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
+  };
+  unsigned long long best = 0;
+  auto take = [&](uint16_t bits, int idx) {
+    const unsigned long long cand = ((unsigned long long)key_of(bits) << 32) | (uint32_t)(~(uint32_t)idx);
+    best = cand > best ? cand : best;
+  };
+  const int vecs = (((uintptr_t)row & 15) == 0) ? n / 8 : 0;  // 16-byte loads where the row allows them
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    const uint4 q = *reinterpret_cast<const uint4*>(row + (size_t)v * 8);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      take((uint16_t)(w[j] & 0xFFFFu), v * 8 + 2 * j);
+      take((uint16_t)(w[j] >> 16), v * 8 + 2 * j + 1);
+    }
+  }
+  for (int i = vecs * 8 + threadIdx.x; i < n; i += blockDim.x) take(row[i], i);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) best_of_warp[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < (blockDim.x >> 5) ? best_of_warp[threadIdx.x] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = (long long)(~(uint32_t)(best & 0xFFFFFFFFull));
+  }
+}
+
 // out[row, j] = silu(gate) * up; the columns of gate_up alternate `group` gate values and the
 // `group` matching up values.
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out, int width,
@@ -444,6 +494,19 @@ extern "C" int fdk_sumsq_tiles(const void* h, float* sumsq, int rows, int width,
   const int tiles = (width + 63) / 64;
   return launch_pdl(sumsq_tiles_kernel, dim3((tiles + 7) / 8, rows), dim3(256), 0, (cudaStream_t)stream,
                     (const uint16_t*)h, sumsq, width, tiles);
+}
+
+extern "C" int fdk_argmax(const void* x, void* out, int rows, int n, int dtype, void* stream) {
+  FDK_CHECK_ARG(x && out, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(rows > 0 && n > 0, FDK_ERR_BAD_ARG, "non-positive size");
+  FDK_CHECK_ARG(dtype == FDK_DTYPE_BF16 || dtype == FDK_DTYPE_F16, FDK_ERR_BAD_ARG, "dtype=%d", dtype);
+  FDK_CHECK_ARG(((uintptr_t)x & 1) == 0 && ((uintptr_t)out & 7) == 0, FDK_ERR_ALIGN, "x must be 2-byte, out 8-byte aligned");
+  if (dtype == FDK_DTYPE_F16) {
+    return launch_pdl(argmax_kernel<true>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, (const uint16_t*)x,
+                      (long long*)out, n);
+  }
+  return launch_pdl(argmax_kernel<false>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, (const uint16_t*)x,
+                    (long long*)out, n);
 }
 
 extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, int group, void* stream) {

@@ -494,17 +494,27 @@ class Generator:
                 self.input_ids[:, context - 1] = prompt_ids[:, -1]
                 model.fill_cache_synthetic(context - 1)
                 logits = model(self.input_ids[:, context - 1].contiguous())
-            self.last_token = logits.argmax(dim=-1)
+            self.last_token = torch.empty(batch_size, dtype=torch.long, device=device)
+            self._choose(logits)
             self.input_ids[:, context] = self.last_token
         self.last_index = torch.tensor(context, device=device)
         self.last_logits = logits
         model.check_status()
 
+    def _choose(self, logits: Tensor) -> None:
+        """Greedy choice (`logits.argmax(dim=-1)` in the reference, src/fdk/models.py:252) into
+        `last_token`, by the native kernel (torch's row-wise argmax runs one thread block over the
+        whole vocabulary: ~45 us at 128 k entries against ~5)."""
+        if logits.is_cuda and logits.dim() == 2 and logits.is_contiguous() and logits.dtype in (torch.bfloat16, torch.float16):
+            native.argmax(logits, self.last_token)
+        else:
+            self.last_token[...] = logits.argmax(dim=-1)
+
     def step(self) -> None:
         with torch.no_grad():
             logits = self.model(self.last_token)
             self.last_logits = logits
-            self.last_token[...] = logits.argmax(dim=-1)
+            self._choose(logits)
             self.last_index += 1
             token = self.last_token[:, None]
             self.input_ids.scatter_(1, self.last_index[None, None].expand_as(token), token)

@@ -114,6 +114,7 @@ _SIGNATURES = {
     "fdk_silu_mul": (ctypes.c_int, [ctypes.c_void_p] * 2 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "fdk_decode_attention_scratch": (ctypes.c_int, [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_size_t)] * 2),
     "fdk_decode_attention": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_int] * 6 + [ctypes.c_void_p]),
+    "fdk_argmax": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "fdk_decode_attention_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]),
     "fdk_workspace_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "fdk_linear_lut": (
@@ -467,6 +468,14 @@ def attention_scratch(batch: int, q_heads: int, kv_heads: int, splits: int, devi
     check(lib().fdk_decode_attention_scratch(batch, q_heads, kv_heads, splits, ctypes.byref(a), ctypes.byref(b)))
     # both zero-filled once: the slices' words are tagged with the use count kept in the counters
     return (torch.zeros(a.value // 4, dtype=torch.float32, device=device), torch.zeros(b.value // 4, dtype=torch.int32, device=device))
+
+
+def argmax(x: Tensor, out: Tensor) -> None:
+    """out[r] = argmax of row r of x [rows, n] (bf16 or fp16; lowest index among equals)."""
+    _require_cuda(x, out)
+    assert x.dim() == 2 and x.is_contiguous() and out.dtype == torch.int64 and out.is_contiguous() and out.numel() == x.shape[0]
+    with torch.cuda.device(x.device):
+        check(lib().fdk_argmax(x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], dtype_code(x.dtype), _stream()))
 
 
 def attention_status(counters: Tensor, batch: int, kv_heads: int) -> int:

@@ -169,6 +169,11 @@ int fdk_rope_append_paired(const void* qkv, const void* pos, void* q_out, void* 
                            int rows, int q_heads, int kv_heads, int head_dim, int max_len, float theta,
                            void* stream);
 
+/* out[r] (device int64) = index of the largest of x[r][0 .. n), the lowest index among equals,
+ * a NaN counting as the largest: the token choice of the reference's greedy Generator.step
+ * (`logits.argmax(dim=-1)`, src/fdk/models.py:252).  x bf16 or fp16, rows of n contiguous. */
+int fdk_argmax(const void* x, void* out, int rows, int n, int dtype, void* stream);
+
 /* out[rows, width] = silu(gate) * up, gate_up [rows, 2 width] being the output of the fused
  * gate|up projection, whose columns alternate `group` gate values and the `group` matching up
  * values (group = width: all gates, then all ups; group = 32: the row order that

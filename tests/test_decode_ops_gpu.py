@@ -152,3 +152,27 @@ def test_rope_append_outside_the_cache_writes_nothing(native, pos_value):
     torch.cuda.synchronize()
     assert bool((k_cache == 7.0).all()) and bool((v_cache == 7.0).all()) and bool((guard == 7.0).all())
     assert not bool(torch.isnan(q_out.float()).any())  # q is still rotated and written
+
+
+@pytest.mark.parametrize("rows,n", [(1, 128256), (3, 1000), (16, 32000), (2, 7)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_argmax_matches_torch(native, rows, n, dtype):
+    """fdk_argmax = torch.argmax on rows without ties; the lowest index among equal maxima; a NaN wins."""
+    gen = torch.Generator(device="cuda").manual_seed(rows * n)
+    x = torch.randn((rows, n), generator=gen, device="cuda").to(dtype)
+    out = torch.full((rows,), -1, dtype=torch.int64, device="cuda")
+    native.argmax(x, out)
+    picked = x.gather(1, out[:, None])[:, 0]
+    assert torch.equal(picked, x.max(dim=1).values)          # a maximum ...
+    is_max = x == x.max(dim=1, keepdim=True).values
+    first = torch.where(is_max, torch.arange(n, device="cuda")[None, :], n).min(dim=1).values
+    assert torch.equal(out, first)                           # ... and the first of them
+    # ties, negative rows and a NaN
+    y = torch.full((3, 100), -2.0, device="cuda", dtype=dtype)
+    y[0, 40] = y[0, 70] = 5.0
+    y[1, 99] = -1.0
+    y[2, 13] = float("nan")
+    y[2, 50] = 9.0
+    out = torch.empty(3, dtype=torch.int64, device="cuda")
+    native.argmax(y, out)
+    assert out.tolist() == [40, 99, 13]
