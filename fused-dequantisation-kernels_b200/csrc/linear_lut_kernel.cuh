@@ -618,8 +618,16 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       }
     }
     if (warp < p.m) {  // one warp per batch row: partial sums added in a fixed order
+      // four loads per lane in flight (128 tiles, i.e. 8192 columns, in one trip to L2)
       float ssum = 0.f;
-      for (int j = lane; j < p.norm_tiles; j += 32) ssum += __ldcg(p.norm_ss + (size_t)warp * p.norm_tiles + j);
+      const float* ss_row = p.norm_ss + (size_t)warp * p.norm_tiles;
+#pragma unroll 1
+      for (int j0 = lane; j0 < p.norm_tiles; j0 += 128) {
+        float part[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) part[u] = j0 + 32 * u < p.norm_tiles ? __ldcg(ss_row + j0 + 32 * u) : 0.f;
+        ssum += (part[0] + part[1]) + (part[2] + part[3]);
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
       if (lane == 0) inv_smem[warp] = rsqrtf(ssum / (float)p.k + p.norm_eps);
