@@ -256,7 +256,9 @@ __global__ void rope_table_kernel(const long long* __restrict__ pos_ptr, uint32_
 
 // sumsq[row][t] = sum of squares of h[row][64 t .. 64 t + 63]; one warp per (row, tile), lane l
 // taking elements l and l + 32, added in the order of the projection kernel's residual output.
-__global__ void sumsq_tiles_kernel(const uint16_t* __restrict__ h, float* __restrict__ sumsq, int width, int tiles) {
+// With `weight`: also x[row][col] = bf16(weight[col] * h[row][col]) (deferred RMSNorm).
+__global__ void sumsq_tiles_kernel(const uint16_t* __restrict__ h, float* __restrict__ sumsq, int width, int tiles,
+                                   const uint16_t* __restrict__ weight, uint16_t* __restrict__ x) {
   pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), row = blockIdx.y;
@@ -268,6 +270,7 @@ __global__ void sumsq_tiles_kernel(const uint16_t* __restrict__ h, float* __rest
     if (col < width) {
       const float v = to_float<false>(h[(size_t)row * width + col]);
       sq = fmaf(v, v, sq);
+      if (weight != nullptr) x[(size_t)row * width + col] = from_float<false>(v * to_float<false>(weight[col]));
     }
   }
   sq = warp_sum(sq);
@@ -493,7 +496,16 @@ extern "C" int fdk_sumsq_tiles(const void* h, float* sumsq, int rows, int width,
   FDK_CHECK_ARG(rows > 0 && width > 0, FDK_ERR_BAD_ARG, "non-positive size");
   const int tiles = (width + 63) / 64;
   return launch_pdl(sumsq_tiles_kernel, dim3((tiles + 7) / 8, rows), dim3(256), 0, (cudaStream_t)stream,
-                    (const uint16_t*)h, sumsq, width, tiles);
+                    (const uint16_t*)h, sumsq, width, tiles, (const uint16_t*)nullptr, (uint16_t*)nullptr);
+}
+
+extern "C" int fdk_norm_prepare(const void* h, const void* weight, void* x, float* sumsq, int rows, int width,
+                                void* stream) {
+  FDK_CHECK_ARG(h && weight && x && sumsq, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(rows > 0 && width > 0, FDK_ERR_BAD_ARG, "non-positive size");
+  const int tiles = (width + 63) / 64;
+  return launch_pdl(sumsq_tiles_kernel, dim3((tiles + 7) / 8, rows), dim3(256), 0, (cudaStream_t)stream,
+                    (const uint16_t*)h, sumsq, width, tiles, (const uint16_t*)weight, (uint16_t*)x);
 }
 
 extern "C" int fdk_argmax(const void* x, void* out, int rows, int n, int dtype, void* stream) {

@@ -140,6 +140,20 @@ static int linear_lut_impl(const void* x, const void* tiled, const void* lut, co
       FDK_CHECK_ARG(fu->resid_sumsq != nullptr, FDK_ERR_BAD_ARG, "resid_sumsq is null");
       p.resid_h = (uint16_t*)fu->resid_h;
       p.resid_ss = fu->resid_sumsq;
+      if (fu->resid_norm_weight != nullptr) {
+        FDK_CHECK_ARG(fu->resid_x != nullptr, FDK_ERR_BAD_ARG, "resid_norm_weight without resid_x");
+        p.resid_w = (const uint16_t*)fu->resid_norm_weight;
+        p.resid_x = (uint16_t*)fu->resid_x;
+      }
+    } else {
+      FDK_CHECK_ARG(fu->resid_norm_weight == nullptr, FDK_ERR_BAD_ARG, "resid_norm_weight goes with the residual output");
+    }
+    if (fu->scale_sumsq != nullptr) {
+      FDK_CHECK_ARG(!norm, FDK_ERR_BAD_ARG, "the RMSNorm is applied to the input or to the output, not both");
+      FDK_CHECK_ARG(fu->scale_tiles > 0, FDK_ERR_BAD_ARG, "scale_tiles=%d", fu->scale_tiles);
+      p.scale_ss = fu->scale_sumsq;
+      p.scale_tiles = fu->scale_tiles;
+      p.scale_eps = fu->scale_eps;
     }
     if (rope) {
       FDK_CHECK_ARG(fu->rope_table && fu->q_out && fu->k_cache && fu->v_cache, FDK_ERR_BAD_ARG, "incomplete rotary fusion");

@@ -269,10 +269,10 @@ __device__ __forceinline__ bool fetch_foreign(const LinearParams& p, float* stas
 // this row tile: per warp one block of E = NB * 4 * SW floats laid out
 // [sub-tile][n-tile][t][g][4].  `foreign`: stash holds the other CTAs' sums (owner of a split
 // tile).  `publish`: the sums go to `mine` in the workspace as tagged words and nothing else is done.
-template <int NB, int DEPOSITS, bool FP16, int EPI>
+template <int NB, int DEPOSITS, bool FP16, int EPI, bool SCALE>
 __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots, uint16_t* gathered,
                                             const float* stash, uint2* mine, bool foreign, bool publish, uint32_t tag,
-                                            int rt, uint32_t push_seq, const uint32_t (&hpre)[8 * NB],
+                                            int rt, uint32_t push_seq, const uint32_t (&hpre)[8 * NB], uint32_t wpre,
                                             const uint8_t* smem_head) {
   const int lane = threadIdx.x & 31;
   const int tt = p.slot_t, sw = 32 * tt;
@@ -301,6 +301,14 @@ __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots,
     if (foreign) {
       const float4 f = *reinterpret_cast<const float4*>(stash + e0);
       acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
+    }
+    if (SCALE && !publish) {
+      // deferred RMSNorm: the complete sums of batch row b are multiplied by the row's factor
+      // (element e = ((blk * tt + tq) * 8 + g) * 4 + i holds batch row 8 nb + 2 tq + (i & 1))
+      const float* inv = reinterpret_cast<const float*>(smem_head + kSmemInv);
+      const int bt = e0 >> 5, blk = bt / tt, tq = bt - blk * tt, nb = blk % NB;
+      const float f0 = inv[8 * nb + 2 * tq], f1 = inv[8 * nb + 2 * tq + 1];
+      acc[0] *= f0; acc[1] *= f1; acc[2] *= f0; acc[3] *= f1;
     }
     if (publish) {
 #pragma unroll
@@ -387,6 +395,10 @@ __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots,
               p.resid_h[(size_t)b * p.n + row] = hnew;
               const float hf = to_float<FP16>(hnew);
               sq = fmaf(hf, hf, sq);
+              if (p.resid_w != nullptr) {  // the next RMSNorm's weight folded in: x of the next projection
+                const float w = to_float<FP16>((uint16_t)(half ? wpre >> 16 : wpre & 0xFFFFu));
+                p.resid_x[(size_t)b * p.n + row] = from_float<FP16>(hf * w);
+              }
             }
           }
 #pragma unroll
@@ -516,7 +528,10 @@ __device__ __forceinline__ bool wait_shared_word(volatile int* word, int want) {
 }
 
 // WARPS compute warps and one finisher warp (the last one).
-// NORM: x is the RMSNorm of p.norm_h, applied while x is staged (needs XRES).
+// NORM: kNormNone; kNormInput: x is the RMSNorm of p.norm_h, applied while x is staged (needs
+// resident x); kNormOutput: the deferred form -- x comes with the norm weight folded in and the
+// complete sums are multiplied by the batch rows' norm factors.
+constexpr int kNormNone = 0, kNormInput = 1, kNormOutput = 2;
 // XM: where a warp finds x -- kXDirect: fragments read from L2 as they are needed; kXResident:
 // all of x copied once per CTA into shared memory; kXStreamed: every lane copies the fragments
 // of its warp's next slab into a two-stage ring of its own with cp.async while it works on the
@@ -527,7 +542,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM, bool TEAM>
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, int NORM, bool TEAM>
 __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     linear_lut_kernel(const __grid_constant__ LinearParams p, const __grid_constant__ InlineLut<BITS> inl) {
   using L = Layout<BITS>;
@@ -593,19 +608,13 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     uses_last = ld_relaxed_s32(p.counters + rt_last);
     // number of this push = reduces completed before this launch (the reduce kernel counts)
     if (EPI == kEpiPush) push_seq = (uint32_t)ld_relaxed_s32(reinterpret_cast<const int*>(p.seq));
-    if constexpr (EPI == kEpiRope) {  // the position and its cos/sin table, kept in shared memory
-      uint32_t* table = reinterpret_cast<uint32_t*>(smem_raw + kSmemRope);
-      table[lane] = __ldcg(p.rope_table + lane);
-      table[lane + 32] = __ldcg(p.rope_table + lane + 32);
-      if (lane == 0) *reinterpret_cast<long long*>(smem_raw + kSmemPos) = *reinterpret_cast<const volatile long long*>(p.rope_pos);
-    }
   }
-  if constexpr (XM == kXResident && NORM) {
+  if constexpr (XM == kXResident && NORM == kNormInput) {
     // x = norm_w * round(h * rsqrt(mean(h^2) + eps)), the roundings of the separate RMSNorm
     // kernel; mean(h^2) from the sums of squares the previous projection left per 64 elements.
     // A thread's first two vectors of h and of the norm weight are requested before the
     // factors are computed, so that all of it costs one round trip to L2.
-    static_assert(!NORM || XM == kXResident, "the norm is applied while x is staged in shared memory");
+    static_assert(NORM != kNormInput || XM == kXResident, "the norm is applied while x is staged in shared memory");
     const int vecs = p.k >> 3, total = p.m * vecs;
     float* inv_smem = reinterpret_cast<float*>(smem_raw + kSmemInv);
     uint4 hv[2], wv[2];
@@ -715,6 +724,49 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
   if (warp == W) {
     // ---- finisher ----
     float* stash = reinterpret_cast<float*>(smem_raw + p.stash_off);
+    // what only this warp's epilogues read is fetched here, after the CTA-wide barrier, so that
+    // the compute warps do not wait for these trips to L2
+    if constexpr (NORM == kNormOutput) {
+      // deferred RMSNorm: factor of every batch row from the per-tile sums of squares (four loads
+      // per lane in flight, fixed order), kept in shared memory for this warp's epilogues
+      float* inv_smem = reinterpret_cast<float*>(smem_raw + kSmemInv);
+#pragma unroll 1
+      for (int b0 = 0; b0 < 8 * NB; b0 += 4) {  // four batch rows at a time: sixteen loads per lane in flight
+        float ssum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int j0 = lane; j0 < p.scale_tiles; j0 += 128) {
+          float part[4][4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              part[i][u] = (b0 + i < p.m && j0 + 32 * u < p.scale_tiles)
+                               ? __ldcg(p.scale_ss + (size_t)(b0 + i) * p.scale_tiles + j0 + 32 * u)
+                               : 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) ssum[i] += (part[i][0] + part[i][1]) + (part[i][2] + part[i][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ssum[i] += __shfl_xor_sync(0xffffffffu, ssum[i], o);
+          if (lane == 0) inv_smem[b0 + i] = b0 + i < p.m ? rsqrtf(ssum[i] / (float)p.k + p.scale_eps) : 0.f;
+        }
+        if (b0 + 4 >= p.m) {  // the remaining rows are unused: zero factors
+          if (lane == 0)
+            for (int b = b0 + 4; b < 8 * NB; ++b) inv_smem[b] = 0.f;
+          break;
+        }
+      }
+      __syncwarp();
+    }
+    if constexpr (EPI == kEpiRope) {  // the position and its cos/sin table, kept in shared memory
+      uint32_t* table = reinterpret_cast<uint32_t*>(smem_raw + kSmemRope);
+      table[lane] = __ldcg(p.rope_table + lane);
+      table[lane + 32] = __ldcg(p.rope_table + lane + 32);
+      if (lane == 0) *reinterpret_cast<long long*>(smem_raw + kSmemPos) = *reinterpret_cast<const volatile long long*>(p.rope_pos);
+    }
+    __syncwarp();
     for (int rt = rt_first; rt <= rt_last; ++rt) {
       const int seg = rt - rt_first;
       const int set = p.slot_sets == 2 ? (seg & 1) : 0;
@@ -726,10 +778,17 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       const int uses = rt == rt_first ? uses_first : uses_last;  // only those two can be split
       const uint32_t tag = ((uint32_t)(uses + 1) << 12) | (uint32_t)rt;
       uint32_t hpre[8 * NB] = {};
+      uint32_t wpre = 0;  // the next norm's weights of rows lane and lane + 32 of the tile
       // the tile's part of the residual stream, requested before the other CTAs' sums are polled
       // and the deposits come in
       if constexpr (EPI == kEpiResid) {
         if (full || owner) {
+          if (p.resid_w != nullptr) {
+            const int row = rt * kTileRows + lane;
+            const uint16_t lo = row < p.n ? __ldg(p.resid_w + row) : (uint16_t)0;
+            const uint16_t hi = row + 32 < p.n ? __ldg(p.resid_w + row + 32) : (uint16_t)0;
+            wpre = (uint32_t)lo | ((uint32_t)hi << 16);
+          }
 #pragma unroll
           for (int b = 0; b < 8 * NB; ++b) {
             if (b < p.m) {
@@ -748,11 +807,11 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
       if (!wait_shared_word(&esync->count[set], W)) timed_out = true;
       __threadfence_block();
       if constexpr (team) {  // one block of sums, made by the compute warps
-        tile_finish<NB, 1, FP16, EPI>(p, my_slots, gathered, stash, p.partial + (size_t)cta * (512 * NB), !full && owner,
-                                      !full && !owner, tag, rt, push_seq, hpre, smem_raw);
+        tile_finish<NB, 1, FP16, EPI, NORM == kNormOutput>(p, my_slots, gathered, stash, p.partial + (size_t)cta * (512 * NB), !full && owner,
+                                      !full && !owner, tag, rt, push_seq, hpre, wpre, smem_raw);
       } else {
-        tile_finish<NB, WARPS, FP16, EPI>(p, my_slots, gathered, stash, p.partial + (size_t)cta * (512 * NB),
-                                          !full && owner, !full && !owner, tag, rt, push_seq, hpre, smem_raw);
+        tile_finish<NB, WARPS, FP16, EPI, NORM == kNormOutput>(p, my_slots, gathered, stash, p.partial + (size_t)cta * (512 * NB),
+                                          !full && owner, !full && !owner, tag, rt, push_seq, hpre, wpre, smem_raw);
       }
       __syncwarp();
       if (lane == 0) {
@@ -1071,7 +1130,7 @@ int launch_kernel(Kernel kernel, std::atomic<size_t> (&configured)[64], const Li
   return FDK_OK;
 }
 
-template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM, bool TEAM>
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, int NORM, bool TEAM>
 int launch_team(const LinearParams& p, const InlineLut<BITS>& inl, int grid, size_t smem, unsigned flags,
                 cudaStream_t stream) {
   static std::atomic<size_t> configured[64] = {};
@@ -1080,7 +1139,7 @@ int launch_team(const LinearParams& p, const InlineLut<BITS>& inl, int grid, siz
 }
 
 // Two n-tiles always run in team mode; one n-tile from five batch rows on.
-template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, bool NORM>
+template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, int NORM>
 int launch_instance(const LinearParams& p, const InlineLut<BITS>& inl, int grid, size_t smem, unsigned flags,
                     cudaStream_t stream) {
   if constexpr (NB == 1) {
@@ -1111,27 +1170,35 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
   const int epi = p.tp > 0 ? kEpiPush : p.silu ? kEpiSilu : p.resid_h != nullptr ? kEpiResid : p.rope_pos != nullptr ? kEpiRope : kEpiStore;
 #define FDK_LAUNCH(EPI_, XM_, NORM_) \
   return launch_instance<BITS, NB, WARPS, FP16, EPI_, XM_, NORM_>(p, inl, grid, smem, flags, stream)
-#define FDK_LAUNCH_X(EPI_)                                 \
-  do {                                                     \
-    if (xm == kXResident) FDK_LAUNCH(EPI_, kXResident, false); \
-    if (xm == kXStreamed) FDK_LAUNCH(EPI_, kXStreamed, false); \
-    FDK_LAUNCH(EPI_, kXDirect, false);                     \
+#define FDK_LAUNCH_X(EPI_, NORM_)                                 \
+  do {                                                            \
+    if (xm == kXResident) FDK_LAUNCH(EPI_, kXResident, NORM_);    \
+    if (xm == kXStreamed) FDK_LAUNCH(EPI_, kXStreamed, NORM_);    \
+    FDK_LAUNCH(EPI_, kXDirect, NORM_);                            \
   } while (0)
   if constexpr (!FP16) {  // the decode fusions exist for bf16 only
     if (norm) {
-      if (epi == kEpiStore) FDK_LAUNCH(kEpiStore, kXResident, true);
-      if (epi == kEpiSilu) FDK_LAUNCH(kEpiSilu, kXResident, true);
-      if (epi == kEpiRope) FDK_LAUNCH(kEpiRope, kXResident, true);
+      if (epi == kEpiStore) FDK_LAUNCH(kEpiStore, kXResident, kNormInput);
+      if (epi == kEpiSilu) FDK_LAUNCH(kEpiSilu, kXResident, kNormInput);
+      if (epi == kEpiRope) FDK_LAUNCH(kEpiRope, kXResident, kNormInput);
       FDK_CHECK_ARG(false, FDK_ERR_BAD_ARG, "the fused RMSNorm goes with the plain, SiLU or rotary output only");
     }
-    if (epi == kEpiResid) FDK_LAUNCH_X(kEpiResid);
-    if (epi == kEpiRope) FDK_LAUNCH_X(kEpiRope);
+    if (p.scale_ss != nullptr) {
+      if (epi == kEpiStore) FDK_LAUNCH_X(kEpiStore, kNormOutput);
+      if (epi == kEpiSilu) FDK_LAUNCH_X(kEpiSilu, kNormOutput);
+      if (epi == kEpiRope) FDK_LAUNCH_X(kEpiRope, kNormOutput);
+      if (epi == kEpiResid) FDK_LAUNCH_X(kEpiResid, kNormOutput);
+      FDK_CHECK_ARG(false, FDK_ERR_BAD_ARG, "the deferred RMSNorm does not go with the tensor-parallel push");
+    }
+    if (epi == kEpiResid) FDK_LAUNCH_X(kEpiResid, kNormNone);
+    if (epi == kEpiRope) FDK_LAUNCH_X(kEpiRope, kNormNone);
   } else {
-    FDK_CHECK_ARG(!norm && epi != kEpiResid && epi != kEpiRope, FDK_ERR_BAD_ARG, "the decode fusions take bf16 only");
+    FDK_CHECK_ARG(!norm && p.scale_ss == nullptr && epi != kEpiResid && epi != kEpiRope, FDK_ERR_BAD_ARG,
+                  "the decode fusions take bf16 only");
   }
-  if (epi == kEpiPush) FDK_LAUNCH_X(kEpiPush);
-  if (epi == kEpiSilu) FDK_LAUNCH_X(kEpiSilu);
-  FDK_LAUNCH_X(kEpiStore);
+  if (epi == kEpiPush) FDK_LAUNCH_X(kEpiPush, kNormNone);
+  if (epi == kEpiSilu) FDK_LAUNCH_X(kEpiSilu, kNormNone);
+  FDK_LAUNCH_X(kEpiStore, kNormNone);
 #undef FDK_LAUNCH_X
 #undef FDK_LAUNCH
 }

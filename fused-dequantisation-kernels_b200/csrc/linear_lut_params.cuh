@@ -45,6 +45,14 @@ struct LinearParams {
   // the new h over the tile's 64 rows
   uint16_t* resid_h;
   float* resid_ss;          // [m, ceil(n / 64)]
+  // deferred RMSNorm, producer side (with the residual output): resid_x[m, n] = bf16(resid_w[row] * h)
+  const uint16_t* resid_w;  // [n] or null
+  uint16_t* resid_x;
+  // deferred RMSNorm, consumer side: the complete sums of batch row b are multiplied by
+  // rsqrt(sum of scale_ss[b][0 .. scale_tiles) / k + scale_eps) before they are rounded
+  const float* scale_ss;    // [m, scale_tiles] or null
+  int scale_tiles;
+  float scale_eps;
   // rotary (rope_pos != null): the rows are the fused q|k|v projection with every q and k head's rows
   // ordered [0..31, 64..95, 32..63, 96..127]; q is rotated into q_out, k rotated and v copied into the
   // caches at *rope_pos (nothing is written for a position outside [0, max_len))

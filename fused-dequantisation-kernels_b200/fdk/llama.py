@@ -117,6 +117,11 @@ class LlamaDecoder(nn.Module):
         self.kv_heads = dims.num_key_value_heads // tp.size
         assert dims.num_key_value_heads % tp.size == 0, "KV heads must split evenly over the ranks"
         assert dims.head_dim == 128
+        # how the fused decode step applies its RMSNorms: by the reading projection while it stages
+        # x, with the framework model's roundings (False), or split between the projections that
+        # write and read the residual stream (True: ~0.5 us less per norm, one bf16 rounding per
+        # element of x placed differently; measured +4 % tokens/s at batch 4, nothing at batch 1)
+        self.deferred_norm = False
 
     # ---- construction -----------------------------------------------------------------
 
@@ -234,10 +239,12 @@ class LlamaDecoder(nn.Module):
         if native_layers and batch <= 16:
             self.rope_tab = torch.zeros(64, device=dev, dtype=torch.int32)
             self.sumsq = torch.zeros((batch, h // 64), device=dev, dtype=torch.float32)
+            self.hw = torch.zeros((batch, h), device=dev, dtype=torch.bfloat16)  # norm weight * residual stream
             normed = [m for l in self.layers for m in (l.qkv, l.gate_up)]
             # up to 8 rows (one n-tile of the fused kernel); from 9 rows on the tensor-core kernel
             # with separate glue kernels is the faster step
-            if self.tp.size == 1 and batch <= 8 and h % 64 == 0 and all(native.linear_norm_fits(batch, h, m.bits) for m in normed):
+            fits = self.deferred_norm or all(native.linear_norm_fits(batch, h, m.bits) for m in normed)
+            if self.tp.size == 1 and batch <= 8 and h % 64 == 0 and fits:
                 self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
             else:  # tensor parallel: the norms add the ranks' partial sums; the rotary epilogue still applies
                 self.rope_fusions = [self._layer_fusions(i, rope_only=True) for i in range(len(self.layers))]
@@ -281,10 +288,26 @@ class LlamaDecoder(nn.Module):
         rope = dict(rope_pos=self.position.data_ptr(), rope_table=self.rope_tab.data_ptr(), q_out=self.q.data_ptr(),
                     k_cache=self.k_cache[i].data_ptr(), v_cache=self.v_cache[i].data_ptr(), q_heads=self.q_heads,
                     kv_heads=self.kv_heads, max_len=self.max_len)
+        if self.deferred_norm:
+            # the norm split in two: the projection that writes the residual stream also writes
+            # norm weight * h (the x of the next projection), which scales its sums by the norm factor
+            scale = dict(scale_sumsq=self.sumsq.data_ptr(), scale_tiles=self.sumsq.shape[1], scale_eps=eps)
+            after = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else None
+
+            def folded(weight: Tensor | None) -> dict:
+                return {} if weight is None else dict(resid_norm_weight=weight.data_ptr(), resid_x=self.hw.data_ptr())
+
+            return (
+                native.LinearFusion(**scale, **rope),                        # q|k|v of hw
+                native.LinearFusion(**resid, **folded(layer.post_norm)),     # o
+                native.LinearFusion(**scale),                                # gate|up of hw
+                native.LinearFusion(**resid, **folded(after)),               # down
+            )
         return (
             native.LinearFusion(**norm(layer.input_norm), **rope),  # q|k|v
-            native.LinearFusion(**resid),                           # o and down
+            native.LinearFusion(**resid),                           # o
             native.LinearFusion(**norm(layer.post_norm)),           # gate|up
+            native.LinearFusion(**resid),                           # down
         )
 
     def _gated(self, layer: DecoderLayer) -> None:
@@ -408,21 +431,29 @@ class LlamaDecoder(nn.Module):
         return logits
 
     def _forward_glue_fused(self) -> Tensor:
-        """The same step in five kernels per layer: the q|k|v projection applies the input RMSNorm
-        while it stages x and the rotary embedding + KV append in its epilogue; the o and down
-        projections add their result to the residual stream and leave the sums of squares for the
-        next norm; the gate|up projection applies the post-attention norm and SiLU(gate) * up."""
+        """The same step in five kernels per layer: the q|k|v projection does the rotary embedding
+        + KV append in its epilogue; the o and down projections add their result to the residual
+        stream and leave the sums of squares for the next norm; the gate|up projection writes
+        SiLU(gate) * up.  The RMSNorms are either applied by the q|k|v and gate|up projections
+        while they stage x (the default), or (`deferred_norm`) split: the
+        projection that writes the residual stream also writes norm weight * h, and the one that
+        reads it multiplies its sums by the norm factor."""
         dims, eps, b = self.dims, self.dims.rms_norm_eps, self.batch
         native.rope_table(self.position, self.rope_tab, dims.rope_theta)
-        native.sumsq_tiles(self.hidden, self.sumsq)
+        if self.deferred_norm:
+            native.norm_prepare(self.hidden, self.layers[0].input_norm, self.hw, self.sumsq)
+            normed_x = self.hw
+        else:
+            native.sumsq_tiles(self.hidden, self.sumsq)
+            normed_x = None  # the projection normalises self.hidden itself while it stages x
         for i, layer in enumerate(self.layers):
-            f_qkv, f_resid, f_gate = self.fusions[i]
-            layer.qkv.fused(None, None, b, f_qkv)
+            f_qkv, f_o, f_gate, f_down = self.fusions[i]
+            layer.qkv.fused(normed_x, None, b, f_qkv)
             native.decode_attention(self.q, self.k_cache[i], self.v_cache[i], self.position, self.attn,
                                     self.attn_scratch, self.attn_counters, self.q_heads, self.kv_heads, self.splits)
-            layer.o.fused(self.attn, None, b, f_resid)
-            layer.gate_up.fused(None, self.act, b, f_gate, silu_pairs=True)
-            layer.down.fused(self.act, None, b, f_resid)
+            layer.o.fused(self.attn, None, b, f_o)
+            layer.gate_up.fused(normed_x, self.act, b, f_gate, silu_pairs=True)
+            layer.down.fused(self.act, None, b, f_down)
         native.rmsnorm(self.hidden, None, self.final_norm, self.normed, eps)
         logits = self._logits()
         self.position += 1

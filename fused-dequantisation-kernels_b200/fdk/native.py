@@ -65,6 +65,11 @@ class LinearFusion(ctypes.Structure):
         ("q_heads", ctypes.c_int),
         ("kv_heads", ctypes.c_int),
         ("max_len", ctypes.c_int),
+        ("resid_norm_weight", ctypes.c_void_p),
+        ("resid_x", ctypes.c_void_p),
+        ("scale_sumsq", ctypes.c_void_p),
+        ("scale_tiles", ctypes.c_int),
+        ("scale_eps", ctypes.c_float),
     ]
 
 
@@ -76,6 +81,7 @@ _SIGNATURES = {
     ),
     "fdk_rope_table": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p]),
     "fdk_sumsq_tiles": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "fdk_norm_prepare": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "fdk_tp_exchange_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_longlong]),
     "fdk_tp_buffer_create": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
     "fdk_tp_buffer_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
@@ -333,6 +339,18 @@ def rope_table(pos: Tensor, table: Tensor, theta: float) -> None:
     assert pos.dtype == torch.int64 and table.dtype == torch.int32 and table.numel() == 64
     with torch.cuda.device(pos.device):
         check(lib().fdk_rope_table(pos.data_ptr(), table.data_ptr(), theta, _stream()))
+
+
+def norm_prepare(h: Tensor, weight: Tensor, x: Tensor, sumsq: Tensor) -> None:
+    """x = bf16(weight * h) and sumsq[rows, ceil(width / 64)] = sums of squares of h per 64 elements:
+    the producer side of the deferred RMSNorm of `linear_lut_fused`."""
+    _require_cuda(h, weight, x, sumsq)
+    rows, width = h.shape
+    assert h.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+    assert h.is_contiguous() and x.is_contiguous() and x.shape == h.shape and weight.numel() == width
+    assert sumsq.dtype == torch.float32 and sumsq.shape == (rows, (width + 63) // 64)
+    with torch.cuda.device(h.device):
+        check(lib().fdk_norm_prepare(h.data_ptr(), weight.data_ptr(), x.data_ptr(), sumsq.data_ptr(), rows, width, _stream()))
 
 
 def sumsq_tiles(h: Tensor, sumsq: Tensor) -> None:

@@ -218,6 +218,17 @@ int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache
  *                copied into the caches [m, kv_heads, max_len, 128] at *rope_pos, with the
  *                roundings of fdk_rope_append; rope_table as fdk_rope_table fills it.
  *   FDK_FLAG_SILU_PAIRS may be combined with the input side.
+ *   deferred RMSNorm: instead of normalising x while it is staged (which costs ~0.6 us before the
+ *                first weight is used), the norm can be split between the projection that writes
+ *                the residual stream and the one that reads it.  Producer (residual output with
+ *                resid_norm_weight): besides h it writes resid_x = bf16(norm_weight * h).
+ *                Consumer (scale_sumsq != NULL; x = that resid_x): every complete sum of batch
+ *                row b is multiplied by rsqrt(sum of scale_sumsq[b][0 .. scale_tiles) / k +
+ *                scale_eps) before it is rounded and handed to the output side (plain, SiLU,
+ *                rotary or residual).  y = inv * (W . (w * h)) equals the norm followed by the
+ *                projection up to one bf16 rounding per element of x (w * bf16(h * inv) in the
+ *                framework model, bf16(w * h) here).  fdk_norm_prepare makes resid_x and the sums
+ *                of squares for a residual stream that no projection has written yet.
  * Results equal the unfused sequence of calls up to the order of the fp32 sum of squares. */
 typedef struct fdk_linear_fusion {
   const void* norm_h;       /* [m, k] or NULL */
@@ -233,6 +244,13 @@ typedef struct fdk_linear_fusion {
   void* k_cache;
   void* v_cache;
   int q_heads, kv_heads, max_len;
+  /* deferred RMSNorm (see above): producer side, with resid_h */
+  const void* resid_norm_weight; /* [n] or NULL */
+  void* resid_x;                 /* [m, n] = bf16(resid_norm_weight * h) */
+  /* consumer side */
+  const float* scale_sumsq;      /* [m, scale_tiles] or NULL */
+  int scale_tiles;
+  float scale_eps;
 } fdk_linear_fusion;
 
 int fdk_linear_lut_fused(const void* x, const void* tiled, const void* lut, const void* lut_host,
@@ -254,6 +272,11 @@ int fdk_rope_table(const void* pos, void* table, float theta, void* stream);
 /* sumsq[b][t] = sum of squares of h[b][64 t .. 64 t + 63] (fp32): the input-side fusion's
  * sums for a residual stream that no projection has written yet (the embedding). */
 int fdk_sumsq_tiles(const void* h, float* sumsq, int rows, int width, void* stream);
+
+/* The same sums, and x[b][j] = bf16(weight[j] * h[b][j]): the producer side of the deferred
+ * RMSNorm for the first layer of a decode step. */
+int fdk_norm_prepare(const void* h, const void* weight, void* x, float* sumsq, int rows, int width,
+                     void* stream);
 
 /* fdk_linear_lut for callers that cannot allocate device memory where they call it -- a
  * plugin inside a host runtime that owns all device allocations, or code running while a

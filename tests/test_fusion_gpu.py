@@ -124,6 +124,60 @@ def test_rotary_output(native, m, q_heads, kv_heads, k, pos_value):
         assert not bool((got_k[:, :, pos_value] == 7.0).all())
 
 
+@pytest.mark.parametrize("bits,m,n,k,mode", [(4, 1, 5120, 3072, "plain"), (4, 3, 2048, 1024, "silu"), (2, 8, 1024, 2048, "plain"),
+                                             (4, 2, 3072, 3072, "resid"), (4, 12, 640, 1024, "plain")])
+def test_deferred_norm(native, bits, m, n, k, mode):
+    """The RMSNorm split in two: fdk_norm_prepare (or a residual output with resid_norm_weight)
+    writes x = bf16(w * h) and the sums of squares; a projection with scale_sumsq multiplies its
+    sums by rsqrt(mean(h^2) + eps).  Against the norm kernel followed by the plain projection:
+    equal up to one bf16 rounding per element of x."""
+    tiled, lut, _ = _problem(native, n, k, bits, m, seed=n + k + m)
+    h = (torch.randn((m, k), device="cuda") * 3).bfloat16()
+    weight = (1 + 0.1 * torch.randn(k, device="cuda")).bfloat16()
+    eps = 1e-6
+    hw = torch.empty_like(h)
+    sumsq = torch.empty((m, k // 64), device="cuda")
+    native.norm_prepare(h, weight, hw, sumsq)
+    assert torch.equal(hw, (h.float() * weight.float()).bfloat16())
+    assert torch.allclose(sumsq.sum(-1), h.float().pow(2).sum(-1), rtol=1e-5)
+
+    normed = torch.empty_like(h)
+    native.rmsnorm(h, None, weight, normed, eps)
+    scale = dict(scale_sumsq=sumsq.data_ptr(), scale_tiles=k // 64, scale_eps=eps)
+    if mode == "resid":
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        native.linear_lut(normed, tiled, lut, y, n, k, bits)
+        r0 = torch.randn((m, n), device="cuda").bfloat16()
+        next_w = (1 + 0.1 * torch.randn(n, device="cuda")).bfloat16()
+        r, rx = r0.clone(), torch.empty_like(r0)
+        rss = torch.empty((m, (n + 63) // 64), device="cuda")
+        fusion = native.LinearFusion(resid_h=r.data_ptr(), resid_sumsq=rss.data_ptr(), resid_norm_weight=next_w.data_ptr(),
+                                     resid_x=rx.data_ptr(), **scale)
+        native.linear_lut_fused(hw, tiled, lut, None, m, n, k, bits, fusion)
+        torch.cuda.synchronize()
+        want = (r0 + y).float()
+        assert (r.float() - want).pow(2).sum().div(want.pow(2).sum()).sqrt().item() < 4e-3
+        assert torch.equal(rx, (r.float() * next_w.float()).bfloat16())  # the folded x of the next projection, bit for bit
+        assert torch.allclose(rss.sum(-1), r.float().pow(2).sum(-1), rtol=1e-4)
+    else:
+        silu = mode == "silu"
+        n_out = n // 2 if silu else n
+        want = torch.empty((m, n_out), dtype=torch.bfloat16, device="cuda")
+        if m <= 8 or silu:
+            native.linear_lut(normed, tiled, lut, want, n, k, bits, silu_pairs=silu)
+        else:  # 9 rows and more: the plain call runs the tensor-core kernel; compare with fp32 torch
+            dense = native.dequantise_tiled(tiled, lut, n, k, bits).float()
+            want = (normed.float() @ dense.T).bfloat16()
+        got = torch.full((m, n_out), float("nan"), dtype=torch.bfloat16, device="cuda")
+        native.linear_lut_fused(hw, tiled, lut, got, m, n, k, bits, native.LinearFusion(**scale), silu_pairs=silu)
+        torch.cuda.synchronize()
+        err = (got.float() - want.float()).pow(2).sum().div(want.float().pow(2).sum()).sqrt().item()
+        # the two forms round x differently (one bf16 rounding per element each way): ~2e-3 on a
+        # projection output, about twice that on a product of two of them
+        assert err < (8e-3 if silu else 5e-3), f"rel-RMS difference {err}"
+    assert native.device_status() == 0
+
+
 def test_paired_row_order_of_the_rotary_kernel(native):
     """fdk_rope_append_paired on a head given in the paired row order = fdk_rope_append on the usual order."""
     from fdk.llama import ROPE_ROW_ORDER
@@ -146,13 +200,15 @@ def test_paired_row_order_of_the_rotary_kernel(native):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("deferred", [True, False])
 @pytest.mark.parametrize("batch", [1, 5, 8, 12])
-def test_decode_step_with_and_without_fusions(batch):
+def test_decode_step_with_and_without_fusions(batch, deferred):
     from fdk import llama, models
 
     device = torch.device("cuda")
     dims = models.LlamaDims("tiny", 512, 3, 8, 2, 1024, vocab_size=640)
     model = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(4, 64), device, seed=5, std=0.05)
+    model.deferred_norm = deferred
     steps = 6
     ids = torch.randint(0, 640, (batch, steps), generator=torch.Generator().manual_seed(2)).to(device)
     logits = []
@@ -174,4 +230,5 @@ def test_decode_step_with_and_without_fusions(batch):
     err = (logits[0] - logits[1]).pow(2).sum().div(logits[1].pow(2).sum()).sqrt().item()
     # up to 8 rows both ways run the same projection kernel; from 9 rows on the unfused step takes the
     # tensor-core kernel for its q|k|v projection (bf16 W, another summation order)
-    assert err < (1e-2 if batch <= 8 else 3e-2), f"rel-RMS difference of the logits {err}"
+    # the deferred norm rounds x once per element in another place than the norm kernel does
+    assert err < (3e-2 if batch > 8 else 2e-2 if deferred else 1e-2), f"rel-RMS difference of the logits {err}"
