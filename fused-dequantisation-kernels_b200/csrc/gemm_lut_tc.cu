@@ -1,4 +1,4 @@
-// Fused dequantise + GEMM for batches of 9 and more rows, on the fifth-generation tensor
+// Fused dequantise + GEMM for batches of 17 and more rows, on the fifth-generation tensor
 // cores:  out[m, n] = x[m, k] . W[n, k]^T  with W = bf16(table value * block scale), the
 // reference's dense W (src/fdk/kernels.py:23-24) bit for bit (fp16(...) for fp16 inputs), built tile by tile in shared
 // memory and never written to HBM.
@@ -518,7 +518,7 @@ int launch_tc(TcParams p, const void* lut_host, const CUtensorMap& map, int tile
 
 }  // namespace
 
-// Batches above 8 rows.  Called by fdk_linear_lut.
+// Batches above 16 rows.  Called by fdk_linear_lut.
 int gemm_lut_tc(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out, int m, int n,
                 int k, int bits, bool fp16, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
   EncodeTiledFn encode = nullptr;

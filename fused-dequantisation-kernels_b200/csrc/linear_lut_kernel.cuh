@@ -471,7 +471,10 @@ __device__ __forceinline__ void tile_finish(const LinearParams& p, float* slots,
 
 // ---- the kernel -------------------------------------------------------------------
 template <int NB>
-constexpr int kGemvWarps = NB == 1 ? 19 : 15;  // compute warps per CTA; with the finisher a multiple of four, within the register file
+// compute warps per CTA; with the finisher a multiple of four.  One n-tile: 19 warps of 96
+// registers.  Two n-tiles need ~160 registers: 11 warps of 168 (15 warps of 128 spilled in the
+// loop and ran the 16-row case 4 us slower at every shape measured).
+constexpr int kGemvWarps = NB == 1 ? 19 : 11;
 constexpr int kXRowPad = 16;  // resident x rows are 16 bytes apart from a 128-byte multiple: no bank conflicts
 
 // A lane's share of one slab: code vectors [sub-tile][v] and the scale vector of each block.

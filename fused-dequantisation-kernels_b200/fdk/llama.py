@@ -122,6 +122,8 @@ class LlamaDecoder(nn.Module):
         # write and read the residual stream (True: ~0.5 us less per norm, one bf16 rounding per
         # element of x placed differently; measured +4 % tokens/s at batch 4, nothing at batch 1)
         self.deferred_norm = False
+        # largest batch whose projections carry the decode-step fusions (more rows: separate kernels)
+        self.fuse_rows = 8
 
     # ---- construction -----------------------------------------------------------------
 
@@ -244,7 +246,7 @@ class LlamaDecoder(nn.Module):
             # up to 8 rows (one n-tile of the fused kernel); from 9 rows on the tensor-core kernel
             # with separate glue kernels is the faster step
             fits = self.deferred_norm or all(native.linear_norm_fits(batch, h, m.bits) for m in normed)
-            if self.tp.size == 1 and batch <= 8 and h % 64 == 0 and fits:
+            if self.tp.size == 1 and batch <= self.fuse_rows and h % 64 == 0 and fits:
                 self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
             else:  # tensor parallel: the norms add the ranks' partial sums; the rotary epilogue still applies
                 self.rope_fusions = [self._layer_fusions(i, rope_only=True) for i in range(len(self.layers))]
@@ -348,7 +350,7 @@ class LlamaDecoder(nn.Module):
         position [batch, vocab]; fills the KV caches and leaves the position at T.  One pass over
         the whole prompt, as the reference's Generator does with transformers' model
         (src/fdk/models.py:241-243): the projections run the fused kernels on [batch * T, K]
-        (the tensor-core kernel from 9 rows on), the norms the RMSNorm kernel; rotary embedding and
+        (the tensor-core kernel from 17 rows on), the norms the RMSNorm kernel; rotary embedding and
         causal attention over the prompt are torch ops (this path runs once per sequence)."""
         dims, eps = self.dims, self.dims.rms_norm_eps
         batch, t = ids.shape

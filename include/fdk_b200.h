@@ -55,7 +55,7 @@ extern "C" {
 #define FDK_FLAG_SILU_PAIRS 2u /* the weight rows come in groups of 64: 32 "gate" rows, then
                            the 32 matching "up" rows; the kernel writes
                            out[m, n / 2] = silu(gate) * up instead of the [m, n] products,
-                           with the roundings of fdk_linear_lut (as it is up to 8 rows)
+                           with the roundings of fdk_linear_lut (as it is up to 16 rows)
                            followed by fdk_silu_mul (group 32).  m <= 16, n a multiple
                            of 64.                                                      */
 
@@ -136,8 +136,8 @@ int fdk_workspace_status(const void* workspace, int* status_host);
  *             kernel by value with the launch parameters, which saves the kernel a
  *             memory round trip before it can start (the table is 16 B .. 4 KB)
  *   out       [m, n] row-major
- *   m         >= 1, any m: up to 8 rows run the GEMV kernel, more the tensor-core kernel
- *             (the GEMV kernel takes up to 16 rows where one of its epilogues is asked for).
+ *   m         >= 1, any m: up to 16 rows run the GEMV kernel (one n-tile of the tensor-core
+ *             instruction up to 8 rows, two from 9), more the tcgen05 kernel.
  * Deterministic: the same inputs give the same bits on every call. */
 int fdk_linear_lut(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
                    int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
@@ -281,7 +281,7 @@ int fdk_norm_prepare(const void* h, const void* weight, void* x, float* sumsq, i
 /* fdk_linear_lut for callers that cannot allocate device memory where they call it -- a
  * plugin inside a host runtime that owns all device allocations, or code running while a
  * stream capture forbids cudaMalloc.  Same arguments as fdk_linear_lut minus the workspace, same
- * results (for 9 rows and more up to the order of the fp32 partial sums, the built-in scratch
+ * results (for 17 rows and more up to the order of the fp32 partial sums, the built-in scratch
  * having no room for the tensor-core kernel's split tiles): the scratch is an array inside the library image (1,327,104 bytes, enough for a
  * GPU of up to 160 multiprocessors; a larger GPU is refused with FDK_ERR_WORKSPACE), held by
  * every GPU that loads the library until the process exits.  The call itself allocates
