@@ -65,10 +65,10 @@ def test_push_then_reduce_equals_plain_path(native, bits, m, n, k, tp):
             got_norm = torch.empty_like(h_plain)
             native.rmsnorm_reduce(h_rank[r], exs[r], weight, got_norm, 1e-5)
             torch.cuda.synchronize()
-            if m <= 8:  # the plain products come from the same kernel
+            if m <= 16:  # the plain products come from the same kernel
                 assert np.array_equal(to_bits(h_rank[r]), to_bits(h_plain)), (step, r)
                 assert np.array_equal(to_bits(got_norm), to_bits(want_norm)), (step, r)
-            else:  # 9 rows and more: the plain products come from the tensor-core kernel
+            else:  # 17 rows and more: the plain products come from the tensor-core kernel
                 assert (h_rank[r].float() - h_plain.float()).abs().max() <= 0.05 * h_plain.float().abs().max(), (step, r)
                 h_rank[r].copy_(h_plain)  # keep the streams identical for the next step
     for r in range(tp):

@@ -57,9 +57,9 @@ def test_static_scratch_entry_matches_workspace_entry(bits, m, n, k):
         assert free_after >= free_before, f"call {call}: {free_before - free_after} bytes of device memory were allocated"
         assert native.static_status() == 0
         assert O.rmsen(O.bf16_to_f32(oracle), O.bf16_to_f32(to_bits(out))) < 4e-3
-        if m <= 8:
+        if m <= 16:
             bad = np.argwhere(to_bits(out) != to_bits(expected))
             assert len(bad) == 0, f"call {call}: {len(bad)} outputs differ, first at {bad[:4].tolist()}, status {native.static_status()}"
-        else:  # 9 rows and more run the tensor-core kernel, whose K range is split over CTAs only
+        else:  # 17 rows and more run the tensor-core kernel, whose K range is split over CTAs only
             # where the workspace has room for the parked partial tiles: another fp32 summation order
             assert (out.float() - expected.float()).abs().max() <= 0.02 * expected.float().abs().max()
