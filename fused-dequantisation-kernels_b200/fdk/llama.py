@@ -122,8 +122,11 @@ class LlamaDecoder(nn.Module):
         # write and read the residual stream (True: ~0.5 us less per norm, one bf16 rounding per
         # element of x placed differently; measured +4 % tokens/s at batch 4, nothing at batch 1)
         self.deferred_norm = False
-        # largest batch whose projections carry the decode-step fusions (more rows: separate kernels)
-        self.fuse_rows = 8
+        # largest batch whose projections carry the decode-step fusions.  Measured on the 4B shape
+        # (tokens/s fused against separate glue kernels): batch 1: 712 / 686, 2: 1367 / 1354,
+        # 4: 2117 / 2241, 8: 3256 / 3430, 16: 4269 / 5152 -- the single finisher warp goes through
+        # all batch rows, and the small glue kernels overlap their neighbours well
+        self.fuse_rows = 2
 
     # ---- construction -----------------------------------------------------------------
 
@@ -243,8 +246,7 @@ class LlamaDecoder(nn.Module):
             self.sumsq = torch.zeros((batch, h // 64), device=dev, dtype=torch.float32)
             self.hw = torch.zeros((batch, h), device=dev, dtype=torch.bfloat16)  # norm weight * residual stream
             normed = [m for l in self.layers for m in (l.qkv, l.gate_up)]
-            # up to 8 rows (one n-tile of the fused kernel); from 9 rows on the tensor-core kernel
-            # with separate glue kernels is the faster step
+            # small batches only (see fuse_rows)
             fits = self.deferred_norm or all(native.linear_norm_fits(batch, h, m.bits) for m in normed)
             if self.tp.size == 1 and batch <= self.fuse_rows and h % 64 == 0 and fits:
                 self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]

@@ -197,6 +197,7 @@ def test_decode_step_with_and_without_fusions(batch, deferred):
     dims = models.LlamaDims("tiny", 512, 3, 8, 2, 1024, vocab_size=640)
     model = llama.LlamaDecoder.random_init(dims, models.QuantisationConfig(4, 64), device, seed=5, std=0.05)
     model.deferred_norm = deferred
+    model.fuse_rows = 8  # the default keeps the fusions to smaller batches; here they are all exercised
     steps = 6
     ids = torch.randint(0, 640, (batch, steps), generator=torch.Generator().manual_seed(2)).to(device)
     logits = []
