@@ -127,6 +127,9 @@ class LlamaDecoder(nn.Module):
         # 4: 2117 / 2241, 8: 3256 / 3430, 16: 4269 / 5152 -- the single finisher warp goes through
         # all batch rows, and the small glue kernels overlap their neighbours well
         self.fuse_rows = 2
+        # largest batch whose q|k|v projection does the rotary embedding + KV append in its epilogue
+        # in the tensor-parallel step (where the norms cannot be fused)
+        self.rope_rows = 16
 
     # ---- construction -----------------------------------------------------------------
 
@@ -250,7 +253,8 @@ class LlamaDecoder(nn.Module):
             fits = self.deferred_norm or all(native.linear_norm_fits(batch, h, m.bits) for m in normed)
             if self.tp.size == 1 and batch <= self.fuse_rows and h % 64 == 0 and fits:
                 self.fusions = [self._layer_fusions(i) for i in range(len(self.layers))]
-            else:  # tensor parallel: the norms add the ranks' partial sums; the rotary epilogue still applies
+            elif batch <= self.rope_rows:
+                # tensor parallel: the norms add the ranks' partial sums; the rotary epilogue still applies
                 self.rope_fusions = [self._layer_fusions(i, rope_only=True) for i in range(len(self.layers))]
         # fused push + reduce instead of NCCL: quantised row-parallel projections, batch <= 16
         self.close()
