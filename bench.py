@@ -12,8 +12,8 @@ even a 20-step run is timed over more than 50 ms and the clock samples fall unde
 
 Printed JSON line: `value` = packed-weight bytes (codes + block scales) of all GPUs per
 second, device-timed with inputs resident in HBM; `e2e` = the same bytes per second
-through the public module call with host buffers (pinned x copied in, y copied out, per
-GEMV); `roofline` relates the per-launch time to the measured HBM copy bandwidth;
+through the module's host-buffer call `QuantisedLinear.forward_host` (one C-ABI call per GEMV:
+pinned x copied in, the projection, y copied out to pinned memory, stream synchronised); `roofline` relates the per-launch time to the measured HBM copy bandwidth;
 `cpu_baseline` times the CPU oracle port of the reference operator on the host cores.
 
 N > 1: the kernel benchmark does not shard (one matrix, one GPU); ranks run independent
@@ -296,20 +296,20 @@ def run_gpu_arm(args) -> None:
             clocks.mark(t_start, time.monotonic())
         elapsed_ms = start.elapsed_time(end)
 
-        # end to end through the module call with host buffers, per GEMV: pinned x -> device,
-        # forward, y -> host (the device->host copy synchronises).
+        # end to end through the module's host-buffer call, per GEMV: pinned x -> device,
+        # the projection, y -> pinned host memory, stream synchronisation (QuantisedLinear.forward_host).
         e2e_steps = max(1, min(args.steps, 5))
         e2e_s = float("nan")
         if not args.kernel_only:
             x_host = [x.cpu().pin_memory() for x in xs]
             y_host = torch.empty((BATCH, N), dtype=torch.bfloat16).pin_memory()
             for layer, xh in zip(layers, x_host):  # warm-up
-                y_host.copy_(layer(xh.to(device, non_blocking=True)))
+                layer.forward_host(xh, y_host)
             barrier()
             t0 = time.perf_counter()
             for _ in range(e2e_steps * PASSES):
                 for layer, xh in zip(layers, x_host):
-                    y_host.copy_(layer(xh.to(device, non_blocking=True)))
+                    layer.forward_host(xh, y_host)  # copy in, GEMV, copy out, synchronise: y_host is valid
             torch.cuda.synchronize()
             e2e_s = time.perf_counter() - t0
         status = native.device_status(device)

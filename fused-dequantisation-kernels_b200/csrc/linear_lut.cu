@@ -201,6 +201,22 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
                          nullptr, nullptr, stream);
 }
 
+extern "C" int fdk_linear_lut_host(const void* x_host, const void* tiled, const void* lut, const void* lut_host,
+                                   void* out_host, int m, int n, int k, int bits, int dtype, void* x_dev, void* out_dev,
+                                   void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
+  FDK_CHECK_ARG(x_host && out_host && x_dev && out_dev, FDK_ERR_BAD_ARG, "null pointer");
+  FDK_CHECK_ARG(m > 0 && n > 0 && k > 0, FDK_ERR_BAD_ARG, "m=%d, n=%d, k=%d must be positive", m, n, k);
+  cudaStream_t s = (cudaStream_t)stream;
+  FDK_CUDA(cudaMemcpyAsync(x_dev, x_host, (size_t)m * k * 2, cudaMemcpyHostToDevice, s));
+  if (int st = linear_lut_impl(x_dev, tiled, lut, lut_host, out_dev, m, n, k, bits, dtype, workspace, workspace_bytes,
+                               flags, nullptr, nullptr, stream)) {
+    return st;
+  }
+  FDK_CUDA(cudaMemcpyAsync(out_host, out_dev, (size_t)m * n * 2, cudaMemcpyDeviceToHost, s));
+  FDK_CUDA(cudaStreamSynchronize(s));
+  return FDK_OK;
+}
+
 extern "C" int fdk_linear_lut_fused(const void* x, const void* tiled, const void* lut, const void* lut_host, void* out,
                                     int m, int n, int k, int bits, int dtype, void* workspace, size_t workspace_bytes,
                                     unsigned flags, const fdk_linear_fusion* fusion, void* stream) {

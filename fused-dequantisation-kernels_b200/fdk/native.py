@@ -127,6 +127,11 @@ _SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p],
     ),
+    "fdk_linear_lut_host": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5
+        + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p],
+    ),
 }
 
 
@@ -311,6 +316,54 @@ def linear_lut(
                 (FLAG_PDL if pdl else 0) | (FLAG_SILU_PAIRS if silu_pairs else 0), _stream(),
             )
         )
+
+
+def linear_lut_host(
+    x_host: Tensor, tiled: Tensor, lut: Tensor, out_host: Tensor, x_dev: Tensor, out_dev: Tensor, n: int, k: int,
+    bits: int, lut_bytes: bytes | None = None,
+) -> None:
+    """out_host[m, n] = x_host[m, k] @ W.T for activations in host memory: copy in, projection, copy
+    out and a stream synchronisation in one library call.  x_dev / out_dev: device staging buffers."""
+    _require_cuda(tiled, lut, x_dev, out_dev)
+    assert not x_host.is_cuda and not out_host.is_cuda and x_host.is_contiguous() and out_host.is_contiguous()
+    m = x_host.shape[0]
+    assert x_dev.numel() >= m * k and out_dev.numel() >= m * n and out_host.numel() == m * n and x_host.shape[1] == k
+    ws = workspace(tiled.device)
+    if lut_bytes is None:
+        lut_bytes = host_lut(lut)
+    with torch.cuda.device(tiled.device):
+        check(
+            lib().fdk_linear_lut_host(
+                x_host.data_ptr(), tiled.data_ptr(), lut.data_ptr(), lut_bytes, out_host.data_ptr(), m, n, k, bits,
+                dtype_code(x_host.dtype), x_dev.data_ptr(), out_dev.data_ptr(), ws.data_ptr(), ws.numel(), 0, _stream(),
+            )
+        )
+
+
+def prepare_linear_lut_host(tiled: Tensor, lut: Tensor, lut_bytes: bytes, x_dev: Tensor, out_dev: Tensor, m: int,
+                            n: int, k: int, bits: int, dtype: torch.dtype):
+    """`linear_lut_host` with everything but the two host pointers bound once (current stream and
+    workspace included): returns call(x_host_ptr, out_host_ptr).  For callers that make the same call
+    many times -- the argument marshalling is a visible part of a 40 us round trip."""
+    _require_cuda(tiled, lut, x_dev, out_dev)
+    assert x_dev.numel() >= m * k and out_dev.numel() >= m * n
+    fn = lib().fdk_linear_lut_host
+    ws = workspace(tiled.device)
+    index = tiled.device.index
+    fixed_a = (tiled.data_ptr(), lut.data_ptr(), lut_bytes)
+    fixed_b = (m, n, k, bits, dtype_code(dtype), x_dev.data_ptr(), out_dev.data_ptr(), ws.data_ptr(), ws.numel(), 0, _stream())
+    keep = (tiled, lut, x_dev, out_dev, ws)  # the buffers live as long as the call does
+
+    def call(x_host_ptr: int, out_host_ptr: int, _keep=keep) -> None:
+        if torch.cuda.current_device() == index:
+            status = fn(x_host_ptr, *fixed_a, out_host_ptr, *fixed_b)
+        else:
+            with torch.cuda.device(index):
+                status = fn(x_host_ptr, *fixed_a, out_host_ptr, *fixed_b)
+        if status != OK:
+            check(status)
+
+    return call
 
 
 def linear_lut_fused(

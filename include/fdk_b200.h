@@ -199,6 +199,17 @@ int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache
                          void* out, void* scratch, void* counters, int batch, int q_heads,
                          int kv_heads, int head_dim, int max_len, int splits, void* stream);
 
+/* fdk_linear_lut for a caller whose activations live in HOST memory (the reference's operators
+ * take device tensors; a host-side caller would copy around them: x.to(device), the operator,
+ * out.cpu()).  One call: x_host [m, k] -> x_dev (asynchronous copy on `stream`), the projection
+ * into out_dev, out_dev -> out_host [m, n], and a synchronisation of `stream`: out_host is valid
+ * on return.  x_host and out_host should be page-locked for the copies to be asynchronous;
+ * x_dev [m, k] and out_dev [m, n] are device staging buffers of the caller (nothing is allocated
+ * here).  Other arguments as fdk_linear_lut. */
+int fdk_linear_lut_host(const void* x_host, const void* tiled, const void* lut, const void* lut_host,
+                        void* out_host, int m, int n, int k, int bits, int dtype, void* x_dev, void* out_dev,
+                        void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+
 /* ---- decode-step fusions of fdk_linear_lut (bf16, m <= 16) -------------------------------
  * Around each quantised projection the reference's model (transformers' Llama, called from
  * Generator.step, src/fdk/models.py:245-255) runs an RMSNorm, a residual add or a rotary

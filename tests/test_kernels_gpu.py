@@ -230,3 +230,22 @@ def test_reference_mm_test_recipe(native):
 
     bench.test_mm_4b_lut8()
     bench.test_mv_4b_lut8()
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 40])
+def test_forward_host_equals_forward(m):
+    """QuantisedLinear.forward_host (fdk_linear_lut_host: copy in, projection, copy out, synchronise)
+    gives the bits of forward() on the same activations."""
+    from fdk import models
+
+    torch.manual_seed(m)
+    w = (torch.randn((640, 512), device="cuda") * 0.05).bfloat16()
+    layer = models.QuantisedLinear.create(w, models.QuantisationConfig(4, 64))
+    x_host = torch.randn((m, 512)).bfloat16().pin_memory()
+    out_host = torch.full((m, 640), float("nan")).bfloat16().pin_memory()
+    back = layer.forward_host(x_host, out_host)
+    assert back is out_host  # valid on return: no synchronisation needed here
+    want = layer(x_host.cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(out_host, want.cpu())
+    assert torch.equal(layer.forward_host(x_host), want.cpu())  # allocates a pinned output itself
