@@ -13,7 +13,8 @@ even a 20-step run is timed over more than 50 ms and the clock samples fall unde
 Printed JSON line: `value` = packed-weight bytes (codes + block scales) of all GPUs per
 second, device-timed with inputs resident in HBM; `e2e` = the same bytes per second
 through the module's host-buffer call `QuantisedLinear.forward_host` (one C-ABI call per GEMV:
-pinned x copied in, the projection, y copied out to pinned memory, stream synchronised); `roofline` relates the per-launch time to the measured HBM copy bandwidth;
+pinned x copied in, the projection, y copied out to pinned memory; the calls of a step are queued
+asynchronously and the step's results awaited once); `roofline` relates the per-launch time to the measured HBM copy bandwidth;
 `cpu_baseline` times the CPU oracle port of the reference operator on the host cores.
 
 N > 1: the kernel benchmark does not shard (one matrix, one GPU); ranks run independent
@@ -307,10 +308,13 @@ def run_gpu_arm(args) -> None:
                 layer.forward_host(xh, y_host)
             barrier()
             t0 = time.perf_counter()
-            for _ in range(e2e_steps * PASSES):
-                for layer, xh in zip(layers, x_host):
-                    layer.forward_host(xh, y_host)  # copy in, GEMV, copy out, synchronise: y_host is valid
-            torch.cuda.synchronize()
+            for _ in range(e2e_steps):
+                # one step = PASSES x COPIES GEMVs, each with its own copy in and copy out, queued
+                # without waiting for each other; the step's results are awaited once, at its end
+                for _ in range(PASSES):
+                    for layer, xh in zip(layers, x_host):
+                        layer.forward_host(xh, y_host, synchronise=False)
+                torch.cuda.synchronize()  # every y of the step has landed in host memory
             e2e_s = time.perf_counter() - t0
         status = native.device_status(device)
         if status != 0:  # a bounded wait ran out inside the timed region: the numbers mean nothing

@@ -209,11 +209,11 @@ extern "C" int fdk_linear_lut_host(const void* x_host, const void* tiled, const 
   cudaStream_t s = (cudaStream_t)stream;
   FDK_CUDA(cudaMemcpyAsync(x_dev, x_host, (size_t)m * k * 2, cudaMemcpyHostToDevice, s));
   if (int st = linear_lut_impl(x_dev, tiled, lut, lut_host, out_dev, m, n, k, bits, dtype, workspace, workspace_bytes,
-                               flags, nullptr, nullptr, stream)) {
+                               flags & ~FDK_FLAG_NO_SYNC, nullptr, nullptr, stream)) {
     return st;
   }
   FDK_CUDA(cudaMemcpyAsync(out_host, out_dev, (size_t)m * n * 2, cudaMemcpyDeviceToHost, s));
-  FDK_CUDA(cudaStreamSynchronize(s));
+  if (!(flags & FDK_FLAG_NO_SYNC)) FDK_CUDA(cudaStreamSynchronize(s));
   return FDK_OK;
 }
 

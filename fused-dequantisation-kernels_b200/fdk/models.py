@@ -118,12 +118,14 @@ class QuantisedLinear(nn.Module):
         )
         return out
 
-    def forward_host(self, x_host: Tensor, out_host: Tensor | None = None) -> Tensor:
+    def forward_host(self, x_host: Tensor, out_host: Tensor | None = None, synchronise: bool = True) -> Tensor:
         """The forward for activations that live in host memory: x_host [m, in_features] (page-locked
         for asynchronous copies) -> out_host [m, out_features], valid on return.  One library call
         does the copy in, the projection, the copy out and the stream synchronisation, instead of
         `layer(x_host.to(device)).cpu()` (three framework calls and their bookkeeping around an
-        11 us kernel)."""
+        11 us kernel).  synchronise=False returns at once: out_host is valid after the caller has
+        synchronised the current stream, x_host must stay untouched until then, and further calls
+        may be queued meanwhile (their copies and kernels then overlap the host's work)."""
         assert self.kernel != "torch.compile" and x_host.ndim == 2 and not x_host.is_cuda
         m = x_host.shape[0]
         if out_host is None:
@@ -131,15 +133,16 @@ class QuantisedLinear(nn.Module):
         assert x_host.shape[1] == self.in_features and x_host.is_contiguous() and x_host.dtype == self.lut.dtype
         assert out_host.shape == (m, self.out_features) and out_host.is_contiguous() and out_host.dtype == x_host.dtype
         tiled = self.tiled()
-        key = (m, id(tiled), torch.cuda.current_stream(tiled.device).cuda_stream)
+        key = (m, id(tiled), torch.cuda.current_stream(tiled.device).cuda_stream, synchronise)
         calls = self.__dict__.setdefault("_host_calls", {})
         call = calls.get(key)
         if call is None:  # staging buffers and the bound library call, once per batch size and stream
             x_dev = torch.empty(m * self.in_features, dtype=x_host.dtype, device=tiled.device)
             out_dev = torch.empty(m * self.out_features, dtype=x_host.dtype, device=tiled.device)
             call = native.prepare_linear_lut_host(tiled, self.lut, self.lut_bytes(), x_dev, out_dev, m, self.out_features,
-                                                  self.in_features, self.bits, x_host.dtype)
-            calls.clear()  # one entry: a changed weight or stream replaces it
+                                                  self.in_features, self.bits, x_host.dtype, synchronise)
+            if len(calls) >= 4:  # a changed weight or stream leaves stale entries behind
+                calls.clear()
             calls[key] = call
         call(x_host.data_ptr(), out_host.data_ptr())
         return out_host

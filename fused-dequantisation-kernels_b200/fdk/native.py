@@ -22,6 +22,7 @@ DTYPE_BF16 = 0
 DTYPE_F16 = 1
 FLAG_PDL = 1
 FLAG_SILU_PAIRS = 2
+FLAG_NO_SYNC = 4
 
 
 class FdkError(RuntimeError):
@@ -341,7 +342,7 @@ def linear_lut_host(
 
 
 def prepare_linear_lut_host(tiled: Tensor, lut: Tensor, lut_bytes: bytes, x_dev: Tensor, out_dev: Tensor, m: int,
-                            n: int, k: int, bits: int, dtype: torch.dtype):
+                            n: int, k: int, bits: int, dtype: torch.dtype, synchronise: bool = True):
     """`linear_lut_host` with everything but the two host pointers bound once (current stream and
     workspace included): returns call(x_host_ptr, out_host_ptr).  For callers that make the same call
     many times -- the argument marshalling is a visible part of a 40 us round trip."""
@@ -351,7 +352,8 @@ def prepare_linear_lut_host(tiled: Tensor, lut: Tensor, lut_bytes: bytes, x_dev:
     ws = workspace(tiled.device)
     index = tiled.device.index
     fixed_a = (tiled.data_ptr(), lut.data_ptr(), lut_bytes)
-    fixed_b = (m, n, k, bits, dtype_code(dtype), x_dev.data_ptr(), out_dev.data_ptr(), ws.data_ptr(), ws.numel(), 0, _stream())
+    fixed_b = (m, n, k, bits, dtype_code(dtype), x_dev.data_ptr(), out_dev.data_ptr(), ws.data_ptr(), ws.numel(),
+               0 if synchronise else FLAG_NO_SYNC, _stream())
     keep = (tiled, lut, x_dev, out_dev, ws)  # the buffers live as long as the call does
 
     def call(x_host_ptr: int, out_host_ptr: int, _keep=keep) -> None:

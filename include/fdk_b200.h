@@ -59,6 +59,13 @@ extern "C" {
                            followed by fdk_silu_mul (group 32).  m <= 16, n a multiple
                            of 64.                                                      */
 
+#define FDK_FLAG_NO_SYNC 4u   /* fdk_linear_lut_host only: return without synchronising the
+                           stream; out_host is valid once the caller has synchronised it,
+                           and x_host must stay untouched until then.  Calls on one stream
+                           may follow each other (they share the staging buffers in stream
+                           order), so that copies and kernels of successive calls overlap
+                           the host's work.                                             */
+
 /* Library version: major*10000 + minor*100 + patch. */
 int fdk_version(void);
 
@@ -203,7 +210,7 @@ int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache
  * take device tensors; a host-side caller would copy around them: x.to(device), the operator,
  * out.cpu()).  One call: x_host [m, k] -> x_dev (asynchronous copy on `stream`), the projection
  * into out_dev, out_dev -> out_host [m, n], and a synchronisation of `stream`: out_host is valid
- * on return.  x_host and out_host should be page-locked for the copies to be asynchronous;
+ * on return (FDK_FLAG_NO_SYNC leaves the synchronisation to the caller).  x_host and out_host should be page-locked for the copies to be asynchronous;
  * x_dev [m, k] and out_dev [m, n] are device staging buffers of the caller (nothing is allocated
  * here).  Other arguments as fdk_linear_lut. */
 int fdk_linear_lut_host(const void* x_host, const void* tiled, const void* lut, const void* lut_host,

@@ -249,3 +249,9 @@ def test_forward_host_equals_forward(m):
     torch.cuda.synchronize()
     assert torch.equal(out_host, want.cpu())
     assert torch.equal(layer.forward_host(x_host), want.cpu())  # allocates a pinned output itself
+    # queued without synchronisation: valid once the stream has been synchronised
+    outs = [torch.full((m, 640), float("nan")).bfloat16().pin_memory() for _ in range(3)]
+    for o in outs:
+        layer.forward_host(x_host, o, synchronise=False)
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, want.cpu()) for o in outs)
