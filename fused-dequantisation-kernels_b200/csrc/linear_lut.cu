@@ -201,18 +201,80 @@ extern "C" int fdk_linear_lut(const void* x, const void* tiled, const void* lut,
                          nullptr, nullptr, stream);
 }
 
+// fdk_linear_lut_host moves its few kilobytes of activations with a kernel of its own where it
+// can: a DMA copy of 16 KB costs ~8 us on the stream, a kernel reading or writing page-locked
+// host memory through its device mapping ~3 us, and it takes part in programmatic dependent
+// launch (the projection's weight prefetch overlaps the copy in).  Host memory that is not
+// page-locked and mapped (cudaPointerGetAttributes says so) is copied by cudaMemcpyAsync.
+namespace fdk {
+namespace hostcopy {
+
+__global__ void host_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int vectors) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vectors; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// The device's address of page-locked, mapped host memory, or null.
+void* mapped_host_pointer(const void* host) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
+int launch_host_copy(const void* src, void* dst, size_t bytes, cudaStream_t stream) {
+  const int vectors = (int)(bytes / 16);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((vectors + 255) / 256 < 8 ? (vectors + 255) / 256 : 8);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FDK_CUDA(cudaLaunchKernelEx(&cfg, host_copy_kernel, (const uint4*)src, (uint4*)dst, vectors));
+  return FDK_OK;
+}
+
+constexpr size_t kHostCopyKernelLimit = 256 * 1024;  // larger activations: the DMA engine's bandwidth wins
+
+}  // namespace hostcopy
+}  // namespace fdk
+using namespace fdk::hostcopy;
+
 extern "C" int fdk_linear_lut_host(const void* x_host, const void* tiled, const void* lut, const void* lut_host,
                                    void* out_host, int m, int n, int k, int bits, int dtype, void* x_dev, void* out_dev,
                                    void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
   FDK_CHECK_ARG(x_host && out_host && x_dev && out_dev, FDK_ERR_BAD_ARG, "null pointer");
   FDK_CHECK_ARG(m > 0 && n > 0 && k > 0, FDK_ERR_BAD_ARG, "m=%d, n=%d, k=%d must be positive", m, n, k);
   cudaStream_t s = (cudaStream_t)stream;
-  FDK_CUDA(cudaMemcpyAsync(x_dev, x_host, (size_t)m * k * 2, cudaMemcpyHostToDevice, s));
+  const size_t x_bytes = (size_t)m * k * 2, out_bytes = (size_t)m * n * 2;
+  auto by_kernel = [](const void* host, const void* dev, size_t bytes) -> void* {
+    if (bytes > kHostCopyKernelLimit || bytes % 16 != 0 || (((uintptr_t)host | (uintptr_t)dev) & 15) != 0) return nullptr;
+    return mapped_host_pointer(host);
+  };
+  void* x_mapped = by_kernel(x_host, x_dev, x_bytes);
+  void* out_mapped = by_kernel(out_host, out_dev, out_bytes);
+  if (x_mapped != nullptr) {
+    if (int st = launch_host_copy(x_mapped, x_dev, x_bytes, s)) return st;
+  } else {
+    FDK_CUDA(cudaMemcpyAsync(x_dev, x_host, x_bytes, cudaMemcpyHostToDevice, s));
+  }
+  // behind a kernel the projection may start early: it only reads weights before it waits
+  const unsigned inner = (flags & ~FDK_FLAG_NO_SYNC) | (x_mapped != nullptr ? FDK_FLAG_PDL : 0u);
   if (int st = linear_lut_impl(x_dev, tiled, lut, lut_host, out_dev, m, n, k, bits, dtype, workspace, workspace_bytes,
-                               flags & ~FDK_FLAG_NO_SYNC, nullptr, nullptr, stream)) {
+                               inner, nullptr, nullptr, stream)) {
     return st;
   }
-  FDK_CUDA(cudaMemcpyAsync(out_host, out_dev, (size_t)m * n * 2, cudaMemcpyDeviceToHost, s));
+  if (out_mapped != nullptr) {
+    if (int st = launch_host_copy(out_dev, out_mapped, out_bytes, s)) return st;
+  } else {
+    FDK_CUDA(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, s));
+  }
   if (!(flags & FDK_FLAG_NO_SYNC)) FDK_CUDA(cudaStreamSynchronize(s));
   return FDK_OK;
 }

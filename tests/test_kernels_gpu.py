@@ -249,6 +249,12 @@ def test_forward_host_equals_forward(m):
     torch.cuda.synchronize()
     assert torch.equal(out_host, want.cpu())
     assert torch.equal(layer.forward_host(x_host), want.cpu())  # allocates a pinned output itself
+    # host memory that is not page-locked takes the cudaMemcpyAsync route inside the library
+    pageable_x = x_host.clone()
+    pageable_out = torch.full((m, 640), float("nan")).bfloat16()
+    assert not pageable_x.is_pinned() and not pageable_out.is_pinned()
+    layer.forward_host(pageable_x, pageable_out)
+    assert torch.equal(pageable_out, want.cpu())
     # queued without synchronisation: valid once the stream has been synchronised
     outs = [torch.full((m, 640), float("nan")).bfloat16().pin_memory() for _ in range(3)]
     for o in outs:
