@@ -400,7 +400,8 @@ def decode_extra(device, world: int, rank: int) -> dict:
     block-64 weights, one decode step per CUDA-graph replay as the reference times it
     (src/fdk/models.py:313-340), synthetic KV-cache contents of the stated context.
       N = 1: "b200-4B" (32 layers, d 3072, FFN 8192, 24/8 heads), context 1024, batch 1 to 256,
-             beside the same loop with bf16 nn.Linear layers (cuBLAS) at batch 1 and 16; and
+             lm_head in bf16 as the reference leaves it; the same with lm_head quantised too at
+             batch 1 and 16; the same loop with bf16 nn.Linear layers (cuBLAS) at batch 1 and 16; and
              "b200-31B" (64 layers, d 6144, FFN 20480, 48/8 heads), context 2048, batch 1.
       N > 1: the models tensor parallel over the N ranks (31B at context 2048, batch 1 and 16; 4B
              at context 1024, batch 1): the o and down projections push their partial sums to
@@ -427,6 +428,16 @@ def decode_extra(device, world: int, rank: int) -> dict:
             model = llama.LlamaDecoder.random_init(dims, config, device, tp, lut=lut)
             for batch in (1, 4, 16, 64, 256):
                 out["runs"].append(run(model, "custom-llama-b200-4B", batch, 1024))
+            del model
+            torch.cuda.empty_cache()
+            # every linear layer quantised, lm_head included (the reference's default leaves it in
+            # bf16, skip="^lm_head$", as the runs above do)
+            every = models.QuantisationConfig(4, 64, skip=None)
+            model = llama.LlamaDecoder.random_init(dims, every, device, tp, lut=lut)
+            for batch in (1, 16):
+                entry = run(model, "custom-llama-b200-4B", batch, 1024)
+                entry["lm_head"] = "4-bit"
+                out["runs"].append(entry)
             del model
             torch.cuda.empty_cache()
             base = llama.LlamaDecoder.random_init(dims, None, device, tp)
