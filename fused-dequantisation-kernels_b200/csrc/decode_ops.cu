@@ -547,8 +547,12 @@ constexpr int kAttnWarps = 8;
 constexpr int kMaxSplits = 64;
 constexpr int kMaxGroup = 8;
 
-template <int G>
-__global__ void __launch_bounds__(kAttnWarps * 32)
+// DENSE: for grids of more CTAs than SMs -- eight keys per warp in flight instead of sixteen, which
+// brings the kernel under 128 registers (ratios up to 4) so that two CTAs share an SM and twice
+// the warps keep loads in flight; small grids (one CTA per SM at most) keep sixteen keys per
+// warp, which saves them a round of memory latency.
+template <int G, bool DENSE>
+__global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
     decode_attention_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
                             const uint16_t* __restrict__ v_cache, const long long* __restrict__ pos_ptr,
                             uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
@@ -570,7 +574,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   // U positions per warp and iteration, all their loads in flight together: with a slice of up
   // to 8 * U keys a warp pays the memory latency once -- and for its first U positions before
   // the wait, beside the previous kernel
-  constexpr int U = (G <= 4) ? 16 : 8;
+  constexpr int U = (G <= 4 && !DENSE) ? 16 : 8;
   uint2 kk[U], vv[U];
   const int pb_first = p0 + warp * U;
   if (pb_first < p1) {
@@ -830,9 +834,17 @@ int launch_attention(const void* q, const void* k_cache, const void* v_cache, co
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G>, (const uint16_t*)q, (const uint16_t*)k_cache,
-                              (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
-                              (int*)counters, q_heads, kv_heads, max_len, chunk));
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  if ((long long)splits * kv_heads * batch > di.sm_count) {
+    FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G, true>, (const uint16_t*)q, (const uint16_t*)k_cache,
+                                (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
+                                (int*)counters, q_heads, kv_heads, max_len, chunk));
+  } else {
+    FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G, false>, (const uint16_t*)q, (const uint16_t*)k_cache,
+                                (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
+                                (int*)counters, q_heads, kv_heads, max_len, chunk));
+  }
   return FDK_OK;
 }
 
