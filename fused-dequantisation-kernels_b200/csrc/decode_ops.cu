@@ -556,11 +556,18 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
     decode_attention_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
                             const uint16_t* __restrict__ v_cache, const long long* __restrict__ pos_ptr,
                             uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
-                            int q_heads, int kv_heads, int max_len, int chunk) {
+                            int q_heads, int kv_heads, int max_len, int chunk, int halves) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ float part[kAttnWarps][G][132];
   __shared__ float wbuf[kAttnWarps][16 * 4 > 8 * G ? 16 * 4 : 8 * G];  // softmax weights of a round, per warp: U * G
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
+  // halves == 2 (one context slice only): the query heads of a KV head are shared between two
+  // CTAs next to each other in the grid, G being half their number (rounded up); the second read
+  // of the keys and values is then mostly served by L2
+  const int split = blockIdx.x, kvh = blockIdx.y / halves, sub = blockIdx.y - kvh * halves, b = blockIdx.z,
+            splits = gridDim.x;
+  const int ratio = q_heads / kv_heads;                  // query heads per KV head
+  const int head0 = kvh * ratio + sub * G;               // this CTA's first query head
+  const int valid = min(G, ratio - sub * G);             // and how many of its G it really has
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // The position only changes between decode steps, and the keys and values of earlier
   // positions were written in earlier steps: both may be read before the kernel that feeds
@@ -593,7 +600,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
   const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
 #pragma unroll
   for (int j = 0; j < G; ++j) {
-    const uint2 qq = *reinterpret_cast<const uint2*>(q + ((size_t)b * q_heads + kvh * G + j) * 128 + lane * 4);
+    const uint2 qq = *reinterpret_cast<const uint2*>(q + ((size_t)b * q_heads + head0 + min(j, valid - 1)) * 128 + lane * 4);
     qf[j][0] = pair_lo<false>(qq.x) * scale; qf[j][1] = pair_hi<false>(qq.x) * scale;
     qf[j][2] = pair_lo<false>(qq.y) * scale; qf[j][3] = pair_hi<false>(qq.y) * scale;
     acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
@@ -711,7 +718,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
         a += part[w][j][d] * c;
       }
       if (splits == 1) {
-        out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(l > 0.f ? a / l : 0.f);
+        if (j < valid) out[((size_t)b * q_heads + head0 + j) * 128 + d] = from_float<false>(l > 0.f ? a / l : 0.f);
       } else {
         st_relaxed_v2(mine + j * 130 + d, make_uint2(__float_as_uint(a), tag));
         if (d == 0) {
@@ -813,7 +820,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
 #pragma unroll
     for (int j = 0; j < G; ++j) {
       const float a = total[j] + other_half[j][d];
-      out[((size_t)b * q_heads + kvh * G + j) * 128 + d] = from_float<false>(denom[j] > 0.f ? a / denom[j] : 0.f);
+      out[((size_t)b * q_heads + head0 + j) * 128 + d] = from_float<false>(denom[j] > 0.f ? a / denom[j] : 0.f);
     }
   }
   if (threadIdx.x == 0) counters[group] = (int)((uses + 1u) & 0x3FFFFFFFu);  // this use is done
@@ -823,10 +830,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
 template <int G>
 int launch_attention(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
                      void* scratch, void* counters, int batch, int q_heads, int kv_heads, int max_len,
-                     int splits, cudaStream_t stream) {
+                     int splits, int halves, cudaStream_t stream) {
   const int chunk = (max_len + splits - 1) / splits;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(splits, kv_heads, batch);
+  cfg.gridDim = dim3(splits, kv_heads * halves, batch);
   cfg.blockDim = dim3(kAttnWarps * 32);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -836,14 +843,14 @@ int launch_attention(const void* q, const void* k_cache, const void* v_cache, co
   cfg.numAttrs = 1;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
-  if ((long long)splits * kv_heads * batch > di.sm_count) {
+  if ((long long)splits * kv_heads * halves * batch > di.sm_count) {
     FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G, true>, (const uint16_t*)q, (const uint16_t*)k_cache,
                                 (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
-                                (int*)counters, q_heads, kv_heads, max_len, chunk));
+                                (int*)counters, q_heads, kv_heads, max_len, chunk, halves));
   } else {
     FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G, false>, (const uint16_t*)q, (const uint16_t*)k_cache,
                                 (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
-                                (int*)counters, q_heads, kv_heads, max_len, chunk));
+                                (int*)counters, q_heads, kv_heads, max_len, chunk, halves));
   }
   return FDK_OK;
 }
@@ -877,14 +884,26 @@ extern "C" int fdk_decode_attention(const void* q, const void* k_cache, const vo
   FDK_CHECK_ARG(splits >= 1 && splits <= kMaxSplits && max_len > 0, FDK_ERR_BAD_ARG, "splits=%d (1..%d), max_len=%d", splits, kMaxSplits, max_len);
   FDK_CHECK_ARG(splits == 1 || (scratch && counters), FDK_ERR_WORKSPACE, "scratch and counters are needed when splits > 1");
   cudaStream_t s = (cudaStream_t)stream;
-  switch (q_heads / kv_heads) {
-    case 1: return launch_attention<1>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
-    case 2: return launch_attention<2>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
-    case 3: return launch_attention<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
-    case 4: return launch_attention<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
-    case 5: return launch_attention<5>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
-    case 6: return launch_attention<6>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
-    case 7: return launch_attention<7>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
-    default: return launch_attention<8>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+  const int group = q_heads / kv_heads;
+  // Ratios above 4 need ~175 registers (one CTA of 8 warps per SM).  Where the grid is larger
+  // than the GPU and the context is not sliced, the query heads of a KV head are shared between
+  // two CTAs of half the ratio instead, which run two to an SM.
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  if (group > 4 && splits == 1 && (long long)kv_heads * batch > di.sm_count) {
+    switch ((group + 1) / 2) {
+      case 3: return launch_attention<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, 1, 2, s);
+      default: return launch_attention<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, 1, 2, s);
+    }
+  }
+  switch (group) {
+    case 1: return launch_attention<1>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    case 2: return launch_attention<2>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    case 3: return launch_attention<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    case 4: return launch_attention<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    case 5: return launch_attention<5>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    case 6: return launch_attention<6>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    case 7: return launch_attention<7>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    default: return launch_attention<8>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
   }
 }
