@@ -535,11 +535,13 @@ extern "C" int fdk_silu_mul(const void* gate_up, void* out, int rows, int width,
 
 // ---- decode attention over the static KV cache ----------------------------------------------
 // One query token per batch row, grouped-query attention, head_dim 128, bf16 cache
-// [batch, kv_heads, max_len, 128].  Grid (splits, kv_heads, batch): a CTA of 4 warps takes one
+// [batch, kv_heads, max_len, 128].  Grid (splits, kv_heads, batch): a CTA of 8 warps takes one
 // slice of the context for all the query heads that share a KV head (so every key/value byte
 // is read once), keeps a running softmax per head, and leaves {max, sum, 128 weighted values}
 // per head in scratch as tagged words; the CTA of slice 0 polls them (bounded), merges the
 // slices and writes the bf16 output.  HBM-bound at large batch (2 x 256 B per position per KV head).
+// Two kernels share that scheme: a scalar one for small grids (latency-bound: at most one CTA
+// per SM, ratios up to 4) and a tensor-core one for everything else.
 namespace fdk {
 namespace {
 
@@ -547,154 +549,15 @@ constexpr int kAttnWarps = 8;
 constexpr int kMaxSplits = 64;
 constexpr int kMaxGroup = 8;
 
-// DENSE: for grids of more CTAs than SMs -- eight keys per warp in flight instead of sixteen, which
-// brings the kernel under 128 registers (ratios up to 4) so that two CTAs share an SM and twice
-// the warps keep loads in flight; small grids (one CTA per SM at most) keep sixteen keys per
-// warp, which saves them a round of memory latency.
-template <int G, bool DENSE>
-__global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
-    decode_attention_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
-                            const uint16_t* __restrict__ v_cache, const long long* __restrict__ pos_ptr,
-                            uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
-                            int q_heads, int kv_heads, int max_len, int chunk, int halves) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  __shared__ float part[kAttnWarps][G][132];
-  __shared__ float wbuf[kAttnWarps][16 * 4 > 8 * G ? 16 * 4 : 8 * G];  // softmax weights of a round, per warp: U * G
-  // halves == 2 (one context slice only): the query heads of a KV head are shared between two
-  // CTAs next to each other in the grid, G being half their number (rounded up); the second read
-  // of the keys and values is then mostly served by L2
-  const int split = blockIdx.x, kvh = blockIdx.y / halves, sub = blockIdx.y - kvh * halves, b = blockIdx.z,
-            splits = gridDim.x;
-  const int ratio = q_heads / kv_heads;                  // query heads per KV head
-  const int head0 = kvh * ratio + sub * G;               // this CTA's first query head
-  const int valid = min(G, ratio - sub * G);             // and how many of its G it really has
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // The position only changes between decode steps, and the keys and values of earlier
-  // positions were written in earlier steps: both may be read before the kernel that feeds
-  // this one (it writes q and the current position's key and value) has finished.
-  // A position outside the cache is clamped (no key at all gives zeros).
-  const long long pos_now = *pos_ptr;
-  const int len = pos_now < 0 ? 0 : (pos_now >= max_len ? max_len : (int)pos_now + 1);
-  const int p0 = split * chunk, p1 = min(len, p0 + chunk);
-  const uint16_t* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
-  const uint16_t* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
-  // U positions per warp and iteration, all their loads in flight together: with a slice of up
-  // to 8 * U keys a warp pays the memory latency once -- and for its first U positions before
-  // the wait, beside the previous kernel
-  constexpr int U = (G <= 4 && !DENSE) ? 16 : 8;
-  uint2 kk[U], vv[U];
-  const int pb_first = p0 + warp * U;
-  if (pb_first < p1) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int p = min(pb_first + u, p1 - 1);  // clamped reads, masked below
-      if (p != len - 1) {  // the current position is read after the wait
-        kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
-        vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
-      }
-    }
-  }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-
-  float qf[G][4], acc[G][4], mx[G], sum[G];
-  const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
-#pragma unroll
-  for (int j = 0; j < G; ++j) {
-    const uint2 qq = *reinterpret_cast<const uint2*>(q + ((size_t)b * q_heads + head0 + min(j, valid - 1)) * 128 + lane * 4);
-    qf[j][0] = pair_lo<false>(qq.x) * scale; qf[j][1] = pair_hi<false>(qq.x) * scale;
-    qf[j][2] = pair_lo<false>(qq.y) * scale; qf[j][3] = pair_hi<false>(qq.y) * scale;
-    acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    mx[j] = -INFINITY;
-    sum[j] = 0.f;
-  }
-  for (int pb = pb_first; pb < p1; pb += kAttnWarps * U) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int p = min(pb + u, p1 - 1);
-      if (pb != pb_first || p == len - 1) {
-        kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
-        vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
-      }
-    }
-    float s[U][G];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const float k0 = pair_lo<false>(kk[u].x), k1 = pair_hi<false>(kk[u].x), k2 = pair_lo<false>(kk[u].y), k3 = pair_hi<false>(kk[u].y);
-#pragma unroll
-      for (int j = 0; j < G; ++j) s[u][j] = qf[j][0] * k0 + qf[j][1] * k1 + qf[j][2] * k2 + qf[j][3] * k3;
-    }
-    // Sum the 32 lanes' partial dot products.  Not U * G butterflies (5 shuffles each): the
-    // position range is halved with the lane distance, so that after log2(U) rounds a group
-    // of 32 / U lanes holds the G totals of ONE position (u_own), at a fifth of the shuffles.
-    auto halve = [&](auto hc, int off) {
-      constexpr int H = decltype(hc)::value;
-      const bool upper = (lane & off) != 0;
-#pragma unroll
-      for (int u = 0; u < H; ++u)
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-          const float send = upper ? s[u][j] : s[u + H][j];
-          const float keep = upper ? s[u + H][j] : s[u][j];
-          s[u][j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-        }
-    };
-    if constexpr (U == 16) {
-      halve(std::integral_constant<int, 8>{}, 16);
-      halve(std::integral_constant<int, 4>{}, 8);
-      halve(std::integral_constant<int, 2>{}, 4);
-      halve(std::integral_constant<int, 1>{}, 2);
-    } else {
-      halve(std::integral_constant<int, 4>{}, 16);
-      halve(std::integral_constant<int, 2>{}, 8);
-      halve(std::integral_constant<int, 1>{}, 4);
-#pragma unroll
-      for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 2);
-    }
-#pragma unroll
-    for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 1);
-    const int u_own = lane / (32 / U);
-    const bool live = pb + u_own < p1;
-    float* wrow = wbuf[warp];
-    float corr[G];
-#pragma unroll
-    for (int j = 0; j < G; ++j) {
-      const float mine = live ? s[0][j] : -INFINITY;
-      float m_new = mine;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, o));
-      m_new = fmaxf(m_new, mx[j]);
-      corr[j] = __expf(mx[j] - m_new);
-      mx[j] = m_new;
-      wrow[u_own * G + j] = __expf(mine - m_new);  // exp(-inf) = 0 for masked positions; every lane of the group writes the same value
-    }
-    __syncwarp();
-#pragma unroll
-    for (int j = 0; j < G; ++j) {
-      float l = sum[j] * corr[j], a0 = acc[j][0] * corr[j], a1 = acc[j][1] * corr[j], a2 = acc[j][2] * corr[j],
-            a3 = acc[j][3] * corr[j];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const float w = wrow[u * G + j];  // broadcast read
-        l += w;
-        a0 += w * pair_lo<false>(vv[u].x);
-        a1 += w * pair_hi<false>(vv[u].x);
-        a2 += w * pair_lo<false>(vv[u].y);
-        a3 += w * pair_hi<false>(vv[u].y);
-      }
-      sum[j] = l; acc[j][0] = a0; acc[j][1] = a1; acc[j][2] = a2; acc[j][3] = a3;
-    }
-    __syncwarp();  // the weights are read before the next round overwrites them
-  }
-  // merge the warps of the CTA (fixed order)
-#pragma unroll
-  for (int j = 0; j < G; ++j) {
-    *reinterpret_cast<float4*>(&part[warp][j][lane * 4]) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-    if (lane == 0) {
-      part[warp][j][128] = mx[j];
-      part[warp][j][129] = sum[j];
-    }
-  }
-  __syncthreads();
+// What follows the key/value loop, shared by the two attention kernels: `part[w][j]` holds warp
+// w's {128 weighted values, max, sum} of head j.  The warps are merged in a fixed order; an
+// unsliced context writes the bf16 output directly, a slice leaves its numbers in scratch as
+// tagged words and the CTA of slice 0 polls them (bounded), merges and writes the output.
+template <int G>
+__device__ __forceinline__ void attention_finish(const float (*part)[G][132], uint16_t* __restrict__ out,
+                                                 float* __restrict__ scratch, int* __restrict__ counters, int split,
+                                                 int splits, int b, int kvh, int kv_heads, int q_heads) {
+  const int head0 = kvh * G;
   // threads 0..127: one output dimension each from here on
   const int d = threadIdx.x & 127;
   const bool writer = threadIdx.x < 128;
@@ -718,7 +581,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
         a += part[w][j][d] * c;
       }
       if (splits == 1) {
-        if (j < valid) out[((size_t)b * q_heads + head0 + j) * 128 + d] = from_float<false>(l > 0.f ? a / l : 0.f);
+        out[((size_t)b * q_heads + head0 + j) * 128 + d] = from_float<false>(l > 0.f ? a / l : 0.f);
       } else {
         st_relaxed_v2(mine + j * 130 + d, make_uint2(__float_as_uint(a), tag));
         if (d == 0) {
@@ -827,32 +690,345 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (DENSE && G <= 4) ? 2 : 1)
   if (!ok) atomicOr(counters + gridDim.z * kv_heads, kStatusTimeout);
 }
 
+// This scalar kernel serves grids of at most one CTA per SM with grouped-query ratios up to 4
+// (small batches: bound by latency, which its prefetch before the wait and its sixteen keys per
+// warp in flight address); everything else goes to the tensor-core kernel below.
+template <int G>
+__global__ void __launch_bounds__(kAttnWarps * 32, 1)
+    decode_attention_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
+                            const uint16_t* __restrict__ v_cache, const long long* __restrict__ pos_ptr,
+                            uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
+                            int q_heads, int kv_heads, int max_len, int chunk) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ __align__(16) float part[kAttnWarps][G][132];
+  __shared__ float wbuf[kAttnWarps][16 * 4 > 8 * G ? 16 * 4 : 8 * G];  // softmax weights of a round, per warp: U * G
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
+  const int head0 = kvh * G;  // this CTA's first query head
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // The position only changes between decode steps, and the keys and values of earlier
+  // positions were written in earlier steps: both may be read before the kernel that feeds
+  // this one (it writes q and the current position's key and value) has finished.
+  // A position outside the cache is clamped (no key at all gives zeros).
+  const long long pos_now = *pos_ptr;
+  const int len = pos_now < 0 ? 0 : (pos_now >= max_len ? max_len : (int)pos_now + 1);
+  const int p0 = split * chunk, p1 = min(len, p0 + chunk);
+  const uint16_t* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
+  const uint16_t* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_len * 128 + lane * 4;
+  // U positions per warp and iteration, all their loads in flight together: with a slice of up
+  // to 8 * U keys a warp pays the memory latency once -- and for its first U positions before
+  // the wait, beside the previous kernel
+  constexpr int U = 16;
+  uint2 kk[U], vv[U];
+  const int pb_first = p0 + warp * U;
+  if (pb_first < p1) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int p = min(pb_first + u, p1 - 1);  // clamped reads, masked below
+      if (p != len - 1) {  // the current position is read after the wait
+        kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
+        vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
+      }
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  float qf[G][4], acc[G][4], mx[G], sum[G];
+  const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
+#pragma unroll
+  for (int j = 0; j < G; ++j) {
+    const uint2 qq = *reinterpret_cast<const uint2*>(q + ((size_t)b * q_heads + head0 + j) * 128 + lane * 4);
+    qf[j][0] = pair_lo<false>(qq.x) * scale; qf[j][1] = pair_hi<false>(qq.x) * scale;
+    qf[j][2] = pair_lo<false>(qq.y) * scale; qf[j][3] = pair_hi<false>(qq.y) * scale;
+    acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    mx[j] = -INFINITY;
+    sum[j] = 0.f;
+  }
+  for (int pb = pb_first; pb < p1; pb += kAttnWarps * U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int p = min(pb + u, p1 - 1);
+      if (pb != pb_first || p == len - 1) {
+        kk[u] = *reinterpret_cast<const uint2*>(kb + (size_t)p * 128);
+        vv[u] = *reinterpret_cast<const uint2*>(vb + (size_t)p * 128);
+      }
+    }
+    float s[U][G];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const float k0 = pair_lo<false>(kk[u].x), k1 = pair_hi<false>(kk[u].x), k2 = pair_lo<false>(kk[u].y), k3 = pair_hi<false>(kk[u].y);
+#pragma unroll
+      for (int j = 0; j < G; ++j) s[u][j] = qf[j][0] * k0 + qf[j][1] * k1 + qf[j][2] * k2 + qf[j][3] * k3;
+    }
+    // Sum the 32 lanes' partial dot products.  Not U * G butterflies (5 shuffles each): the
+    // position range is halved with the lane distance, so that after log2(U) rounds a group
+    // of 32 / U lanes holds the G totals of ONE position (u_own), at a fifth of the shuffles.
+    auto halve = [&](auto hc, int off) {
+      constexpr int H = decltype(hc)::value;
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int u = 0; u < H; ++u)
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          const float send = upper ? s[u][j] : s[u + H][j];
+          const float keep = upper ? s[u + H][j] : s[u][j];
+          s[u][j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    };
+    if constexpr (U == 16) {
+      halve(std::integral_constant<int, 8>{}, 16);
+      halve(std::integral_constant<int, 4>{}, 8);
+      halve(std::integral_constant<int, 2>{}, 4);
+      halve(std::integral_constant<int, 1>{}, 2);
+    } else {
+      halve(std::integral_constant<int, 4>{}, 16);
+      halve(std::integral_constant<int, 2>{}, 8);
+      halve(std::integral_constant<int, 1>{}, 4);
+#pragma unroll
+      for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 2);
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 1);
+    const int u_own = lane / (32 / U);
+    const bool live = pb + u_own < p1;
+    float* wrow = wbuf[warp];
+    float corr[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      const float mine = live ? s[0][j] : -INFINITY;
+      float m_new = mine;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, o));
+      m_new = fmaxf(m_new, mx[j]);
+      corr[j] = __expf(mx[j] - m_new);
+      mx[j] = m_new;
+      wrow[u_own * G + j] = __expf(mine - m_new);  // exp(-inf) = 0 for masked positions; every lane of the group writes the same value
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      float l = sum[j] * corr[j], a0 = acc[j][0] * corr[j], a1 = acc[j][1] * corr[j], a2 = acc[j][2] * corr[j],
+            a3 = acc[j][3] * corr[j];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float w = wrow[u * G + j];  // broadcast read
+        l += w;
+        a0 += w * pair_lo<false>(vv[u].x);
+        a1 += w * pair_hi<false>(vv[u].x);
+        a2 += w * pair_lo<false>(vv[u].y);
+        a3 += w * pair_hi<false>(vv[u].y);
+      }
+      sum[j] = l; acc[j][0] = a0; acc[j][1] = a1; acc[j][2] = a2; acc[j][3] = a3;
+    }
+    __syncwarp();  // the weights are read before the next round overwrites them
+  }
+  // merge the warps of the CTA (fixed order)
+#pragma unroll
+  for (int j = 0; j < G; ++j) {
+    *reinterpret_cast<float4*>(&part[warp][j][lane * 4]) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+    if (lane == 0) {
+      part[warp][j][128] = mx[j];
+      part[warp][j][129] = sum[j];
+    }
+  }
+  __syncthreads();
+  attention_finish<G>(part, out, scratch, counters, split, splits, b, kvh, kv_heads, q_heads);
+}
+
+// ---- the same attention on the tensor cores, for grids larger than the GPU --------------------
+// With every query head of a KV head in one CTA the scalar kernel above spends ~120 warp
+// instructions per key at ratios 5 to 8 and is bound by instruction issue, not by HBM.  Here a
+// warp takes 16 keys per step through two `mma.sync.m16n8k16`s:
+//   S^T[head, key]  = Q[head, dim] . K[key, dim]^T   (A = Q, eight heads in rows 0-7, rows 8-15
+//                                                     zero; B = K, read from global memory)
+//   O^T[dim, head] += V[key, dim]^T . P^T[key, head] (A = V through `ldmatrix.trans` from a
+//                                                     shared-memory tile; B = P as bf16)
+// The accumulator layout of the first product is the B-operand layout of the second, so the
+// softmax weights never leave their lane.  The contraction over the 128 dimensions does not
+// care about their order: lane (g, t) reads 16 contiguous bytes (dimensions 32c + 8t .. + 7) of
+// key g per 32-dimension chunk c and uses the four words as the b0/b1 operands of two
+// contraction steps, q being read in the same order.
+// Same grid, slices and hand-over between slices as the scalar kernel; ~25 instructions per key
+// and warp step.  G = query heads per KV head (1..8).
+constexpr int kMmaKeys = 16;                            // keys per warp and step
+constexpr int kMmaPitch = 272;                          // bytes per key in the V tile (256 + 16: conflict-free ldmatrix)
+constexpr int kMmaTile = kMmaKeys * kMmaPitch;          // one V tile
+constexpr int kMmaSmem = kAttnWarps * 2 * kMmaTile;     // two stages per warp; the warps' partial results reuse it
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int G>
+__global__ void __launch_bounds__(kAttnWarps * 32, 2)
+    decode_attention_mma_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
+                                const uint16_t* __restrict__ v_cache, const long long* __restrict__ pos_ptr,
+                                uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
+                                int q_heads, int kv_heads, int max_len, int chunk) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  // As in the scalar kernel: the position and the keys and values of earlier positions may be
+  // read before the kernel that feeds this one has finished; q and position len - 1 may not.
+  const long long pos_now = *pos_ptr;
+  const int len = pos_now < 0 ? 0 : (pos_now >= max_len ? max_len : (int)pos_now + 1);
+  const int p0 = split * chunk, p1 = min(len, p0 + chunk);
+  const uint16_t* kb = k_cache + ((size_t)b * kv_heads + kvh) * max_len * 128;
+  const uint16_t* vb = v_cache + ((size_t)b * kv_heads + kvh) * max_len * 128;
+  unsigned char* tile = mma_smem + warp * 2 * kMmaTile;
+  const uint32_t tile_s = (uint32_t)__cvta_generic_to_shared(tile);
+
+  uint4 k0[4], k1[4];  // keys base + g and base + 8 + g
+  // which: 0 = every position, 1 = all but position len - 1, 2 = position len - 1 only
+  auto load_keys = [&](int base, int which) {
+    const int pa = min(base + g, p1 - 1), pb = min(base + 8 + g, p1 - 1);  // clamped, masked below
+    const uint16_t* r0 = kb + (size_t)pa * 128 + t * 8;
+    const uint16_t* r1 = kb + (size_t)pb * 128 + t * 8;
+    const bool do0 = which == 0 || ((pa == len - 1) == (which == 2));
+    const bool do1 = which == 0 || ((pb == len - 1) == (which == 2));
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (do0) k0[c] = *reinterpret_cast<const uint4*>(r0 + c * 32);
+      if (do1) k1[c] = *reinterpret_cast<const uint4*>(r1 + c * 32);
+    }
+  };
+  auto copy_values = [&](int base, int stage, int which) {  // 16 keys x 256 B, 16 B per lane and instruction
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = i * 32 + lane, key = idx >> 4, seg = idx & 15;
+      const int pv = min(base + key, p1 - 1);
+      const uint16_t* src = vb + (size_t)pv * 128 + seg * 8;
+      const uint32_t dst = tile_s + stage * kMmaTile + key * kMmaPitch + seg * 16;
+      if (which == 0 || ((pv == len - 1) == (which == 2)))
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+  };
+  constexpr int kStride = kAttnWarps * kMmaKeys;
+  int base = p0 + warp * kMmaKeys, stage = 0;
+  if (base < p1) {
+    load_keys(base, 1);
+    copy_values(base, 0, 1);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (base < p1 && base + kMmaKeys >= len) {  // the step that holds the current position (clamped rows repeat it)
+    load_keys(base, 2);
+    copy_values(base, 0, 2);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  uint4 qa[4];  // head g, dimensions 32c + 8t .. + 7
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    qa[c] = g < G ? *reinterpret_cast<const uint4*>(q + ((size_t)b * q_heads + kvh * G + g) * 128 + c * 32 + t * 8)
+                  : make_uint4(0u, 0u, 0u, 0u);
+
+  float o[8][4];  // O^T: dimensions 16m + g (c0, c1) and 16m + 8 + g (c2, c3), heads 2t and 2t + 1
+#pragma unroll
+  for (int m = 0; m < 8; ++m) o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f;
+  float mx = -INFINITY, sum = 0.f;  // of head g; the sum is this lane's share (keys 2t, 2t+1, 8+2t, 9+2t of every step)
+  const float scale = 0.08838834764831845f;  // 1 / sqrt(128)
+  // ldmatrix.x4.trans row addresses: matrix (lane >> 3) = {keys 0-7 | 8-15} x {dims 0-7 | 8-15} of a 16-dimension column block
+  const uint32_t ldm_off = (uint32_t)(((lane & 7) + ((lane >> 4) << 3)) * kMmaPitch + ((lane >> 3) & 1) * 16);
+
+  for (; base < p1; base += kStride, stage ^= 1) {
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};  // heads g (c0, c1): keys 2t, 2t+1 | 8+2t, 9+2t
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      mma_bf16(sa, qa[c].x, 0u, qa[c].y, 0u, k0[c].x, k0[c].y);
+      mma_bf16(sb, qa[c].x, 0u, qa[c].y, 0u, k1[c].x, k1[c].y);
+      mma_bf16(sa, qa[c].z, 0u, qa[c].w, 0u, k0[c].z, k0[c].w);
+      mma_bf16(sb, qa[c].z, 0u, qa[c].w, 0u, k1[c].z, k1[c].w);
+    }
+    // the next step's keys and values are requested while this step's are worked on
+    if (base + kStride < p1) {
+      load_keys(base + kStride, 0);
+      copy_values(base + kStride, stage ^ 1, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int key0 = base + 2 * t;
+    const float s0 = key0 < p1 ? sa[0] * scale : -INFINITY, s1 = key0 + 1 < p1 ? sa[1] * scale : -INFINITY;
+    const float s2 = key0 + 8 < p1 ? sb[0] * scale : -INFINITY, s3 = key0 + 9 < p1 ? sb[1] * scale : -INFINITY;
+    float m_new = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
+    m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 1));
+    m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 2));
+    m_new = fmaxf(m_new, mx);  // finite: the step has at least key `base` below p1
+    const float corr = __expf(mx - m_new);
+    mx = m_new;
+    const float w0 = __expf(s0 - m_new), w1 = __expf(s1 - m_new), w2 = __expf(s2 - m_new), w3 = __expf(s3 - m_new);
+    sum = sum * corr + ((w0 + w1) + (w2 + w3));
+    uint32_t pb0, pb1;  // P^T as the B operand: keys 2t, 2t+1 | 8+2t, 9+2t of head g
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pb0) : "f"(w1), "f"(w0));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pb1) : "f"(w3), "f"(w2));
+    // the accumulators hold heads 2t and 2t + 1: their correction factors sit in lanes 8t and 8t + 4
+    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      o[m][0] *= c_even; o[m][1] *= c_odd; o[m][2] *= c_even; o[m][3] *= c_odd;
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // this step's values have landed
+    __syncwarp();
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      uint32_t a0, a1, a2, a3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                   : "r"(tile_s + stage * kMmaTile + ldm_off + m * 32));
+      mma_bf16(o[m], a0, a1, a2, a3, pb0, pb1);
+    }
+    __syncwarp();  // the tile is read before the step after next overwrites it
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();  // every warp is done with its tiles: the space now holds the warps' results
+  float(*part)[G][132] = reinterpret_cast<float(*)[G][132]>(mma_smem);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+  sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+  if (t == 0 && g < G) {
+    part[warp][g][128] = mx;
+    part[warp][g][129] = sum;
+  }
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    if (2 * t < G) {
+      part[warp][2 * t][16 * m + g] = o[m][0];
+      part[warp][2 * t][16 * m + 8 + g] = o[m][2];
+    }
+    if (2 * t + 1 < G) {
+      part[warp][2 * t + 1][16 * m + g] = o[m][1];
+      part[warp][2 * t + 1][16 * m + 8 + g] = o[m][3];
+    }
+  }
+  __syncthreads();
+  attention_finish<G>(part, out, scratch, counters, split, splits, b, kvh, kv_heads, q_heads);
+}
+
+template <int G>
+int launch_attention_mma(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
+                         void* scratch, void* counters, int batch, int q_heads, int kv_heads, int max_len,
+                         int splits, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  FDK_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    FDK_CUDA(cudaFuncSetAttribute(decode_attention_mma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem));
+    configured[dev & 63] = true;
+  }
+  const int chunk = (max_len + splits - 1) / splits;
+  return launch_pdl(decode_attention_mma_kernel<G>, dim3(splits, kv_heads, batch), dim3(kAttnWarps * 32), (size_t)kMmaSmem,
+                    stream, (const uint16_t*)q, (const uint16_t*)k_cache, (const uint16_t*)v_cache,
+                    (const long long*)pos, (uint16_t*)out, (float*)scratch, (int*)counters, q_heads, kv_heads, max_len,
+                    chunk);
+}
+
 template <int G>
 int launch_attention(const void* q, const void* k_cache, const void* v_cache, const void* pos, void* out,
                      void* scratch, void* counters, int batch, int q_heads, int kv_heads, int max_len,
-                     int splits, int halves, cudaStream_t stream) {
+                     int splits, cudaStream_t stream) {
   const int chunk = (max_len + splits - 1) / splits;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(splits, kv_heads * halves, batch);
-  cfg.blockDim = dim3(kAttnWarps * 32);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  DeviceInfo di;
-  if (int st = device_info(&di)) return st;
-  if ((long long)splits * kv_heads * halves * batch > di.sm_count) {
-    FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G, true>, (const uint16_t*)q, (const uint16_t*)k_cache,
-                                (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
-                                (int*)counters, q_heads, kv_heads, max_len, chunk, halves));
-  } else {
-    FDK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_kernel<G, false>, (const uint16_t*)q, (const uint16_t*)k_cache,
-                                (const uint16_t*)v_cache, (const long long*)pos, (uint16_t*)out, (float*)scratch,
-                                (int*)counters, q_heads, kv_heads, max_len, chunk, halves));
-  }
-  return FDK_OK;
+  return launch_pdl(decode_attention_kernel<G>, dim3(splits, kv_heads, batch), dim3(kAttnWarps * 32), 0, stream,
+                    (const uint16_t*)q, (const uint16_t*)k_cache, (const uint16_t*)v_cache, (const long long*)pos,
+                    (uint16_t*)out, (float*)scratch, (int*)counters, q_heads, kv_heads, max_len, chunk);
 }
 
 }  // namespace
@@ -885,25 +1061,25 @@ extern "C" int fdk_decode_attention(const void* q, const void* k_cache, const vo
   FDK_CHECK_ARG(splits == 1 || (scratch && counters), FDK_ERR_WORKSPACE, "scratch and counters are needed when splits > 1");
   cudaStream_t s = (cudaStream_t)stream;
   const int group = q_heads / kv_heads;
-  // Ratios above 4 need ~175 registers (one CTA of 8 warps per SM).  Where the grid is larger
-  // than the GPU and the context is not sliced, the query heads of a KV head are shared between
-  // two CTAs of half the ratio instead, which run two to an SM.
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
-  if (group > 4 && splits == 1 && (long long)kv_heads * batch > di.sm_count) {
-    switch ((group + 1) / 2) {
-      case 3: return launch_attention<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, 1, 2, s);
-      default: return launch_attention<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, 1, 2, s);
+  // Grids larger than the GPU and grouped-query ratios above 4: the tensor-core kernel.
+  if ((long long)splits * kv_heads * batch > di.sm_count || group > 4) {
+    switch (group) {
+      case 1: return launch_attention_mma<1>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+      case 2: return launch_attention_mma<2>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+      case 3: return launch_attention_mma<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+      case 4: return launch_attention_mma<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+      case 5: return launch_attention_mma<5>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+      case 6: return launch_attention_mma<6>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+      case 7: return launch_attention_mma<7>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+      default: return launch_attention_mma<8>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
     }
   }
   switch (group) {
-    case 1: return launch_attention<1>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
-    case 2: return launch_attention<2>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
-    case 3: return launch_attention<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
-    case 4: return launch_attention<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
-    case 5: return launch_attention<5>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
-    case 6: return launch_attention<6>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
-    case 7: return launch_attention<7>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
-    default: return launch_attention<8>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, 1, s);
+    case 1: return launch_attention<1>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 2: return launch_attention<2>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    case 3: return launch_attention<3>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
+    default: return launch_attention<4>(q, k_cache, v_cache, pos, out, scratch, counters, batch, q_heads, kv_heads, max_len, splits, s);
   }
 }

@@ -335,7 +335,8 @@ def hbm_peak_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
-def run_attention_benchmark(batches: list[int], context: int, q_heads: int, kv_heads: int, log: "Log") -> None:
+def run_attention_benchmark(batches: list[int], context: int, q_heads: int, kv_heads: int, log: "Log",
+                            slices: int | None = None) -> None:
     """Times the decode attention kernel alone: one query token per batch row against a static
     bf16 KV cache (the layout of fdk.llama), a CUDA graph of 20 launches replayed 10 times;
     logs microseconds per launch, the rate at which keys and values are read and the largest
@@ -346,7 +347,7 @@ def run_attention_benchmark(batches: list[int], context: int, q_heads: int, kv_h
     peak, peak_kind = hbm_peak_gbs()
     for batch in batches:
         max_len = context + 129
-        splits = max(1, min(max_len // 128, 148 // (batch * kv_heads), 16))  # as fdk.llama picks
+        splits = slices or native.attention_slices(batch, q_heads, kv_heads, max_len)
         k_cache = torch.randn((batch, kv_heads, max_len, 128), device=device).bfloat16()
         v_cache = torch.randn((batch, kv_heads, max_len, 128), device=device).bfloat16()
         q = torch.randn((batch, q_heads * 128), device=device).bfloat16()
@@ -427,11 +428,12 @@ def _main() -> None:
                         help="Time the decode attention kernel instead (batch sizes from -m, see --context, --heads)")
     parser.add_argument("--context", default=1024, type=int, help="--attention: positions in the KV cache")
     parser.add_argument("--heads", default=[24, 8], type=int, nargs=2, help="--attention: query heads, KV heads")
+    parser.add_argument("--slices", default=None, type=int, help="--attention: context slices (default: as fdk.llama picks)")
     args = parser.parse_args()
 
     if args.attention:
         with Log("py") as log:
-            run_attention_benchmark(args.m, args.context, args.heads[0], args.heads[1], log)
+            run_attention_benchmark(args.m, args.context, args.heads[0], args.heads[1], log, args.slices)
         return
 
     if args.profile == "":

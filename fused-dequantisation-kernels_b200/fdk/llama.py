@@ -231,10 +231,7 @@ class LlamaDecoder(nn.Module):
         self.attn = torch.empty((batch, self.q_heads * 128), device=dev, dtype=dt)
         self.position = torch.zeros((), device=dev, dtype=torch.int64)
         self.host_position = 0  # eager calls made so far (graph replays are bounded on the device instead)
-        # context slices per (batch row, KV head): about 128 keys each (a CTA's eight warps then
-        # load nearly all their keys in one go), as long as that stays within one CTA per SM:
-        # more slices than that only add merge work (16 rows: 16 us unsliced, 32 us in 4 slices)
-        self.splits = max(1, min(max_len // 128, 148 // (batch * self.kv_heads), 16))
+        self.splits = native.attention_slices(batch, self.q_heads, self.kv_heads, max_len)
         self.attn_scratch, self.attn_counters = native.attention_scratch(batch, self.q_heads, self.kv_heads, self.splits, dev)
         # the projections do the norms, the residual adds and the rotary embedding themselves where
         # they can: native quantised layers, one rank, batches up to 16 rows, x small enough to be staged
