@@ -1059,6 +1059,8 @@ extern "C" int fdk_decode_attention(const void* q, const void* k_cache, const vo
                 "q_heads=%d must be 1..%d times kv_heads=%d", q_heads, kMaxGroup, kv_heads);
   FDK_CHECK_ARG(splits >= 1 && splits <= kMaxSplits && max_len > 0, FDK_ERR_BAD_ARG, "splits=%d (1..%d), max_len=%d", splits, kMaxSplits, max_len);
   FDK_CHECK_ARG(splits == 1 || (scratch && counters), FDK_ERR_WORKSPACE, "scratch and counters are needed when splits > 1");
+  FDK_CHECK_ARG((((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) == 0, FDK_ERR_ALIGN,
+                "q, caches and out must be 16-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
   const int group = q_heads / kv_heads;
   DeviceInfo di;

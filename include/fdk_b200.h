@@ -190,7 +190,8 @@ int fdk_silu_mul(const void* gate_up, void* out, int rows, int width, int group,
 /* Decode attention: one query token per batch row against the static KV cache
  * [batch, kv_heads, max_len, 128] (bf16), keys 0 .. *pos (device int64; the current token's
  * key and value must already be appended), grouped-query (q_heads / kv_heads in 1..8).
- * q, out: [batch, q_heads * 128].  The context is cut into `splits` slices handled by
+ * q, out: [batch, q_heads * 128]; q, the caches and out 16-byte aligned (FDK_ERR_ALIGN).
+ * The context is cut into `splits` slices handled by
  * different CTAs; with splits > 1, `scratch` and `counters` of the sizes given by
  * fdk_decode_attention_scratch are needed, BOTH zero-filled once before their first use and
  * then left to the library: the slices hand their sums over as {value, tag} words whose tag

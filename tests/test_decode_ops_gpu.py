@@ -80,9 +80,10 @@ def test_decode_attention_matches_fp32_reference(native, group, splits, batch):
             assert worst <= 2.0**-7 * expected.abs().max().item() + 1e-3, f"pos={pos_value}: max error {worst}"
 
 
-def test_decode_attention_position_outside_the_cache_is_clamped(native):
+@pytest.mark.parametrize("group", [3, 6])  # the scalar and the tensor-core kernel
+def test_decode_attention_position_outside_the_cache_is_clamped(native, group):
     """A position past the cache reads the whole cache and nothing beyond it."""
-    batch, group, splits = 2, 3, 4
+    batch, splits = 2, 4
     q_heads = group * KV_HEADS
     k_cache, v_cache = _cache(16)
     k_cache, v_cache = k_cache[:batch].contiguous(), v_cache[:batch].contiguous()
@@ -95,6 +96,22 @@ def test_decode_attention_position_outside_the_cache_is_clamped(native):
     torch.cuda.synchronize()
     assert (out.float() - expected).pow(2).sum().div(expected.pow(2).sum()).sqrt().item() < 6e-3
     assert native.attention_status(counters, batch, KV_HEADS) == 0
+
+
+def test_decode_attention_rejects_misaligned_pointers(native):
+    """The kernels read 16 bytes per lane: a q that starts 8 bytes into an allocation is refused
+    on the host (nothing is launched)."""
+    batch, q_heads = 2, 6
+    k_cache, v_cache = _cache(16)
+    k_cache, v_cache = k_cache[:batch].contiguous(), v_cache[:batch].contiguous()
+    buffer = torch.zeros(batch * q_heads * 128 + 8, device="cuda", dtype=torch.bfloat16)
+    q = buffer[4:4 + batch * q_heads * 128].view(batch, q_heads * 128)
+    out = torch.empty((batch, q_heads * 128), device="cuda", dtype=torch.bfloat16)
+    scratch, counters = native.attention_scratch(batch, q_heads, KV_HEADS, 1, torch.device("cuda"))
+    with pytest.raises(native.FdkError):
+        native.decode_attention(q, k_cache, v_cache, torch.tensor(5, device="cuda"), out, scratch, counters,
+                                q_heads, KV_HEADS, 1)
+    torch.cuda.synchronize()
 
 
 def rope_reference(x, pos: int, theta: float):
