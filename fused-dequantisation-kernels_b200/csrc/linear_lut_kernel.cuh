@@ -535,15 +535,14 @@ __device__ __forceinline__ bool wait_shared_word(volatile int* word, int want) {
 // resident x); kNormOutput: the deferred form -- x comes with the norm weight folded in and the
 // complete sums are multiplied by the batch rows' norm factors.
 constexpr int kNormNone = 0, kNormInput = 1, kNormOutput = 2;
-// XM: where a warp finds x -- kXDirect: fragments read from L2 as they are needed; kXResident:
-// all of x copied once per CTA into shared memory; kXStreamed: every lane copies the fragments
-// of its warp's next slab into a two-stage ring of its own with cp.async while it works on the
-// current one (larger batches: the copy of x no longer stands before the loop).
-constexpr int kXDirect = 0, kXResident = 1, kXStreamed = 2;
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
+// XM: where a warp finds x -- kXDirect: fragments read from L2 as they are needed (x is small
+// and was just written by the kernel before this one); kXResident: all of x copied once per CTA
+// into shared memory, which the fused RMSNorm needs.  Measured on a B200 at every batch size
+// from 1 to 16 and every decode shape, reading the fragments straight from L2 beats both a
+// resident copy and a per-warp cp.async ring (8192^2: 10.65 -> 10.37 us at one row, 21.0 ->
+// 17.1 us at 16 rows): shared memory is the busiest unit of this kernel (table lookups), and
+// x does not have to go through it.
+constexpr int kXDirect = 0, kXResident = 1;
 
 template <int BITS, int NB, int WARPS, bool FP16, int EPI, int XM, int NORM, bool TEAM>
 __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
@@ -919,34 +918,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     x_lane[nb] = XM == kXResident ? xres_addr + b * p.xres_row + t * 32 : (uint32_t)(b * p.k + t * 16);
   }
 
-  // streamed x: a lane's private ring, [stage][block][n-tile][half] vectors 512 bytes apart
-  constexpr uint32_t kRingStage = L::KSB * NB * 1024;
-  const uint32_t ring_lane = raw + p.xring_off + warp * (2 * kRingStage) + lane * 16;
-  auto issue_x = [&](int stage, int kpos) {  // the fragments of the slab at position kpos of its row tile
-#pragma unroll
-    for (int jb = 0; jb < L::KSB; ++jb) {
-      const int col = (kpos * L::KSB + jb) * kBlock;
-      if (L::KSB == 1 || col < p.k) {
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-          // lanes of unused batch columns copy nothing: what they multiply is never stored
-          if (g + 8 * nb < p.m) {
-            const uint32_t dst = ring_lane + stage * kRingStage + (jb * NB + nb) * 1024;
-            cp_async16(dst, p.x + x_lane[nb] + col);
-            cp_async16(dst + 512, p.x + x_lane[nb] + col + 8);
-          }
-        }
-      }
-    }
-  };
-  if constexpr (XM == kXStreamed) {
-    if (it < c1) issue_x(0, ks);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  }
-
-  // Works on the slab held in `s`, at position `kpos` inside its row tile; `stage` is its half
-  // of the ring of x fragments.
-  auto compute = [&](const SlabRegs<BITS>& s, int kpos, int stage) {
+  // Works on the slab held in `s`, at position `kpos` inside its row tile.
+  auto compute = [&](const SlabRegs<BITS>& s, int kpos) {
     auto block = [&](auto jbc) {
       constexpr int JB = decltype(jbc)::value;
       const int col = (kpos * L::KSB + JB) * kBlock;
@@ -958,9 +931,6 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
         if constexpr (XM == kXResident) {
           lo = ring128(x_lane[nb] + col * 2);
           hi = ring128(x_lane[nb] + col * 2 + 16);
-        } else if constexpr (XM == kXStreamed) {
-          lo = ring128(ring_lane + stage * kRingStage + (JB * NB + nb) * 1024);
-          hi = ring128(ring_lane + stage * kRingStage + (JB * NB + nb) * 1024 + 512);
         } else {
           lo = ldg_l2(p.x + x_lane[nb] + col);
           hi = ldg_l2(p.x + x_lane[nb] + col + 8);
@@ -1003,21 +973,12 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
 
   // One step: start loading the warp's next slab into `nxt`, ask L2 for the one after it, work
   // on the slab in `cur`, move on.  Returns false when the warp has no slab left.
-  auto step = [&](const SlabRegs<BITS>& cur, SlabRegs<BITS>& nxt, int stage) {
+  auto step = [&](const SlabRegs<BITS>& cur, SlabRegs<BITS>& nxt) {
     if (it >= c1) return false;
     if (rt != cur_rt) flush_until(rt);
     if (it + W < c1) load_slab<BITS>(nxt, wp + kStep, lane);
-    if constexpr (XM == kXStreamed) {
-      if (it + W < c1) {
-        int ks_next = ks + W;  // where the warp's next slab sits in its row tile
-        while (ks_next >= p.k_slabs) ks_next -= p.k_slabs;
-        issue_x(stage ^ 1, ks_next);
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the copies just issued: this slab's x is in
-    }
     if (it + 2 * W < c1) prefetch_slab_l2<BITS>(wp + 2 * (size_t)kStep, lane);
-    compute(cur, ks, stage);
+    compute(cur, ks);
     wp += kStep;
     it += W;
     ks += W;
@@ -1028,7 +989,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1)
     return true;
   };
   // two register sets, used alternately
-  while (step(s, s2, 0) && step(s2, s, 1)) {
+  while (step(s, s2) && step(s2, s)) {
   }
   flush_until(rt_last + 1);
   if (timed_out && lane == 0) atomicOr(p.counters + kStatusWord, kStatusTimeout);
@@ -1041,20 +1002,14 @@ inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 // Plans the shared-memory layout of one CTA as offsets from the start of its dynamic shared
 // memory, which kernels see at address `base` of the shared window:
 //   [sync words] ... [table, at a multiple of 64 KB of the window when it is the wide one] ...
-// with the reduction slots, the sums and x (all of it, or the ring of the streamed mode) placed
-// below the table where there is room, above it otherwise.  Chooses how the kernel finds x
-// (*xmode): the fused RMSNorm needs all of x in shared memory.  Otherwise x is streamed where a
-// CTA has few slabs (no staging phase before a short loop: measured 0.1-0.2 us faster up to ~40
-// slabs per CTA) or x is large (a copy per CTA of more than 40 KB costs more than it saves), and
-// staged whole for long loops over a small x (0.2-0.3 us faster from ~80 slabs per CTA on: no
-// cp.async in the loop); whichever does not fit falls back to the other, then to reading
-// fragments straight from L2.  Returns the dynamic size needed.
+// with the reduction slots, the sums and (for the fused RMSNorm) all of x placed below the table
+// where there is room, above it otherwise.  Sets how the kernel finds x (*xmode): resident in
+// shared memory for the fused RMSNorm, read from L2 otherwise; -1 if a resident x does not fit.
+// Returns the dynamic size needed.
 template <int BITS, int NB>
-size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, int slabs_per_cta, LinearParams& p,
-                 int* xmode) {
+size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, LinearParams& p, int* xmode) {
   constexpr bool WIDE = BITS != 3;
   using T = Table<BITS, WIDE>;
-  using L = Layout<BITS>;
   const uint32_t tt = ((p.m < 8 ? p.m : 8) + 1) / 2;
   const uint32_t e_bytes = NB * kSubTiles * 32 * tt * sizeof(float);  // the sums of one row tile
   // large deposits (batches of five rows and more, or two n-tiles) are added up by the compute
@@ -1062,7 +1017,6 @@ size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, int
   const bool team = tt >= 3 || NB == 2;
   const uint32_t xres_row = (uint32_t)p.k * 2 + kXRowPad;
   const uint32_t xres_bytes = align_up((uint32_t)p.m * xres_row, 128);
-  const uint32_t ring_bytes = (uint32_t)warps * 2 * L::KSB * NB * 1024;
   p.team = team ? 1 : 0;
   p.slot_sets = 2;
   p.slot_t = tt;
@@ -1089,22 +1043,17 @@ size_t plan_smem(uint32_t base, int warps, size_t limit, bool need_resident, int
     p.tsum_off = team ? place(3 * e_bytes) : 0;  // two blocks of sums used in turn + the gather block of the push
     p.stash_off = place(e_bytes);
     p.xres_off = mode == kXResident ? place(xres_bytes) : 0;
-    p.xring_off = mode == kXStreamed ? place(ring_bytes) : 0;
     return high;
   };
-  const bool stage_whole = need_resident || (xres_bytes <= 40 * 1024 && slabs_per_cta >= 64);
-  const int order[3] = {stage_whole ? kXResident : kXStreamed, stage_whole ? kXStreamed : kXResident, kXDirect};
-  for (int mode : order) {
-    if (need_resident && mode != kXResident) break;
-    for (uint32_t phases = 1; phases <= (team ? 4u : 1u); phases *= 2) {
-      const size_t need = layout(phases, mode);
-      if (need <= limit) {
-        *xmode = mode;
-        return need;
-      }
+  const int mode = need_resident ? kXResident : kXDirect;
+  for (uint32_t phases = 1; phases <= (team ? 4u : 1u); phases *= 2) {
+    const size_t need = layout(phases, mode);
+    if (need <= limit) {
+      *xmode = mode;
+      return need;
     }
   }
-  *xmode = -1;  // nothing fits (the fused RMSNorm on too large an x)
+  *xmode = -1;  // does not fit (the fused RMSNorm on too large an x)
   return layout(1, kXDirect);
 }
 
@@ -1159,8 +1108,7 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
   if (int st = device_info(&di)) return st;
   const bool norm = p.norm_h != nullptr;
   int xm = kXDirect;
-  const int ctas = sm_count < p.total ? sm_count : p.total;
-  const size_t smem = plan_smem<BITS, NB>(base, WARPS, (size_t)di.max_smem_optin, norm, p.total / ctas, p, &xm);
+  const size_t smem = plan_smem<BITS, NB>(base, WARPS, (size_t)di.max_smem_optin, norm, p, &xm);
   FDK_CHECK_ARG(xm >= 0, FDK_ERR_SHAPE, "the fused RMSNorm needs x [%d, %d] to fit in shared memory", p.m, p.k);
   FDK_CHECK_ARG(smem <= (size_t)di.max_smem_optin, FDK_ERR_CUDA, "shared-memory plan of %zu bytes exceeds %d", smem,
                 di.max_smem_optin);
@@ -1173,12 +1121,6 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
   const int epi = p.tp > 0 ? kEpiPush : p.silu ? kEpiSilu : p.resid_h != nullptr ? kEpiResid : p.rope_pos != nullptr ? kEpiRope : kEpiStore;
 #define FDK_LAUNCH(EPI_, XM_, NORM_) \
   return launch_instance<BITS, NB, WARPS, FP16, EPI_, XM_, NORM_>(p, inl, grid, smem, flags, stream)
-#define FDK_LAUNCH_X(EPI_, NORM_)                                 \
-  do {                                                            \
-    if (xm == kXResident) FDK_LAUNCH(EPI_, kXResident, NORM_);    \
-    if (xm == kXStreamed) FDK_LAUNCH(EPI_, kXStreamed, NORM_);    \
-    FDK_LAUNCH(EPI_, kXDirect, NORM_);                            \
-  } while (0)
   if constexpr (!FP16) {  // the decode fusions exist for bf16 only
     if (norm) {
       if (epi == kEpiStore) FDK_LAUNCH(kEpiStore, kXResident, kNormInput);
@@ -1187,22 +1129,21 @@ int launch_width(LinearParams p, const InlineLut<BITS>& inl, int sm_count, unsig
       FDK_CHECK_ARG(false, FDK_ERR_BAD_ARG, "the fused RMSNorm goes with the plain, SiLU or rotary output only");
     }
     if (p.scale_ss != nullptr) {
-      if (epi == kEpiStore) FDK_LAUNCH_X(kEpiStore, kNormOutput);
-      if (epi == kEpiSilu) FDK_LAUNCH_X(kEpiSilu, kNormOutput);
-      if (epi == kEpiRope) FDK_LAUNCH_X(kEpiRope, kNormOutput);
-      if (epi == kEpiResid) FDK_LAUNCH_X(kEpiResid, kNormOutput);
+      if (epi == kEpiStore) FDK_LAUNCH(kEpiStore, kXDirect, kNormOutput);
+      if (epi == kEpiSilu) FDK_LAUNCH(kEpiSilu, kXDirect, kNormOutput);
+      if (epi == kEpiRope) FDK_LAUNCH(kEpiRope, kXDirect, kNormOutput);
+      if (epi == kEpiResid) FDK_LAUNCH(kEpiResid, kXDirect, kNormOutput);
       FDK_CHECK_ARG(false, FDK_ERR_BAD_ARG, "the deferred RMSNorm does not go with the tensor-parallel push");
     }
-    if (epi == kEpiResid) FDK_LAUNCH_X(kEpiResid, kNormNone);
-    if (epi == kEpiRope) FDK_LAUNCH_X(kEpiRope, kNormNone);
+    if (epi == kEpiResid) FDK_LAUNCH(kEpiResid, kXDirect, kNormNone);
+    if (epi == kEpiRope) FDK_LAUNCH(kEpiRope, kXDirect, kNormNone);
   } else {
     FDK_CHECK_ARG(!norm && p.scale_ss == nullptr && epi != kEpiResid && epi != kEpiRope, FDK_ERR_BAD_ARG,
                   "the decode fusions take bf16 only");
   }
-  if (epi == kEpiPush) FDK_LAUNCH_X(kEpiPush, kNormNone);
-  if (epi == kEpiSilu) FDK_LAUNCH_X(kEpiSilu, kNormNone);
-  FDK_LAUNCH_X(kEpiStore, kNormNone);
-#undef FDK_LAUNCH_X
+  if (epi == kEpiPush) FDK_LAUNCH(kEpiPush, kXDirect, kNormNone);
+  if (epi == kEpiSilu) FDK_LAUNCH(kEpiSilu, kXDirect, kNormNone);
+  FDK_LAUNCH(kEpiStore, kXDirect, kNormNone);
 #undef FDK_LAUNCH
 }
 
@@ -1244,9 +1185,9 @@ int norm_fits_bits(int m, int k, int* fits) {
   p.k = k;
   int xm = -1;
   if (m > 8) {
-    plan_smem<BITS, 2>(base, kGemvWarps<2>, (size_t)di.max_smem_optin, true, 0, p, &xm);
+    plan_smem<BITS, 2>(base, kGemvWarps<2>, (size_t)di.max_smem_optin, true, p, &xm);
   } else {
-    plan_smem<BITS, 1>(base, kGemvWarps<1>, (size_t)di.max_smem_optin, true, 0, p, &xm);
+    plan_smem<BITS, 1>(base, kGemvWarps<1>, (size_t)di.max_smem_optin, true, p, &xm);
   }
   *fits = xm >= 0 ? 1 : 0;
   return FDK_OK;

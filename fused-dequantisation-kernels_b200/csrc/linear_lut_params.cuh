@@ -29,7 +29,6 @@ struct LinearParams {
   uint32_t team;          // 1: the compute warps add their deposits themselves into tsum, the finisher starts there
   uint32_t slot_phases;   // team mode: the deposits of a tile are made and added in this many parts (1, 2, 4)
   uint32_t tsum_off;      // team mode: [2][E] sums used in turn + [E] gather block of the tensor-parallel push
-  uint32_t xring_off;     // streamed x: per warp two stages of [block][n-tile][2][32 lanes][16 B]
   uint32_t xres_off;      // all of x staged once per CTA at this offset (resident x)
   uint32_t xres_row;      // bytes between its rows
   uint32_t stash_off;     // E floats: the other CTAs' sums of a split row tile, fetched ahead by the finisher
