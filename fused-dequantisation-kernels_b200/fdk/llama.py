@@ -117,16 +117,19 @@ class LlamaDecoder(nn.Module):
         self.kv_heads = dims.num_key_value_heads // tp.size
         assert dims.num_key_value_heads % tp.size == 0, "KV heads must split evenly over the ranks"
         assert dims.head_dim == 128
-        # how the fused decode step applies its RMSNorms: by the reading projection while it stages
-        # x, with the framework model's roundings (False), or split between the projections that
-        # write and read the residual stream (True: ~0.5 us less per norm, one bf16 rounding per
-        # element of x placed differently; measured +4 % tokens/s at batch 4, nothing at batch 1)
-        self.deferred_norm = False
+        # how the fused decode step applies its RMSNorms: split between the projections that write
+        # and read the residual stream (True: the reading projection takes its x fragments straight
+        # from L2 like every other projection and scales its sums; one bf16 rounding per element
+        # of x sits elsewhere than in the framework model), or by the reading projection while it
+        # copies x into shared memory, with the framework model's roundings (False).  Measured on
+        # the 4B shape, tokens/s split / while copying: batch 1: 754 / 740, 2: 1456 / 1426,
+        # 4: 2426 / 2298
+        self.deferred_norm = True
         # largest batch whose projections carry the decode-step fusions.  Measured on the 4B shape
-        # (tokens/s fused against separate glue kernels): batch 1: 712 / 686, 2: 1367 / 1354,
-        # 4: 2117 / 2241, 8: 3256 / 3430, 16: 4269 / 5152 -- the single finisher warp goes through
-        # all batch rows, and the small glue kernels overlap their neighbours well
-        self.fuse_rows = 2
+        # (tokens/s fused against separate glue kernels): batch 1: 754 / 719, 2: 1456 / 1397,
+        # 4: 2426 / 2374, 8: 3780 / 3838 -- the single finisher warp goes through all batch rows,
+        # and the small glue kernels overlap their neighbours well
+        self.fuse_rows = 4
         # largest batch whose q|k|v projection does the rotary embedding + KV append in its epilogue
         # in the tensor-parallel step (where the norms cannot be fused)
         self.rope_rows = 16
@@ -439,10 +442,10 @@ class LlamaDecoder(nn.Module):
         """The same step in five kernels per layer: the q|k|v projection does the rotary embedding
         + KV append in its epilogue; the o and down projections add their result to the residual
         stream and leave the sums of squares for the next norm; the gate|up projection writes
-        SiLU(gate) * up.  The RMSNorms are either applied by the q|k|v and gate|up projections
-        while they stage x (the default), or (`deferred_norm`) split: the
+        SiLU(gate) * up.  The RMSNorms are either split (`deferred_norm`, the default): the
         projection that writes the residual stream also writes norm weight * h, and the one that
-        reads it multiplies its sums by the norm factor."""
+        reads it multiplies its sums by the norm factor; or applied by the q|k|v and gate|up
+        projections while they copy x into shared memory."""
         dims, eps, b = self.dims, self.dims.rms_norm_eps, self.batch
         native.rope_table(self.position, self.rope_tab, dims.rope_theta)
         if self.deferred_norm:
