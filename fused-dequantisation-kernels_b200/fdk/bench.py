@@ -223,7 +223,10 @@ class LutBenchmark(Benchmark):
         lut8 = torch.cartesian_prod(*[lut] * (8 // s.bits)).view(256, -1)
         bs = torch.rand((s.copies, s.n, s.k // s.g), device="cuda", dtype=self.dtype)
         out = torch.empty(o_shape, device="cuda", dtype=self.dtype)
-        fn = lambda i: self.fn(a[i % s.copies], bq[i % s.copies], lut8, bs[i % s.copies], out[i % s.copies])
+        # one tensor object per weight set, made once: the native operators keep the repacked form
+        # of a weight tensor per tensor OBJECT, and a fresh view per call would be repacked per call
+        bqs, bss = list(bq.unbind(0)), list(bs.unbind(0))
+        fn = lambda i: self.fn(a[i % s.copies], bqs[i % s.copies], lut8, bss[i % s.copies], out[i % s.copies])
         for i in range(s.copies):  # one-time work per weight set (the native path repacks it) stays out of the timing
             fn(i)
         return fn
@@ -424,6 +427,8 @@ def _main() -> None:
     parser.add_argument("--profile", default="", help="Select a specific method to profile (skip tests)")
     parser.add_argument("--include", default="", help="Methods to include (regex)")
     parser.add_argument("--exclude", default="_ref", help="Methods to exclude (regex)")
+    parser.add_argument("--pdl", action="store_true",
+                        help="Launch the native LUT operators with programmatic dependent launch (as a decode loop does)")
     parser.add_argument("--attention", action="store_true",
                         help="Time the decode attention kernel instead (batch sizes from -m, see --context, --heads)")
     parser.add_argument("--context", default=1024, type=int, help="--attention: positions in the KV cache")
@@ -436,6 +441,7 @@ def _main() -> None:
             run_attention_benchmark(args.m, args.context, args.heads[0], args.heads[1], log, args.slices)
         return
 
+    kernels.programmatic_launch = args.pdl
     if args.profile == "":
         run_tests()
 

@@ -71,6 +71,13 @@ def tiled_for(b: Tensor, bs: Tensor, n: int, k: int, bits: int) -> Tensor:
 
 ### native operators
 
+# Programmatic dependent launch for the two operators below: the kernel may be scheduled while
+# the previous kernel of the stream is still running, reads its weights and its table right
+# away and waits for that kernel only before it reads x or writes out.  Off by default: it is
+# for callers whose weights do not change between launches (a decode loop, a benchmark).
+programmatic_launch = False
+
+
 
 def run_mv_lut(a: Tensor, b: Tensor, lut: Tensor, bs: Tensor, out: Tensor) -> None:
     # shape inference
@@ -85,7 +92,7 @@ def run_mv_lut(a: Tensor, b: Tensor, lut: Tensor, bs: Tensor, out: Tensor) -> No
     assert bs.shape == (n, k // group_size)
     assert lut.shape == ((8, 1) if bits == 3 else (256, 8 // bits))
     assert all([t.is_contiguous() for t in [a, b, lut, bs, out]])
-    native.linear_lut(a[None], tiled_for(b, bs, n, k, bits), lut, out[None], n, k, bits)
+    native.linear_lut(a[None], tiled_for(b, bs, n, k, bits), lut, out[None], n, k, bits, pdl=programmatic_launch)
 
 
 def run_mm_lut(a: Tensor, b: Tensor, lut: Tensor, bs: Tensor, out: Tensor) -> None:
@@ -102,7 +109,7 @@ def run_mm_lut(a: Tensor, b: Tensor, lut: Tensor, bs: Tensor, out: Tensor) -> No
     assert lut.shape == ((8, 1) if bits == 3 else (256, 8 // bits))
     assert out.shape == (m, n)
     assert all([t.is_contiguous() for t in [a, b, lut, out]])
-    native.linear_lut(a, tiled_for(b, bs, n, k, bits), lut, out, n, k, bits)
+    native.linear_lut(a, tiled_for(b, bs, n, k, bits), lut, out, n, k, bits, pdl=programmatic_launch)
 
 
 def dequantise(b: Tensor, lut: Tensor, bs: Tensor) -> Tensor:
