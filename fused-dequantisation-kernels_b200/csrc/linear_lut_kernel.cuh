@@ -2,7 +2,7 @@
 // W given as tiled low-bit codes + block scales + a lookup table (fdk_layout.cuh).
 //
 // Shape of the kernel (one persistent CTA per SM: 19 compute warps and one finisher warp for
-// batches up to 8 rows, 15 + 1 for 9 to 16 rows):
+// batches up to 8 rows, 11 + 1 for 9 to 16 rows):
 //   * The weight stream is cut into slabs (64 rows x 64*KSB columns, 2-6 KB).  The
 //     slabs of the whole matrix form one linear sequence (row tile major); CTA c owns
 //     a contiguous range of it ("stream-K"), its compute warps take slabs round-robin.
@@ -15,8 +15,9 @@
 //     (prefetch.global.L2, a line per lane).  The codes never pass through shared
 //     memory.  The first loads are issued before the kernel waits for its predecessor
 //     on the stream (programmatic dependent launch): they read weights only.
-//   * x is copied once per CTA into shared memory when it fits (after the wait),
-//     otherwise its fragments are read from L2 as they are needed.
+//   * Every warp reads the x fragments of its slab from L2 as it needs them (x is small and
+//     was just written); only the fused RMSNorm keeps a copy of x in shared memory, which
+//     is otherwise left to the table lookups.
 //   * Codes are turned into tensor-core A fragments by table lookup in shared memory:
 //     one code byte indexes a byte table replicated per lane (lut_table.cuh) whose rows
 //     are 256 bytes apart in a table that starts at a multiple of 64 KB of the shared
