@@ -266,15 +266,15 @@ extern "C" int fdk_linear_lut_host(const void* x_host, const void* tiled, const 
   }
   // behind a kernel the projection may start early: it only reads weights before it waits
   const unsigned inner = (flags & ~FDK_FLAG_NO_SYNC) | (x_mapped != nullptr ? FDK_FLAG_PDL : 0u);
-  if (int st = linear_lut_impl(x_dev, tiled, lut, lut_host, out_dev, m, n, k, bits, dtype, workspace, workspace_bytes,
+  // The result is written once and never read back by the kernels: into mapped host memory the
+  // projection stores it itself (posted writes over PCIe), which saves a copy per call.  x is
+  // read by every CTA and does need its copy in device memory.
+  void* out = out_mapped != nullptr ? out_mapped : out_dev;
+  if (int st = linear_lut_impl(x_dev, tiled, lut, lut_host, out, m, n, k, bits, dtype, workspace, workspace_bytes,
                                inner, nullptr, nullptr, stream)) {
     return st;
   }
-  if (out_mapped != nullptr) {
-    if (int st = launch_host_copy(out_dev, out_mapped, out_bytes, s)) return st;
-  } else {
-    FDK_CUDA(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, s));
-  }
+  if (out_mapped == nullptr) FDK_CUDA(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, s));
   if (!(flags & FDK_FLAG_NO_SYNC)) FDK_CUDA(cudaStreamSynchronize(s));
   return FDK_OK;
 }

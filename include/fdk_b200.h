@@ -213,7 +213,8 @@ int fdk_decode_attention(const void* q, const void* k_cache, const void* v_cache
  * into out_dev, out_dev -> out_host [m, n], and a synchronisation of `stream`: out_host is valid
  * on return (FDK_FLAG_NO_SYNC leaves the synchronisation to the caller).  x_host and out_host should be page-locked for the copies to be asynchronous;
  * x_dev [m, k] and out_dev [m, n] are device staging buffers of the caller (nothing is allocated
- * here).  Other arguments as fdk_linear_lut. */
+ * here); where out_host is page-locked, mapped and 16-byte aligned the projection stores its
+ * result straight into it and out_dev is left untouched.  Other arguments as fdk_linear_lut. */
 int fdk_linear_lut_host(const void* x_host, const void* tiled, const void* lut, const void* lut_host,
                         void* out_host, int m, int n, int k, int bits, int dtype, void* x_dev, void* out_dev,
                         void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
