@@ -108,3 +108,21 @@ def test_exchange_entry_points_validate_without_a_gpu(lib):
     ex = native.make_exchange(2, 1, [4096, 8192], 512)
     assert (ex.tp, ex.rank, ex.slot_elems, ex.buffers[1]) == (2, 1, 512, 8192)
     assert ctypes.sizeof(native.TpExchange) == 8 + 8 * 8 + 8
+
+
+def test_attention_slice_plan():
+    """`attention_slices`: about 96 keys or more per slice, at most 16 slices, the grid within the
+    given number of CTAs (two per SM of a B200 here)."""
+    from fdk import native
+
+    plan = lambda batch, kv, max_len: native.attention_slices(batch, 3 * kv, kv, max_len, ctas=296)
+    assert plan(1, 8, 1153) == 12      # context 1024 of the 4B model: 12 slices of 97 keys
+    assert plan(1, 8, 2177) == 16      # capped
+    assert plan(4, 8, 1153) == 9       # 296 // 32
+    assert plan(16, 8, 1153) == 2
+    assert plan(64, 8, 1153) == 1      # larger than the GPU already: one slice
+    assert plan(1, 8, 64) == 1         # fewer than 96 keys: one slice
+    for batch in (1, 2, 3, 5, 8, 13, 40):
+        for kv in (1, 2, 8):
+            s = plan(batch, kv, 4096)
+            assert 1 <= s <= 16 and (s == 1 or s * batch * kv <= 296)
