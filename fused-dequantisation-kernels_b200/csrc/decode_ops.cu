@@ -699,9 +699,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1)
                             const uint16_t* __restrict__ v_cache, const long long* __restrict__ pos_ptr,
                             uint16_t* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
                             int q_heads, int kv_heads, int max_len, int chunk) {
+  static_assert(G >= 1 && G <= 4, "ratios above 4 take the tensor-core kernel");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ __align__(16) float part[kAttnWarps][G][132];
-  __shared__ float wbuf[kAttnWarps][16 * 4 > 8 * G ? 16 * 4 : 8 * G];  // softmax weights of a round, per warp: U * G
+  __shared__ float wbuf[kAttnWarps][16 * G];  // softmax weights of a round, per warp: U * G
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
   const int head0 = kvh * G;  // this CTA's first query head
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -774,18 +775,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1)
           s[u][j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
         }
     };
-    if constexpr (U == 16) {
-      halve(std::integral_constant<int, 8>{}, 16);
-      halve(std::integral_constant<int, 4>{}, 8);
-      halve(std::integral_constant<int, 2>{}, 4);
-      halve(std::integral_constant<int, 1>{}, 2);
-    } else {
-      halve(std::integral_constant<int, 4>{}, 16);
-      halve(std::integral_constant<int, 2>{}, 8);
-      halve(std::integral_constant<int, 1>{}, 4);
-#pragma unroll
-      for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 2);
-    }
+    static_assert(U == 16, "four halving rounds take sixteen positions down to one per pair of lanes");
+    halve(std::integral_constant<int, 8>{}, 16);
+    halve(std::integral_constant<int, 4>{}, 8);
+    halve(std::integral_constant<int, 2>{}, 4);
+    halve(std::integral_constant<int, 1>{}, 2);
 #pragma unroll
     for (int j = 0; j < G; ++j) s[0][j] += __shfl_xor_sync(0xffffffffu, s[0][j], 1);
     const int u_own = lane / (32 / U);
